@@ -1,0 +1,97 @@
+"""Builds the native library in-tree with nvcc for sm_100a.
+
+The reference builds one executable per `.cu` with a Makefile
+(`Makefile:33-40`, `nvcc -std=c++17 -O3 -arch=$(CUDA_ARCH)`); here every kernel
+goes into one shared library, `credit_b200/lib/libcredit_b200.so`, plus thin
+command-line front ends that link against it.
+"""
+from __future__ import annotations
+
+import os
+import shutil
+import subprocess
+import sys
+from pathlib import Path
+
+PACKAGE_DIR = Path(__file__).resolve().parent
+REPO_ROOT = PACKAGE_DIR.parent
+CSRC = PACKAGE_DIR / "csrc"
+LIB_DIR = PACKAGE_DIR / "lib"
+BIN_DIR = PACKAGE_DIR / "bin"
+LIB_PATH = LIB_DIR / "libcredit_b200.so"
+
+ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
+COMMON_FLAGS = ["-std=c++17", "-O3", "-lineinfo", *ARCH_FLAGS]
+
+# Sources of the shared library (every other file in csrc/ is a header).
+LIB_SOURCES = ["launch.cu"]
+# name of the executable -> source
+CLI_SOURCES: dict[str, str] = {}
+
+
+def nvcc_path() -> str:
+    found = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    if not Path(found).exists():
+        raise RuntimeError("nvcc not found: the native library cannot be built")
+    return found
+
+
+def _newest_source_mtime() -> float:
+    paths = list(CSRC.glob("*")) + [REPO_ROOT / "include" / "credit_b200.h"]
+    return max(p.stat().st_mtime for p in paths if p.is_file())
+
+
+def _run(cmd: list[str], verbose: bool) -> str:
+    result = subprocess.run(cmd, text=True, capture_output=True, check=False)
+    if result.returncode != 0:
+        raise RuntimeError(
+            f"command failed ({result.returncode}): {' '.join(cmd)}\n{result.stdout}\n{result.stderr}"
+        )
+    if verbose:
+        sys.stderr.write(result.stdout + result.stderr)
+    return result.stdout + result.stderr
+
+
+def build_library(force: bool = False, verbose: bool = False, ptxas_log: Path | None = None) -> Path:
+    """Compiles libcredit_b200.so if it is missing or older than its sources."""
+    LIB_DIR.mkdir(parents=True, exist_ok=True)
+    if not force and LIB_PATH.exists() and LIB_PATH.stat().st_mtime >= _newest_source_mtime():
+        return LIB_PATH
+    cmd = [
+        nvcc_path(), *COMMON_FLAGS, "-Xcompiler", "-fPIC", "-shared", "-Xptxas", "-v",
+        "-o", str(LIB_PATH), *[str(CSRC / s) for s in LIB_SOURCES],
+    ]
+    log = _run(cmd, verbose)
+    if ptxas_log is not None:
+        ptxas_log.write_text(log)
+    return LIB_PATH
+
+
+def build_cli(force: bool = False, verbose: bool = False) -> list[Path]:
+    """Compiles the command-line front ends (they link against the library)."""
+    BIN_DIR.mkdir(parents=True, exist_ok=True)
+    build_library(force=force, verbose=verbose)
+    built = []
+    for name, source in CLI_SOURCES.items():
+        out = BIN_DIR / name
+        src = CSRC / source
+        if not force and out.exists() and out.stat().st_mtime >= max(src.stat().st_mtime, LIB_PATH.stat().st_mtime):
+            built.append(out)
+            continue
+        cmd = [
+            nvcc_path(), *COMMON_FLAGS, f"-DCREDIT_CLI_WORKLOAD_{name.upper()}=1", "-o", str(out), str(src),
+            f"-L{LIB_DIR}", "-lcredit_b200", "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN/../lib",
+        ]
+        _run(cmd, verbose)
+        built.append(out)
+    return built
+
+
+def build_all(force: bool = False, verbose: bool = False) -> None:
+    build_library(force=force, verbose=verbose)
+    build_cli(force=force, verbose=verbose)
+
+
+if __name__ == "__main__":
+    build_all(force="--force" in sys.argv, verbose="-v" in sys.argv)
+    print(LIB_PATH)

@@ -1,0 +1,743 @@
+// Host side of the C ABI declared in include/credit_b200.h: argument checks,
+// launch planning (cluster size, slice, ring depth, grid), cached function
+// attributes and the cluster launches themselves. This is the one shared
+// launcher that replaces the host glue every reference binary carries a copy of
+// (query_device_info, benchmark_block_*, benchmark_cluster;
+// src/workloads/layernorm_backward.cu:440-593).
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <map>
+#include <mutex>
+#include <tuple>
+
+#include "../../include/credit_b200.h"
+#include "norm_kernels.cuh"
+#include "reduce_kernels.cuh"
+
+namespace credit {
+
+// Device status word: kernels OR their failure bits into it.
+__device__ int g_status_word;
+
+namespace {
+
+thread_local char t_last_error[512] = "";
+
+int fail(int code, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(t_last_error, sizeof(t_last_error), fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+int cuda_fail(cudaError_t err, const char* what) {
+    return fail(CREDIT_ERR_CUDA, "%s: %s", what, cudaGetErrorString(err));
+}
+
+#define CREDIT_CUDA_TRY(expr)                                  \
+    do {                                                       \
+        cudaError_t err__ = (expr);                            \
+        if (err__ != cudaSuccess) return cuda_fail(err__, #expr); \
+    } while (0)
+
+struct DeviceState {
+    bool ready = false;
+    credit_device_info info{};
+    int* status_ptr = nullptr;
+};
+
+std::mutex g_mutex;
+std::map<int, DeviceState> g_devices;
+// (device, function) pairs whose attributes are already set.
+std::map<std::pair<int, const void*>, bool> g_prepared;
+// (device, function, cluster, smem, threads) -> co-resident clusters
+std::map<std::tuple<int, const void*, int, int, int>, int> g_active_clusters;
+
+int load_device(int device, DeviceState** out) {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    DeviceState& st = g_devices[device];
+    if (!st.ready) {
+        cudaDeviceProp prop{};
+        CREDIT_CUDA_TRY(cudaGetDeviceProperties(&prop, device));
+        std::memset(&st.info, 0, sizeof(st.info));
+        std::snprintf(st.info.name, sizeof(st.info.name), "%s", prop.name);
+        st.info.sm_major = prop.major;
+        st.info.sm_minor = prop.minor;
+        st.info.sm_count = prop.multiProcessorCount;
+        int cluster_launch = 0;
+        CREDIT_CUDA_TRY(cudaDeviceGetAttribute(&cluster_launch, cudaDevAttrClusterLaunch, device));
+        st.info.cluster_launch = cluster_launch;
+        st.info.max_cluster_size = cluster_launch ? kMaxClusterSize : 1;
+        st.info.max_dynamic_smem_per_block = static_cast<int>(prop.sharedMemPerBlockOptin);
+        st.info.smem_per_sm = static_cast<int>(prop.sharedMemPerMultiprocessor);
+        st.info.l2_bytes = prop.l2CacheSize;
+        int khz = 0;
+        CREDIT_CUDA_TRY(cudaDeviceGetAttribute(&khz, cudaDevAttrClockRate, device));
+        st.info.clock_khz = khz;
+        CREDIT_CUDA_TRY(cudaDeviceGetAttribute(&khz, cudaDevAttrMemoryClockRate, device));
+        st.info.mem_clock_khz = khz;
+        int bits = 0;
+        CREDIT_CUDA_TRY(cudaDeviceGetAttribute(&bits, cudaDevAttrGlobalMemoryBusWidth, device));
+        st.info.mem_bus_bits = bits;
+        int current = 0;
+        CREDIT_CUDA_TRY(cudaGetDevice(&current));
+        if (current != device) CREDIT_CUDA_TRY(cudaSetDevice(device));
+        void* sym = nullptr;
+        cudaError_t err = cudaGetSymbolAddress(&sym, g_status_word);
+        if (err == cudaSuccess) err = cudaMemset(sym, 0, sizeof(int));
+        if (current != device) cudaSetDevice(current);
+        if (err != cudaSuccess) return cuda_fail(err, "status word set-up");
+        st.status_ptr = static_cast<int*>(sym);
+        st.ready = true;
+    }
+    *out = &st;
+    return CREDIT_OK;
+}
+
+int current_device_state(DeviceState** out) {
+    int device = 0;
+    CREDIT_CUDA_TRY(cudaGetDevice(&device));
+    return load_device(device, out);
+}
+
+int prepare_function(int device, const void* func, int max_smem) {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    auto key = std::make_pair(device, func);
+    if (g_prepared.count(key)) return CREDIT_OK;
+    cudaFuncAttributes fa{};
+    CREDIT_CUDA_TRY(cudaFuncGetAttributes(&fa, func));
+    // static + dynamic shared memory together must stay within the opt-in limit
+    const int max_dynamic = max_smem - static_cast<int>(fa.sharedSizeBytes);
+    CREDIT_CUDA_TRY(cudaFuncSetAttribute(func, cudaFuncAttributeMaxDynamicSharedMemorySize, max_dynamic));
+    CREDIT_CUDA_TRY(cudaFuncSetAttribute(func, cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
+    g_prepared[key] = true;
+    return CREDIT_OK;
+}
+
+struct Launch {
+    const void* func = nullptr;
+    int grid = 0;
+    int threads = 0;
+    int cluster = 1;
+    int smem = 0;
+    cudaStream_t stream = nullptr;
+};
+
+void fill_config(const Launch& l, cudaLaunchConfig_t* cfg, cudaLaunchAttribute* attr) {
+    std::memset(cfg, 0, sizeof(*cfg));
+    cfg->gridDim = dim3(static_cast<unsigned>(l.grid));
+    cfg->blockDim = dim3(static_cast<unsigned>(l.threads));
+    cfg->dynamicSmemBytes = static_cast<size_t>(l.smem);
+    cfg->stream = l.stream;
+    attr->id = cudaLaunchAttributeClusterDimension;
+    attr->val.clusterDim.x = static_cast<unsigned>(l.cluster);
+    attr->val.clusterDim.y = 1;
+    attr->val.clusterDim.z = 1;
+    cfg->attrs = attr;
+    cfg->numAttrs = 1;
+}
+
+int launch_cluster_kernel(const Launch& l, void** args) {
+    cudaLaunchConfig_t cfg;
+    cudaLaunchAttribute attr;
+    fill_config(l, &cfg, &attr);
+    CREDIT_CUDA_TRY(cudaLaunchKernelExC(&cfg, l.func, args));
+    return CREDIT_OK;
+}
+
+// Clusters of this shape that can be resident at once on the device.
+int max_active_clusters(int device, const void* func, int cluster, int smem, int threads,
+                        int* out) {
+    auto key = std::make_tuple(device, func, cluster, smem, threads);
+    {
+        std::lock_guard<std::mutex> lock(g_mutex);
+        auto it = g_active_clusters.find(key);
+        if (it != g_active_clusters.end()) {
+            *out = it->second;
+            return CREDIT_OK;
+        }
+    }
+    Launch l;
+    l.func = func;
+    l.grid = cluster;
+    l.threads = threads;
+    l.cluster = cluster;
+    l.smem = smem;
+    cudaLaunchConfig_t cfg;
+    cudaLaunchAttribute attr;
+    fill_config(l, &cfg, &attr);
+    int n = 0;
+    cudaError_t err = cudaOccupancyMaxActiveClusters(&n, func, &cfg);
+    if (err != cudaSuccess) {
+        cudaGetLastError();
+        return fail(CREDIT_ERR_UNSUPPORTED,
+                    "cluster size %d with %d B shared memory and %d threads cannot be scheduled: %s",
+                    cluster, smem, threads, cudaGetErrorString(err));
+    }
+    if (n <= 0) {
+        return fail(CREDIT_ERR_UNSUPPORTED,
+                    "cluster size %d with %d B shared memory and %d threads: no resident cluster",
+                    cluster, smem, threads);
+    }
+    std::lock_guard<std::mutex> lock(g_mutex);
+    g_active_clusters[key] = n;
+    *out = n;
+    return CREDIT_OK;
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+int round_up(int v, int m) { return (v + m - 1) / m * m; }
+
+bool valid_cluster_size(int p) { return p == 1 || p == 2 || p == 4 || p == 8 || p == 16; }
+
+struct Shape {
+    int rows;
+    int cols;
+    int elem_bytes;
+    int vec_elems;
+};
+
+int check_shape(int64_t rows, int64_t cols, int dtype, Shape* s) {
+    if (dtype != CREDIT_F32 && dtype != CREDIT_BF16)
+        return fail(CREDIT_ERR_INVALID_ARGUMENT, "unknown dtype %d", dtype);
+    if (rows < 0 || rows > (1ll << 30))
+        return fail(CREDIT_ERR_INVALID_ARGUMENT, "rows=%lld out of range [0, 2^30]",
+                    static_cast<long long>(rows));
+    if (cols < 1 || cols > (1ll << 30))
+        return fail(CREDIT_ERR_INVALID_ARGUMENT, "cols=%lld out of range [1, 2^30]",
+                    static_cast<long long>(cols));
+    s->rows = static_cast<int>(rows);
+    s->cols = static_cast<int>(cols);
+    s->elem_bytes = dtype == CREDIT_F32 ? 4 : 2;
+    s->vec_elems = 16 / s->elem_bytes;
+    return CREDIT_OK;
+}
+
+int check_opts(const credit_launch_opts* o, credit_launch_opts* out) {
+    credit_launch_opts z{};
+    if (o != nullptr) z = *o;
+    if (z.cluster_size != 0 && !valid_cluster_size(z.cluster_size))
+        return fail(CREDIT_ERR_INVALID_ARGUMENT, "cluster_size must be 0, 1, 2, 4, 8 or 16 (got %d)",
+                    z.cluster_size);
+    if (z.variant < CREDIT_VARIANT_AUTO || z.variant > CREDIT_VARIANT_CLUSTER_SMEM)
+        return fail(CREDIT_ERR_INVALID_ARGUMENT, "unknown variant %d", z.variant);
+    if (z.stages < 0 || z.stages > kMaxStages)
+        return fail(CREDIT_ERR_INVALID_ARGUMENT, "stages must be in [0, %d] (got %d)", kMaxStages,
+                    z.stages);
+    if (z.threads != 0 && z.threads != 256 && z.threads != 512)
+        return fail(CREDIT_ERR_INVALID_ARGUMENT, "threads must be 0, 256 or 512 (got %d)", z.threads);
+    if (z.schedule < CREDIT_SCHEDULE_AUTO || z.schedule > CREDIT_SCHEDULE_PERSISTENT)
+        return fail(CREDIT_ERR_INVALID_ARGUMENT, "unknown schedule %d", z.schedule);
+    if (z.load_path < CREDIT_LOAD_AUTO || z.load_path > CREDIT_LOAD_LDG)
+        return fail(CREDIT_ERR_INVALID_ARGUMENT, "unknown load_path %d", z.load_path);
+    if (z.chunk_bytes < 0 || z.chunk_bytes % 1024 != 0 || z.chunk_bytes > 65536)
+        return fail(CREDIT_ERR_INVALID_ARGUMENT,
+                    "chunk_bytes must be a multiple of 1024 up to 65536 (got %d)", z.chunk_bytes);
+    if (z.variant == CREDIT_VARIANT_BLOCK_SMEM || z.variant == CREDIT_VARIANT_BLOCK_READ) {
+        if (z.cluster_size > 1)
+            return fail(CREDIT_ERR_INVALID_ARGUMENT, "block variants run with cluster_size 1 (got %d)",
+                        z.cluster_size);
+        z.cluster_size = 1;
+    }
+    if (z.variant == CREDIT_VARIANT_CLUSTER_SMEM && z.cluster_size == 1)
+        return fail(CREDIT_ERR_INVALID_ARGUMENT, "the cluster variant needs cluster_size >= 2");
+    *out = z;
+    return CREDIT_OK;
+}
+
+// ---------------------------------------------------------------------------
+// kernel tables
+// ---------------------------------------------------------------------------
+template <typename T>
+const void* rmsnorm_func(int threads, bool aligned) {
+    if (threads == 512)
+        return aligned ? (const void*)rmsnorm_fwd_kernel<T, 512, true>
+                       : (const void*)rmsnorm_fwd_kernel<T, 512, false>;
+    return aligned ? (const void*)rmsnorm_fwd_kernel<T, 256, true>
+                   : (const void*)rmsnorm_fwd_kernel<T, 256, false>;
+}
+
+template <typename T>
+const void* layernorm_fwd_func(int threads, bool aligned) {
+    if (threads == 512)
+        return aligned ? (const void*)layernorm_fwd_kernel<T, 512, true>
+                       : (const void*)layernorm_fwd_kernel<T, 512, false>;
+    return aligned ? (const void*)layernorm_fwd_kernel<T, 256, true>
+                   : (const void*)layernorm_fwd_kernel<T, 256, false>;
+}
+
+// dx only; statistics recomputed (has_stats=false) or given.
+template <typename T>
+const void* layernorm_bwd_dx_func(int threads, bool aligned, bool has_stats) {
+    if (has_stats) {
+        if (threads == 512)
+            return aligned ? (const void*)layernorm_bwd_kernel<T, 512, 1, true, true, false>
+                           : (const void*)layernorm_bwd_kernel<T, 512, 1, false, true, false>;
+        return aligned ? (const void*)layernorm_bwd_kernel<T, 256, 1, true, true, false>
+                       : (const void*)layernorm_bwd_kernel<T, 256, 1, false, true, false>;
+    }
+    if (threads == 512)
+        return aligned ? (const void*)layernorm_bwd_kernel<T, 512, 1, true, false, false>
+                       : (const void*)layernorm_bwd_kernel<T, 512, 1, false, false, false>;
+    return aligned ? (const void*)layernorm_bwd_kernel<T, 256, 1, true, false, false>
+                   : (const void*)layernorm_bwd_kernel<T, 256, 1, false, false, false>;
+}
+
+template <typename T>
+const void* layernorm_bwd_grads_func(int threads, int vpt) {
+    if (threads == 512) {
+        if (vpt == 1) return (const void*)layernorm_bwd_kernel<T, 512, 1, true, true, true>;
+        if (vpt == 2) return (const void*)layernorm_bwd_kernel<T, 512, 2, true, true, true>;
+        return (const void*)layernorm_bwd_kernel<T, 512, 4, true, true, true>;
+    }
+    if (vpt == 1) return (const void*)layernorm_bwd_kernel<T, 256, 1, true, true, true>;
+    if (vpt == 2) return (const void*)layernorm_bwd_kernel<T, 256, 2, true, true, true>;
+    return (const void*)layernorm_bwd_kernel<T, 256, 4, true, true, true>;
+}
+
+const void* row_reduce_func(int load_path, int threads, bool aligned) {
+    if (load_path == CREDIT_LOAD_TMA)
+        return threads == 512 ? (const void*)row_reduce_tma_kernel<512>
+                              : (const void*)row_reduce_tma_kernel<256>;
+    if (!aligned) return (const void*)row_reduce_ldg_kernel<256, 1, false>;
+    return threads == 512 ? (const void*)row_reduce_ldg_kernel<512, 4, true>
+                          : (const void*)row_reduce_ldg_kernel<256, 8, true>;
+}
+
+const void* workload_func(int workload, int dtype, const credit_plan_info& p) {
+    const bool f32 = dtype == CREDIT_F32;
+    const bool al = p.aligned != 0;
+    switch (workload) {
+        case CREDIT_WL_RMSNORM_FORWARD:
+            return f32 ? rmsnorm_func<float>(p.threads, al) : rmsnorm_func<__nv_bfloat16>(p.threads, al);
+        case CREDIT_WL_ROW_REDUCE:
+            return row_reduce_func(p.load_path, p.threads, al);
+        case CREDIT_WL_LAYERNORM_FORWARD:
+            return f32 ? layernorm_fwd_func<float>(p.threads, al)
+                       : layernorm_fwd_func<__nv_bfloat16>(p.threads, al);
+        case CREDIT_WL_LAYERNORM_BACKWARD:
+            return f32 ? layernorm_bwd_dx_func<float>(p.threads, al, false)
+                       : layernorm_bwd_dx_func<__nv_bfloat16>(p.threads, al, false);
+        case CREDIT_WL_LAYERNORM_BACKWARD_STATS:
+            if (p.vectors_per_thread > 0)
+                return f32 ? layernorm_bwd_grads_func<float>(p.threads, p.vectors_per_thread)
+                           : layernorm_bwd_grads_func<__nv_bfloat16>(p.threads, p.vectors_per_thread);
+            return f32 ? layernorm_bwd_dx_func<float>(p.threads, al, true)
+                       : layernorm_bwd_dx_func<__nv_bfloat16>(p.threads, al, true);
+        default:
+            return nullptr;
+    }
+}
+
+// ---------------------------------------------------------------------------
+// planning
+// ---------------------------------------------------------------------------
+constexpr int kColsumRowsPerBlock = 128;   // fallback column-sum kernel: rows per partial ...
+constexpr int kColsumMaxBlocks = 1024;     // ... unless that would make more partials than this
+constexpr int kAutoStageBytes = 32 * 1024; // automatic cluster size aims at this much per stage
+constexpr int kAutoRingBytes = 96 * 1024;  // and at this much ring per CTA
+
+int inputs_staged(int workload) {
+    return (workload == CREDIT_WL_LAYERNORM_BACKWARD || workload == CREDIT_WL_LAYERNORM_BACKWARD_STATS)
+               ? 2
+               : 1;
+}
+
+// Resolves everything that does not need the occupancy query. `want_grads`
+// only matters for CREDIT_WL_LAYERNORM_BACKWARD_STATS.
+int plan_static(int workload, const Shape& s, int dtype, const credit_launch_opts& o,
+                bool pointers_aligned, bool want_grads, const credit_device_info& dev,
+                credit_plan_info* p) {
+    std::memset(p, 0, sizeof(*p));
+    if (workload < CREDIT_WL_RMSNORM_FORWARD || workload > CREDIT_WL_LAYERNORM_BACKWARD_STATS)
+        return fail(CREDIT_ERR_INVALID_ARGUMENT, "unknown workload %d", workload);
+    if (workload == CREDIT_WL_ROW_REDUCE && dtype != CREDIT_F32)
+        return fail(CREDIT_ERR_INVALID_ARGUMENT, "row_reduce takes fp32 input");
+    if (o.variant == CREDIT_VARIANT_BLOCK_READ)
+        return fail(CREDIT_ERR_UNSUPPORTED, "the block_read variant is not built for this workload");
+    if (!dev.cluster_launch && o.cluster_size > 1)
+        return fail(CREDIT_ERR_UNSUPPORTED, "device cannot launch thread-block clusters");
+
+    const int max_smem = dev.max_dynamic_smem_per_block;
+    const int max_cluster = dev.cluster_launch ? kMaxClusterSize : 1;
+    p->aligned = (pointers_aligned && s.cols % s.vec_elems == 0) ? 1 : 0;
+    p->variant = o.variant;
+    p->kernel_launches = 1;
+
+    if (workload == CREDIT_WL_ROW_REDUCE) {
+        p->load_path = o.load_path != CREDIT_LOAD_AUTO ? o.load_path
+                                                       : (p->aligned ? CREDIT_LOAD_TMA : CREDIT_LOAD_LDG);
+        if (p->load_path == CREDIT_LOAD_TMA && !p->aligned)
+            return fail(CREDIT_ERR_UNSUPPORTED,
+                        "bulk-copy path needs 16-byte aligned rows (cols %% 4 == 0, aligned base)");
+        p->threads = o.threads ? o.threads : 256;
+        int cluster = o.cluster_size;
+        if (cluster == 0) {
+            // Enough CTAs to cover the device a few times, but slices of at least 64 KiB.
+            cluster = 1;
+            while (cluster < max_cluster && 1ll * s.rows * cluster < 8ll * dev.sm_count &&
+                   1ll * s.cols * 4 / (cluster * 2) >= 65536)
+                cluster *= 2;
+            if (o.variant == CREDIT_VARIANT_CLUSTER_SMEM && cluster < 2) cluster = 2;
+        }
+        p->cluster_size = cluster;
+        p->slice_elems = round_up((s.cols + cluster - 1) / cluster, 64);
+        if (p->load_path == CREDIT_LOAD_TMA) {
+            int chunk_bytes = o.chunk_bytes ? o.chunk_bytes : 16384;
+            chunk_bytes = std::min(chunk_bytes, round_up(p->slice_elems * 4, 1024));
+            p->chunk_elems = chunk_bytes / 4;
+            p->stages = o.stages ? o.stages : 4;
+            p->smem_bytes = kControlBytes + p->stages * chunk_bytes;
+            if (p->smem_bytes > max_smem)
+                return fail(CREDIT_ERR_UNSUPPORTED, "ring of %d x %d B exceeds %d B of shared memory",
+                            p->stages, chunk_bytes, max_smem);
+            p->schedule = o.schedule ? o.schedule : CREDIT_SCHEDULE_PERSISTENT;
+        } else {
+            p->stages = 0;
+            p->chunk_elems = 0;
+            p->smem_bytes = 0;
+            p->schedule = o.schedule ? o.schedule : CREDIT_SCHEDULE_ROW_PER_CLUSTER;
+        }
+        return CREDIT_OK;
+    }
+
+    // staged kernels
+    const int nin = inputs_staged(workload);
+    const bool grads = workload == CREDIT_WL_LAYERNORM_BACKWARD_STATS && want_grads;
+    p->load_path = p->aligned ? CREDIT_LOAD_TMA : CREDIT_LOAD_LDG;
+    if (o.load_path == CREDIT_LOAD_TMA && !p->aligned)
+        return fail(CREDIT_ERR_UNSUPPORTED,
+                    "bulk-copy path needs 16-byte aligned rows and base pointers");
+
+    auto stage_bytes_for = [&](int cluster) {
+        return nin * round_up((s.cols + cluster - 1) / cluster, 64) * s.elem_bytes;
+    };
+    int cluster = o.cluster_size;
+    if (cluster == 0) {
+        cluster = o.variant == CREDIT_VARIANT_CLUSTER_SMEM ? 2 : 1;
+        while (cluster < max_cluster && stage_bytes_for(cluster) > kAutoStageBytes) cluster *= 2;
+    }
+    if (cluster > max_cluster)
+        return fail(CREDIT_ERR_UNSUPPORTED, "cluster size %d not available on this device", cluster);
+    p->cluster_size = cluster;
+    p->slice_elems = round_up((s.cols + cluster - 1) / cluster, 64);
+    const int stage_bytes = stage_bytes_for(cluster);
+    if (kControlBytes + stage_bytes > max_smem)
+        return fail(CREDIT_ERR_UNSUPPORTED,
+                    "a slice of %d B per CTA (cluster size %d) exceeds %d B of shared memory",
+                    stage_bytes, cluster, max_smem);
+
+    p->threads = o.threads ? o.threads : 256;
+    p->vectors_per_thread = 0;
+    if (grads && p->aligned) {
+        const int nvec = p->slice_elems / s.vec_elems;
+        int threads = o.threads;
+        if (threads == 0) threads = nvec > 512 ? 512 : 256;
+        int vpt = (nvec + threads - 1) / threads;
+        if (vpt == 3) vpt = 4;
+        if (vpt <= 4) {
+            p->threads = threads;
+            p->vectors_per_thread = vpt;
+        }
+        // otherwise: dx kernel + separate column-sum kernel
+    }
+
+    p->schedule = o.schedule;
+    if (p->schedule == CREDIT_SCHEDULE_AUTO)
+        p->schedule = (p->aligned || p->vectors_per_thread > 0) ? CREDIT_SCHEDULE_PERSISTENT
+                                                                : CREDIT_SCHEDULE_ROW_PER_CLUSTER;
+    if (p->vectors_per_thread > 0 && p->schedule != CREDIT_SCHEDULE_PERSISTENT)
+        return fail(CREDIT_ERR_INVALID_ARGUMENT,
+                    "column sums are accumulated by persistent clusters; schedule must be persistent");
+
+    int stages = o.stages;
+    if (!p->aligned || p->schedule == CREDIT_SCHEDULE_ROW_PER_CLUSTER) {
+        stages = 1;
+    } else if (stages == 0) {
+        stages = std::max(1, std::min(4, kAutoRingBytes / stage_bytes));
+        while (stages > 1 && kControlBytes + stages * stage_bytes > max_smem) --stages;
+    }
+    p->stages = stages;
+    p->smem_bytes = kControlBytes + stages * stage_bytes;
+    if (p->smem_bytes > max_smem)
+        return fail(CREDIT_ERR_UNSUPPORTED, "%d stages of %d B exceed %d B of shared memory", stages,
+                    stage_bytes, max_smem);
+    return CREDIT_OK;
+}
+
+// Grid size; needs the device for the occupancy query when persistent.
+int plan_grid(int device, const void* func, const Shape& s, credit_plan_info* p) {
+    int clusters = s.rows;
+    if (p->schedule == CREDIT_SCHEDULE_PERSISTENT && s.rows > 0) {
+        int resident = 0;
+        int rc = max_active_clusters(device, func, p->cluster_size, p->smem_bytes, p->threads, &resident);
+        if (rc != CREDIT_OK) return rc;
+        clusters = std::min(s.rows, resident);
+    }
+    if (1ll * clusters * p->cluster_size > 0x7fffffffll)
+        return fail(CREDIT_ERR_UNSUPPORTED, "%d rows x cluster size %d exceeds the grid limit", clusters,
+                    p->cluster_size);
+    p->num_clusters = clusters;
+    p->grid_ctas = clusters * p->cluster_size;
+    return CREDIT_OK;
+}
+
+int colsum_blocks(int rows) {
+    return std::max(1, std::min((rows + kColsumRowsPerBlock - 1) / kColsumRowsPerBlock, kColsumMaxBlocks));
+}
+
+size_t grads_workspace_bytes(const Shape& s, const credit_plan_info& p) {
+    const size_t partials = p.vectors_per_thread > 0 ? static_cast<size_t>(p.num_clusters)
+                                                     : static_cast<size_t>(colsum_blocks(s.rows));
+    return partials * 2 * static_cast<size_t>(s.cols) * sizeof(float);
+}
+
+struct Resolved {
+    DeviceState* dev = nullptr;
+    int device = 0;
+    Shape shape{};
+    credit_plan_info plan{};
+    const void* func = nullptr;
+};
+
+int resolve(int workload, int64_t rows, int64_t cols, int dtype, const credit_launch_opts* opts,
+            bool pointers_aligned, bool want_grads, Resolved* r) {
+    int rc = check_shape(rows, cols, dtype, &r->shape);
+    if (rc != CREDIT_OK) return rc;
+    credit_launch_opts o;
+    rc = check_opts(opts, &o);
+    if (rc != CREDIT_OK) return rc;
+    CREDIT_CUDA_TRY(cudaGetDevice(&r->device));
+    rc = load_device(r->device, &r->dev);
+    if (rc != CREDIT_OK) return rc;
+    rc = plan_static(workload, r->shape, dtype, o, pointers_aligned, want_grads, r->dev->info, &r->plan);
+    if (rc != CREDIT_OK) return rc;
+    r->func = workload_func(workload, dtype, r->plan);
+    if (r->func == nullptr) return fail(CREDIT_ERR_INVALID_ARGUMENT, "no kernel for workload %d", workload);
+    rc = prepare_function(r->device, r->func, r->dev->info.max_dynamic_smem_per_block);
+    if (rc != CREDIT_OK) return rc;
+    rc = plan_grid(r->device, r->func, r->shape, &r->plan);
+    if (rc != CREDIT_OK) return rc;
+    if (workload == CREDIT_WL_LAYERNORM_BACKWARD_STATS && want_grads) {
+        r->plan.workspace_bytes = grads_workspace_bytes(r->shape, r->plan);
+        r->plan.kernel_launches = r->plan.vectors_per_thread > 0 ? 2 : 3;
+    }
+    return CREDIT_OK;
+}
+
+Launch make_launch(const Resolved& r, void* stream) {
+    Launch l;
+    l.func = r.func;
+    l.grid = r.plan.grid_ctas;
+    l.threads = r.plan.threads;
+    l.cluster = r.plan.cluster_size;
+    l.smem = r.plan.smem_bytes;
+    l.stream = static_cast<cudaStream_t>(stream);
+    return l;
+}
+
+StagedArgs staged_args(const Resolved& r) {
+    StagedArgs a;
+    a.rows = r.shape.rows;
+    a.cols = r.shape.cols;
+    a.slice_elems = r.plan.slice_elems;
+    a.num_clusters = r.plan.num_clusters;
+    a.stages = r.plan.stages;
+    a.status = r.dev->status_ptr;
+    return a;
+}
+
+}  // namespace
+}  // namespace credit
+
+using namespace credit;
+
+extern "C" {
+
+const char* credit_last_error(void) { return t_last_error; }
+
+int credit_query_device(int device, credit_device_info* info) {
+    if (info == nullptr) return fail(CREDIT_ERR_INVALID_ARGUMENT, "info is NULL");
+    if (device < 0) CREDIT_CUDA_TRY(cudaGetDevice(&device));
+    DeviceState* st = nullptr;
+    int rc = load_device(device, &st);
+    if (rc != CREDIT_OK) return rc;
+    *info = st->info;
+    return CREDIT_OK;
+}
+
+int credit_device_status(int* status_out, int reset) {
+    DeviceState* st = nullptr;
+    int rc = current_device_state(&st);
+    if (rc != CREDIT_OK) return rc;
+    CREDIT_CUDA_TRY(cudaDeviceSynchronize());
+    int word = 0;
+    CREDIT_CUDA_TRY(cudaMemcpy(&word, st->status_ptr, sizeof(int), cudaMemcpyDeviceToHost));
+    if (reset && word != 0) CREDIT_CUDA_TRY(cudaMemset(st->status_ptr, 0, sizeof(int)));
+    if (status_out != nullptr) *status_out = word;
+    if (word != 0)
+        return fail(CREDIT_ERR_DEVICE_STATUS, "device status word = %d (1: wait timed out, 2: bad geometry)",
+                    word);
+    return CREDIT_OK;
+}
+
+int credit_plan(int workload, int64_t rows, int64_t cols, int dtype, const credit_launch_opts* opts,
+                credit_plan_info* plan) {
+    if (plan == nullptr) return fail(CREDIT_ERR_INVALID_ARGUMENT, "plan is NULL");
+    Resolved r;
+    int rc = resolve(workload, rows, cols, dtype, opts, true, true, &r);
+    if (rc != CREDIT_OK) return rc;
+    *plan = r.plan;
+    return CREDIT_OK;
+}
+
+int credit_rmsnorm_forward(const void* x, const float* gamma, void* y, int64_t rows, int64_t cols,
+                           float eps, int dtype, const credit_launch_opts* opts, void* stream) {
+    if (x == nullptr || gamma == nullptr || y == nullptr)
+        return fail(CREDIT_ERR_INVALID_ARGUMENT, "x, gamma and y must not be NULL");
+    Resolved r;
+    int rc = resolve(CREDIT_WL_RMSNORM_FORWARD, rows, cols, dtype, opts,
+                     aligned16(x) && aligned16(gamma) && aligned16(y), false, &r);
+    if (rc != CREDIT_OK) return rc;
+    if (r.shape.rows == 0) return CREDIT_OK;
+    StagedArgs a = staged_args(r);
+    void* args[] = {&x, &gamma, &y, &eps, &a};
+    return launch_cluster_kernel(make_launch(r, stream), args);
+}
+
+int credit_row_reduce(const float* x, float* out_sum, float* out_max, int64_t* out_argmax,
+                      int64_t rows, int64_t cols, const credit_launch_opts* opts, void* stream) {
+    if (x == nullptr || out_sum == nullptr || out_max == nullptr || out_argmax == nullptr)
+        return fail(CREDIT_ERR_INVALID_ARGUMENT, "x and the three outputs must not be NULL");
+    Resolved r;
+    int rc = resolve(CREDIT_WL_ROW_REDUCE, rows, cols, CREDIT_F32, opts, aligned16(x), false, &r);
+    if (rc != CREDIT_OK) return rc;
+    if (r.shape.rows == 0) return CREDIT_OK;
+    ReduceArgs a;
+    a.rows = r.shape.rows;
+    a.cols = r.shape.cols;
+    a.slice_elems = r.plan.slice_elems;
+    a.num_clusters = r.plan.num_clusters;
+    a.stages = r.plan.stages;
+    a.chunk_elems = r.plan.chunk_elems;
+    a.status = r.dev->status_ptr;
+    long long* argmax = reinterpret_cast<long long*>(out_argmax);
+    void* args[] = {&x, &out_sum, &out_max, &argmax, &a};
+    return launch_cluster_kernel(make_launch(r, stream), args);
+}
+
+int credit_layernorm_forward(const void* x, const float* gamma, const float* beta, void* y,
+                             float* mean, float* rstd, int64_t rows, int64_t cols, float eps,
+                             int dtype, const credit_launch_opts* opts, void* stream) {
+    if (x == nullptr || gamma == nullptr || beta == nullptr || y == nullptr || mean == nullptr ||
+        rstd == nullptr)
+        return fail(CREDIT_ERR_INVALID_ARGUMENT, "x, gamma, beta, y, mean and rstd must not be NULL");
+    Resolved r;
+    int rc = resolve(CREDIT_WL_LAYERNORM_FORWARD, rows, cols, dtype, opts,
+                     aligned16(x) && aligned16(gamma) && aligned16(beta) && aligned16(y), false, &r);
+    if (rc != CREDIT_OK) return rc;
+    if (r.shape.rows == 0) return CREDIT_OK;
+    StagedArgs a = staged_args(r);
+    void* args[] = {&x, &gamma, &beta, &y, &mean, &rstd, &eps, &a};
+    return launch_cluster_kernel(make_launch(r, stream), args);
+}
+
+int credit_layernorm_backward(const void* x, const void* dy, const float* gamma, void* dx,
+                              int64_t rows, int64_t cols, float eps, int dtype,
+                              const credit_launch_opts* opts, void* stream) {
+    if (x == nullptr || dy == nullptr || gamma == nullptr || dx == nullptr)
+        return fail(CREDIT_ERR_INVALID_ARGUMENT, "x, dy, gamma and dx must not be NULL");
+    Resolved r;
+    int rc = resolve(CREDIT_WL_LAYERNORM_BACKWARD, rows, cols, dtype, opts,
+                     aligned16(x) && aligned16(dy) && aligned16(gamma) && aligned16(dx), false, &r);
+    if (rc != CREDIT_OK) return rc;
+    if (r.shape.rows == 0) return CREDIT_OK;
+    StagedArgs a = staged_args(r);
+    const float* no_stats = nullptr;
+    float* no_partials = nullptr;
+    void* args[] = {&x, &dy, &gamma, &no_stats, &no_stats, &dx, &no_partials, &eps, &a};
+    return launch_cluster_kernel(make_launch(r, stream), args);
+}
+
+size_t credit_layernorm_backward_stats_workspace_bytes(int64_t rows, int64_t cols, int dtype,
+                                                       const credit_launch_opts* opts) {
+    Resolved r;
+    int rc = resolve(CREDIT_WL_LAYERNORM_BACKWARD_STATS, rows, cols, dtype, opts, true, true, &r);
+    if (rc != CREDIT_OK) return 0;
+    // Unaligned base pointers fall back to the column-sum kernel, whose partial
+    // count differs: report the larger of the two so either path fits.
+    Shape s = r.shape;
+    credit_plan_info fallback = r.plan;
+    fallback.vectors_per_thread = 0;
+    return std::max(r.plan.workspace_bytes, grads_workspace_bytes(s, fallback));
+}
+
+int credit_layernorm_backward_stats(const void* x, const void* dy, const float* gamma,
+                                    const float* mean, const float* rstd, void* dx, float* dgamma,
+                                    float* dbeta, int64_t rows, int64_t cols, int dtype,
+                                    const credit_launch_opts* opts, void* workspace,
+                                    size_t workspace_bytes, void* stream) {
+    if (x == nullptr || dy == nullptr || gamma == nullptr || mean == nullptr || rstd == nullptr ||
+        dx == nullptr)
+        return fail(CREDIT_ERR_INVALID_ARGUMENT, "x, dy, gamma, mean, rstd and dx must not be NULL");
+    if ((dgamma == nullptr) != (dbeta == nullptr))
+        return fail(CREDIT_ERR_INVALID_ARGUMENT, "dgamma and dbeta must both be given or both be NULL");
+    const bool want_grads = dgamma != nullptr;
+    Resolved r;
+    int rc = resolve(CREDIT_WL_LAYERNORM_BACKWARD_STATS, rows, cols, dtype, opts,
+                     aligned16(x) && aligned16(dy) && aligned16(gamma) && aligned16(dx) &&
+                         (!want_grads || aligned16(workspace)),
+                     want_grads, &r);
+    if (rc != CREDIT_OK) return rc;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (want_grads) {
+        if (workspace == nullptr || workspace_bytes < r.plan.workspace_bytes)
+            return fail(CREDIT_ERR_WORKSPACE, "workspace of %zu B given, %zu B needed", workspace_bytes,
+                        r.plan.workspace_bytes);
+    }
+    if (r.shape.rows == 0) {
+        if (want_grads) {
+            CREDIT_CUDA_TRY(cudaMemsetAsync(dgamma, 0, sizeof(float) * r.shape.cols, s));
+            CREDIT_CUDA_TRY(cudaMemsetAsync(dbeta, 0, sizeof(float) * r.shape.cols, s));
+        }
+        return CREDIT_OK;
+    }
+    StagedArgs a = staged_args(r);
+    float* partials = static_cast<float*>(workspace);
+    float eps = 0.0f;
+    void* args[] = {&x, &dy, &gamma, &mean, &rstd, &dx, &partials, &eps, &a};
+    rc = launch_cluster_kernel(make_launch(r, stream), args);
+    if (rc != CREDIT_OK) return rc;
+    if (!want_grads) return CREDIT_OK;
+
+    int num_partials = r.plan.num_clusters;
+    const int col_blocks = (r.shape.cols + 255) / 256;
+    if (r.plan.vectors_per_thread == 0) {
+        num_partials = colsum_blocks(r.shape.rows);
+        const int rows_per_block = (r.shape.rows + num_partials - 1) / num_partials;
+        dim3 grid(static_cast<unsigned>(col_blocks), static_cast<unsigned>(num_partials));
+        if (dtype == CREDIT_F32)
+            layernorm_bwd_colsum_kernel<float><<<grid, 256, 0, s>>>(
+                static_cast<const float*>(x), static_cast<const float*>(dy), mean, rstd, partials,
+                r.shape.rows, r.shape.cols, rows_per_block);
+        else
+            layernorm_bwd_colsum_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(
+                static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(dy), mean,
+                rstd, partials, r.shape.rows, r.shape.cols, rows_per_block);
+        CREDIT_CUDA_TRY(cudaGetLastError());
+    }
+    layernorm_bwd_finish_kernel<<<col_blocks, 256, 0, s>>>(partials, dgamma, dbeta, r.shape.cols,
+                                                           num_partials);
+    CREDIT_CUDA_TRY(cudaGetLastError());
+    return CREDIT_OK;
+}
+
+}  // extern "C"

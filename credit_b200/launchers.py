@@ -1,0 +1,200 @@
+"""In-process launcher table of the native backend.
+
+Same convention as the reference's Triton table
+(`dsmem_eval/triton_kernels.py:300-414`): `launcher(inputs, outputs, ...)`
+takes caller-owned device tensors, enqueues on the current CUDA stream and
+returns nothing; `allocate_outputs(name, inputs)` pre-allocates the outputs. The
+Triton knobs (`block_size`, `num_warps`) have no meaning for these kernels; the
+knobs here are the cluster size and the other launch options of the C ABI.
+
+torch is used for device memory and streams only; every kernel is in
+`libcredit_b200.so`.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _native as N
+
+_DTYPES = {torch.float32: N.F32, torch.bfloat16: N.BF16}
+
+
+def _stream_ptr() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _check_matrix(name: str, t: torch.Tensor, dtype=None, shape=None) -> None:
+    if not isinstance(t, torch.Tensor) or not t.is_cuda:
+        raise ValueError(f"{name} must be a CUDA tensor")
+    if not t.is_contiguous():
+        raise ValueError(f"{name} must be contiguous")
+    if dtype is not None and t.dtype != dtype:
+        raise ValueError(f"{name} must have dtype {dtype}, got {t.dtype}")
+    if shape is not None and tuple(t.shape) != tuple(shape):
+        raise ValueError(f"{name} must have shape {tuple(shape)}, got {tuple(t.shape)}")
+
+
+def _row_dtype(x: torch.Tensor) -> int:
+    if x.dtype not in _DTYPES:
+        raise ValueError(f"unsupported dtype {x.dtype}: float32 and bfloat16 only")
+    return _DTYPES[x.dtype]
+
+
+def _opts(cluster_size: int, opts) -> "N.LaunchOpts | None":
+    o = N.make_opts(opts)
+    if cluster_size:
+        if o is None:
+            o = N.LaunchOpts()
+        else:
+            o = N.LaunchOpts(**{name: getattr(o, name) for name, _ in N.LaunchOpts._fields_})
+        o.cluster_size = int(cluster_size)
+    return o
+
+
+def _ref(o):
+    import ctypes
+    return None if o is None else ctypes.byref(o)
+
+
+def launch_rmsnorm_forward(inputs, outputs, cluster_size: int = 0, opts=None, eps: float = 1.0e-6) -> None:
+    x, gamma = inputs
+    (y,) = outputs
+    _check_matrix("x", x)
+    rows, cols = x.shape
+    _check_matrix("gamma", gamma, torch.float32, (cols,))
+    _check_matrix("y", y, x.dtype, x.shape)
+    o = _opts(cluster_size, opts)
+    with torch.cuda.device(x.device):
+        N.check(N.load().credit_rmsnorm_forward(
+            x.data_ptr(), gamma.data_ptr(), y.data_ptr(), rows, cols, eps, _row_dtype(x), _ref(o),
+            _stream_ptr()))
+
+
+def launch_row_reduce(inputs, outputs, cluster_size: int = 0, opts=None) -> None:
+    (x,) = inputs
+    row_sum, row_max, row_argmax = outputs
+    _check_matrix("x", x, torch.float32)
+    rows, cols = x.shape
+    _check_matrix("sum", row_sum, torch.float32, (rows,))
+    _check_matrix("max", row_max, torch.float32, (rows,))
+    _check_matrix("argmax", row_argmax, torch.int64, (rows,))
+    o = _opts(cluster_size, opts)
+    with torch.cuda.device(x.device):
+        N.check(N.load().credit_row_reduce(
+            x.data_ptr(), row_sum.data_ptr(), row_max.data_ptr(), row_argmax.data_ptr(), rows, cols,
+            _ref(o), _stream_ptr()))
+
+
+def launch_layernorm_forward(inputs, outputs, cluster_size: int = 0, opts=None, eps: float = 1.0e-5) -> None:
+    x, gamma, beta = inputs
+    y, mean, rstd = outputs
+    _check_matrix("x", x)
+    rows, cols = x.shape
+    _check_matrix("gamma", gamma, torch.float32, (cols,))
+    _check_matrix("beta", beta, torch.float32, (cols,))
+    _check_matrix("y", y, x.dtype, x.shape)
+    _check_matrix("mean", mean, torch.float32, (rows,))
+    _check_matrix("rstd", rstd, torch.float32, (rows,))
+    o = _opts(cluster_size, opts)
+    with torch.cuda.device(x.device):
+        N.check(N.load().credit_layernorm_forward(
+            x.data_ptr(), gamma.data_ptr(), beta.data_ptr(), y.data_ptr(), mean.data_ptr(),
+            rstd.data_ptr(), rows, cols, eps, _row_dtype(x), _ref(o), _stream_ptr()))
+
+
+def launch_layernorm_backward(inputs, outputs, cluster_size: int = 0, opts=None, eps: float = 1.0e-5) -> None:
+    """dx with statistics recomputed from x: the reference workload
+    (`launch_layernorm_backward`, triton_kernels.py:300-312)."""
+    x, dy, gamma = inputs
+    (dx,) = outputs
+    _check_matrix("x", x)
+    rows, cols = x.shape
+    _check_matrix("dy", dy, x.dtype, x.shape)
+    _check_matrix("gamma", gamma, torch.float32, (cols,))
+    _check_matrix("dx", dx, x.dtype, x.shape)
+    o = _opts(cluster_size, opts)
+    with torch.cuda.device(x.device):
+        N.check(N.load().credit_layernorm_backward(
+            x.data_ptr(), dy.data_ptr(), gamma.data_ptr(), dx.data_ptr(), rows, cols, eps,
+            _row_dtype(x), _ref(o), _stream_ptr()))
+
+
+def layernorm_backward_stats_workspace_bytes(rows: int, cols: int, dtype: torch.dtype,
+                                             cluster_size: int = 0, opts=None) -> int:
+    o = _opts(cluster_size, opts)
+    # credit_plan raises with the precise status if the shape or options are unusable
+    N.plan(N.WL_LAYERNORM_BACKWARD_STATS, rows, cols, _DTYPES[dtype], o)
+    return int(N.load().credit_layernorm_backward_stats_workspace_bytes(
+        rows, cols, _DTYPES[dtype], _ref(o)))
+
+
+def launch_layernorm_backward_stats(inputs, outputs, cluster_size: int = 0, opts=None,
+                                    workspace: torch.Tensor | None = None) -> None:
+    """dx, dgamma, dbeta from x, dy, gamma and the saved fp32 mean/rstd. `workspace` is a
+    uint8 CUDA tensor of at least `layernorm_backward_stats_workspace_bytes(...)` bytes; when
+    omitted one is allocated through torch's caching allocator for this call."""
+    x, dy, gamma, mean, rstd = inputs
+    if len(outputs) == 1:
+        (dx,), dgamma, dbeta = outputs, None, None
+    else:
+        dx, dgamma, dbeta = outputs
+    _check_matrix("x", x)
+    rows, cols = x.shape
+    _check_matrix("dy", dy, x.dtype, x.shape)
+    _check_matrix("gamma", gamma, torch.float32, (cols,))
+    _check_matrix("mean", mean, torch.float32, (rows,))
+    _check_matrix("rstd", rstd, torch.float32, (rows,))
+    _check_matrix("dx", dx, x.dtype, x.shape)
+    o = _opts(cluster_size, opts)
+    ws_ptr, ws_bytes = 0, 0
+    if dgamma is not None:
+        _check_matrix("dgamma", dgamma, torch.float32, (cols,))
+        _check_matrix("dbeta", dbeta, torch.float32, (cols,))
+        if workspace is None:
+            need = layernorm_backward_stats_workspace_bytes(rows, cols, x.dtype, 0, o)
+            workspace = torch.empty(max(need, 16), dtype=torch.uint8, device=x.device)
+        _check_matrix("workspace", workspace, torch.uint8)
+        ws_ptr, ws_bytes = workspace.data_ptr(), workspace.numel()
+    with torch.cuda.device(x.device):
+        N.check(N.load().credit_layernorm_backward_stats(
+            x.data_ptr(), dy.data_ptr(), gamma.data_ptr(), mean.data_ptr(), rstd.data_ptr(),
+            dx.data_ptr(), 0 if dgamma is None else dgamma.data_ptr(),
+            0 if dbeta is None else dbeta.data_ptr(), rows, cols, _row_dtype(x), _ref(o), ws_ptr,
+            ws_bytes, _stream_ptr()))
+
+
+NATIVE_LAUNCHERS = {
+    "rmsnorm_forward": launch_rmsnorm_forward,
+    "row_reduce": launch_row_reduce,
+    "layernorm_forward": launch_layernorm_forward,
+    "layernorm_backward": launch_layernorm_backward,
+    "layernorm_backward_stats": launch_layernorm_backward_stats,
+}
+
+
+def allocate_outputs(name: str, inputs: tuple[torch.Tensor, ...]) -> tuple[torch.Tensor, ...]:
+    """Output tensors for one call (reference: allocate_outputs, triton_kernels.py:403-414)."""
+    x = inputs[0]
+    rows, cols = x.shape
+    dev = x.device
+    if name == "row_reduce":
+        return (
+            torch.empty(rows, device=dev, dtype=torch.float32),
+            torch.empty(rows, device=dev, dtype=torch.float32),
+            torch.empty(rows, device=dev, dtype=torch.int64),
+        )
+    if name == "layernorm_forward":
+        return (
+            torch.empty_like(x),
+            torch.empty(rows, device=dev, dtype=torch.float32),
+            torch.empty(rows, device=dev, dtype=torch.float32),
+        )
+    if name == "layernorm_backward_stats":
+        return (
+            torch.empty_like(x),
+            torch.empty(cols, device=dev, dtype=torch.float32),
+            torch.empty(cols, device=dev, dtype=torch.float32),
+        )
+    if name in ("rmsnorm_forward", "layernorm_backward"):
+        return (torch.empty_like(x),)
+    raise KeyError(f"unknown workload {name!r}")

@@ -1,0 +1,196 @@
+/*
+ * credit_b200 -- C ABI of the sm_100a wide-row cluster/DSMEM kernels.
+ *
+ * The reference project (CREDIT) has no library boundary: its evaluation
+ * pipeline spawns one executable per workload (dsmem_eval/runner.py:280-347) and
+ * calls Triton through an in-process launcher table
+ * (dsmem_eval/triton_kernels.py:300-400). This header is the boundary a
+ * maintainer binds with ctypes to add a third, native backend: every entry point
+ * below names the reference interface it stands in for.
+ *
+ * Conventions
+ *  - Every function returns CREDIT_OK (0) or a negative credit_status; nothing
+ *    exits the process or throws (the reference's CUDA_CHECK calls std::exit,
+ *    src/workloads/layernorm_backward.cu:20-28). credit_last_error() gives the
+ *    text for the calling thread's last failure.
+ *  - Matrix pointers are caller-owned DEVICE pointers to row-major, densely
+ *    packed [rows, cols] arrays on the current device. gamma/beta/dgamma/dbeta
+ *    are always fp32 [cols]; per-row statistics are fp32 [rows].
+ *  - Launches are asynchronous on `stream` (a cudaStream_t passed as void*; NULL
+ *    is the default stream). No call allocates device memory or synchronises,
+ *    except where stated.
+ *  - Rows whose byte length is a multiple of 16 with 16-byte aligned base
+ *    pointers take the bulk-copy/128-bit path; anything else is served by scalar
+ *    kernels with the same results.
+ *  - `opts` may be NULL (all fields 0 = automatic).
+ */
+#ifndef CREDIT_B200_H
+#define CREDIT_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum credit_status {
+    CREDIT_OK = 0,
+    CREDIT_ERR_INVALID_ARGUMENT = -1, /* bad pointer, size, dtype or option */
+    CREDIT_ERR_UNSUPPORTED = -2,      /* shape does not fit the requested variant (the
+                                         reference prints "n/a" for such a variant,
+                                         layernorm_backward.cu:508-511, 563-565) */
+    CREDIT_ERR_CUDA = -3,             /* a CUDA runtime call failed */
+    CREDIT_ERR_WORKSPACE = -4,        /* workspace missing or too small */
+    CREDIT_ERR_DEVICE_STATUS = -5     /* a kernel reported a timeout or bad geometry */
+} credit_status;
+
+typedef enum credit_dtype { CREDIT_F32 = 0, CREDIT_BF16 = 1 } credit_dtype;
+
+/* Variant names follow the reference's RESULT lines
+ * (layernorm_backward.cu:489, 517, 555). */
+typedef enum credit_variant {
+    CREDIT_VARIANT_AUTO = 0,
+    CREDIT_VARIANT_BLOCK_READ = 1,   /* one CTA per row, no staging, re-reads global memory */
+    CREDIT_VARIANT_BLOCK_SMEM = 2,   /* one CTA per row, row staged in shared memory */
+    CREDIT_VARIANT_CLUSTER_SMEM = 3  /* row split over a cluster, partials through DSMEM */
+} credit_variant;
+
+typedef enum credit_load_path {
+    CREDIT_LOAD_AUTO = 0,
+    CREDIT_LOAD_TMA = 1,  /* bulk-async copies into a shared-memory ring */
+    CREDIT_LOAD_LDG = 2   /* 128-bit read-only loads into registers (streaming kernels) */
+} credit_load_path;
+
+typedef enum credit_schedule {
+    CREDIT_SCHEDULE_AUTO = 0,
+    CREDIT_SCHEDULE_ROW_PER_CLUSTER = 1, /* grid = rows clusters */
+    CREDIT_SCHEDULE_PERSISTENT = 2       /* grid = resident clusters, each walks many rows */
+} credit_schedule;
+
+typedef struct credit_launch_opts {
+    int cluster_size; /* CTAs per row: 1,2,4,8,16; 0 = automatic */
+    int variant;      /* credit_variant */
+    int stages;       /* shared-memory ring depth, 1..8; 0 = automatic */
+    int threads;      /* threads per CTA: 256 or 512; 0 = automatic */
+    int schedule;     /* credit_schedule */
+    int load_path;    /* credit_load_path (streaming kernels) */
+    int chunk_bytes;  /* ring chunk of the streaming kernels, multiple of 1024; 0 = automatic */
+    int reserved;
+} credit_launch_opts;
+
+/* The fields of DeviceInfo in the reference binaries
+ * (layernorm_backward.cu:50-58, query_device_info :440-468) plus what the cost
+ * model needs. */
+typedef struct credit_device_info {
+    char name[256];
+    int sm_major;
+    int sm_minor;
+    int sm_count;
+    int cluster_launch;            /* cudaDevAttrClusterLaunch */
+    int max_cluster_size;          /* largest cluster this library will launch (16 on sm_100) */
+    int max_dynamic_smem_per_block; /* sharedMemPerBlockOptin */
+    int smem_per_sm;
+    int l2_bytes;
+    int clock_khz;                 /* maximum SM clock */
+    int mem_clock_khz;
+    int mem_bus_bits;
+} credit_device_info;
+
+typedef enum credit_workload {
+    CREDIT_WL_RMSNORM_FORWARD = 0,
+    CREDIT_WL_ROW_REDUCE = 1,
+    CREDIT_WL_LAYERNORM_FORWARD = 2,
+    CREDIT_WL_LAYERNORM_BACKWARD = 3,      /* statistics recomputed, dx only */
+    CREDIT_WL_LAYERNORM_BACKWARD_STATS = 4 /* statistics given, dx + dgamma + dbeta */
+} credit_workload;
+
+/* What a call would launch: the resolved form of credit_launch_opts. */
+typedef struct credit_plan_info {
+    int cluster_size;
+    int variant;
+    int stages;
+    int threads;
+    int schedule;
+    int load_path;
+    int aligned;            /* 1 = 16-byte path */
+    int slice_elems;        /* columns per CTA */
+    int chunk_elems;        /* streaming kernels: columns per ring chunk */
+    int vectors_per_thread; /* LayerNorm backward with column sums */
+    int num_clusters;       /* clusters in the grid */
+    int grid_ctas;
+    int smem_bytes;         /* dynamic shared memory per CTA */
+    int kernel_launches;    /* kernels one call enqueues */
+    size_t workspace_bytes;
+} credit_plan_info;
+
+/* Library and device ---------------------------------------------------- */
+
+/* Text of the calling thread's last failure ("" if none). */
+const char* credit_last_error(void);
+
+/* Replaces query_device_info (layernorm_backward.cu:440-468). device < 0 means
+ * the current device. */
+int credit_query_device(int device, credit_device_info* info);
+
+/* Reads (and optionally clears) the current device's status word: bit 0 = an
+ * mbarrier wait timed out, bit 1 = a kernel refused its launch geometry.
+ * Synchronises the device. Returns CREDIT_ERR_DEVICE_STATUS if any bit is set. */
+int credit_device_status(int* status_out, int reset);
+
+/* Resolves opts for a workload and shape without launching. Replaces the
+ * shape gating in benchmark_block_staged / benchmark_cluster
+ * (layernorm_backward.cu:499-593). */
+int credit_plan(int workload, int64_t rows, int64_t cols, int dtype,
+                const credit_launch_opts* opts, credit_plan_info* plan);
+
+/* Workloads -------------------------------------------------------------- */
+
+/* y = x * rsqrt(mean_row(x^2) + eps) * gamma. x, y: dtype [rows, cols].
+ * No reference kernel exists for this workload; it runs on the same cluster
+ * core as cluster_bwd_staged_kernel (layernorm_backward.cu:376-438) with one
+ * reduction stage of one partial. */
+int credit_rmsnorm_forward(const void* x, const float* gamma, void* y, int64_t rows, int64_t cols,
+                           float eps, int dtype, const credit_launch_opts* opts, void* stream);
+
+/* Per-row sum, maximum and index of the first maximum of fp32 x [rows, cols].
+ * The max-type one-stage reduction of cluster_quant_staged_kernel
+ * (rowwise_quant.cu:321-363) with the column index carried along.
+ * out_argmax is int64 [rows]. */
+int credit_row_reduce(const float* x, float* out_sum, float* out_max, int64_t* out_argmax,
+                      int64_t rows, int64_t cols, const credit_launch_opts* opts, void* stream);
+
+/* y = (x - mean) * rstd * gamma + beta, rstd = rsqrt(var + eps) (biased var).
+ * mean, rstd: fp32 [rows] outputs. No reference kernel; same cluster core. */
+int credit_layernorm_forward(const void* x, const float* gamma, const float* beta, void* y,
+                             float* mean, float* rstd, int64_t rows, int64_t cols, float eps,
+                             int dtype, const credit_launch_opts* opts, void* stream);
+
+/* dx of LayerNorm with the row statistics recomputed from x. Replaces
+ * block_bwd_read_kernel / block_bwd_staged_kernel / cluster_bwd_staged_kernel
+ * (layernorm_backward.cu:274-438) and launch_layernorm_backward
+ * (dsmem_eval/triton_kernels.py:300-312); formula of
+ * dsmem_eval/workloads.py:53-61. */
+int credit_layernorm_backward(const void* x, const void* dy, const float* gamma, void* dx,
+                              int64_t rows, int64_t cols, float eps, int dtype,
+                              const credit_launch_opts* opts, void* stream);
+
+/* LayerNorm backward with given statistics: dx plus the column sums
+ * dgamma = sum_rows dy * xhat and dbeta = sum_rows dy (fp32 [cols]); dgamma and
+ * dbeta may both be NULL to skip them. Needs a device workspace of at least
+ * credit_layernorm_backward_stats_workspace_bytes() (per-cluster partial column
+ * sums; contents are overwritten). Extends cluster_bwd_staged_kernel to the
+ * bf16 / precomputed-statistics / parameter-gradient form. */
+size_t credit_layernorm_backward_stats_workspace_bytes(int64_t rows, int64_t cols, int dtype,
+                                                       const credit_launch_opts* opts);
+int credit_layernorm_backward_stats(const void* x, const void* dy, const float* gamma,
+                                    const float* mean, const float* rstd, void* dx, float* dgamma,
+                                    float* dbeta, int64_t rows, int64_t cols, int dtype,
+                                    const credit_launch_opts* opts, void* workspace,
+                                    size_t workspace_bytes, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* CREDIT_B200_H */
