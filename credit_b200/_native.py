@@ -27,6 +27,7 @@ BF16 = 1
 VARIANT_AUTO, VARIANT_BLOCK_READ, VARIANT_BLOCK_SMEM, VARIANT_CLUSTER_SMEM = 0, 1, 2, 3
 LOAD_AUTO, LOAD_TMA, LOAD_LDG = 0, 1, 2
 SCHEDULE_AUTO, SCHEDULE_ROW_PER_CLUSTER, SCHEDULE_PERSISTENT = 0, 1, 2
+FLAG_NO_REGISTER_PATH = 1
 
 WL_RMSNORM_FORWARD = 0
 WL_ROW_REDUCE = 1
@@ -57,7 +58,7 @@ class LaunchOpts(Structure):
         ("schedule", c_int),
         ("load_path", c_int),
         ("chunk_bytes", c_int),
-        ("reserved", c_int),
+        ("flags", c_int),
     ]
 
 
@@ -125,6 +126,10 @@ PROTOTYPES: dict[str, tuple] = {
     "credit_layernorm_backward_stats": (
         c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                 c_int64, c_int64, c_int, _OPTS_P, c_void_p, c_size_t, c_void_p]),
+    "credit_row_reduce_host_scratch_bytes": (c_size_t, [c_int64, c_int64]),
+    "credit_row_reduce_host": (
+        c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, _OPTS_P, c_void_p,
+                c_size_t, c_void_p]),
 }
 
 _lib: ctypes.CDLL | None = None

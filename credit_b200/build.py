@@ -23,8 +23,17 @@ LIB_PATH = LIB_DIR / "libcredit_b200.so"
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 COMMON_FLAGS = ["-std=c++17", "-O3", "-lineinfo", *ARCH_FLAGS]
 
-# Sources of the shared library (every other file in csrc/ is a header).
-LIB_SOURCES = ["launch.cu"]
+# Translation units of the shared library (every other file in csrc/ is a header).
+LIB_SOURCES = [
+    "launch.cu",
+    "tables_rmsnorm.cu",
+    "tables_layernorm_fwd.cu",
+    "tables_layernorm_bwd.cu",
+    "tables_layernorm_bwd_f32.cu",
+    "tables_layernorm_bwd_bf16.cu",
+    "tables_row_reduce.cu",
+]
+OBJ_DIR = LIB_DIR / "obj"
 # name of the executable -> source
 CLI_SOURCES: dict[str, str] = {}
 
@@ -52,18 +61,28 @@ def _run(cmd: list[str], verbose: bool) -> str:
     return result.stdout + result.stderr
 
 
+def _compile_object(source: str, verbose: bool) -> tuple[Path, str]:
+    obj = OBJ_DIR / (Path(source).stem + ".o")
+    cmd = [nvcc_path(), *COMMON_FLAGS, "-Xcompiler", "-fPIC", "-Xptxas", "-v", "-c",
+           str(CSRC / source), "-o", str(obj)]
+    return obj, _run(cmd, verbose)
+
+
 def build_library(force: bool = False, verbose: bool = False, ptxas_log: Path | None = None) -> Path:
-    """Compiles libcredit_b200.so if it is missing or older than its sources."""
+    """Compiles libcredit_b200.so if it is missing or older than its sources. The
+    translation units are compiled in parallel and linked into one shared library."""
+    from concurrent.futures import ThreadPoolExecutor
+
     LIB_DIR.mkdir(parents=True, exist_ok=True)
     if not force and LIB_PATH.exists() and LIB_PATH.stat().st_mtime >= _newest_source_mtime():
         return LIB_PATH
-    cmd = [
-        nvcc_path(), *COMMON_FLAGS, "-Xcompiler", "-fPIC", "-shared", "-Xptxas", "-v",
-        "-o", str(LIB_PATH), *[str(CSRC / s) for s in LIB_SOURCES],
-    ]
-    log = _run(cmd, verbose)
+    OBJ_DIR.mkdir(parents=True, exist_ok=True)
+    with ThreadPoolExecutor(max_workers=min(len(LIB_SOURCES), os.cpu_count() or 1)) as pool:
+        results = list(pool.map(lambda src: _compile_object(src, verbose), LIB_SOURCES))
+    objects = [str(obj) for obj, _ in results]
+    _run([nvcc_path(), *ARCH_FLAGS, "-shared", "-o", str(LIB_PATH), *objects], verbose)
     if ptxas_log is not None:
-        ptxas_log.write_text(log)
+        ptxas_log.write_text("\n".join(log for _, log in results))
     return LIB_PATH
 
 

@@ -11,18 +11,9 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "launch_args.h"
+
 namespace credit {
-
-constexpr int kMaxClusterSize = 16;   // 8 portable, 16 with the non-portable opt-in
-constexpr int kMaxWarpsPerCta = 32;
-constexpr int kMaxStages = 8;
-// Bytes reserved at the start of dynamic shared memory for barriers and
-// reduction scratch; row data starts after it (keeps 1024-byte alignment).
-constexpr int kControlBytes = 4096;
-
-// Bits of the device status word (see credit_device_status in the C ABI).
-constexpr int kStatusWaitTimeout = 1;      // an mbarrier wait ran out of patience
-constexpr int kStatusBadGeometry = 2;      // a kernel saw a launch shape it cannot handle
 
 // ---------------------------------------------------------------------------
 // addressing

@@ -1,0 +1,26 @@
+// Kernel selection: each function returns the __global__ entry point for a
+// configuration (or nullptr if it was not instantiated). Every kernel family is
+// compiled in its own translation unit so the library builds in parallel.
+#pragma once
+
+#include <cuda_runtime.h>
+
+namespace credit {
+
+// vpt > 0 selects the register-resident kernel with that many 16-byte vectors per
+// thread; vpt == 0 the generic shared-memory kernel (aligned or scalar).
+const void* rmsnorm_kernel_for(int dtype, int threads, int vpt, bool aligned);
+const void* layernorm_fwd_kernel_for(int dtype, int threads, int vpt, bool aligned);
+const void* layernorm_bwd_kernel_for(int dtype, int threads, int vpt, bool aligned, bool has_stats,
+                                     bool grads);
+const void* row_reduce_kernel_for(int load_path, int threads, bool aligned);
+
+// Column sums of LayerNorm backward for shapes outside the register path, and
+// the finishing reduction over per-cluster (or per-row-block) partials.
+cudaError_t launch_layernorm_bwd_colsum(int dtype, const void* x, const void* dy, const float* mean,
+                                        const float* rstd, float* partials, int rows, int cols,
+                                        int num_blocks, cudaStream_t stream);
+cudaError_t launch_layernorm_bwd_finish(const float* partials, float* dgamma, float* dbeta, int cols,
+                                        int num_partials, cudaStream_t stream);
+
+}  // namespace credit

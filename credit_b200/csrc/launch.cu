@@ -17,8 +17,9 @@
 #include <tuple>
 
 #include "../../include/credit_b200.h"
-#include "norm_kernels.cuh"
-#include "reduce_kernels.cuh"
+#include "cluster_primitives.cuh"
+#include "kernel_tables.h"
+#include "launch_args.h"
 
 namespace credit {
 
@@ -241,6 +242,8 @@ int check_opts(const credit_launch_opts* o, credit_launch_opts* out) {
     if (z.chunk_bytes < 0 || z.chunk_bytes % 1024 != 0 || z.chunk_bytes > 65536)
         return fail(CREDIT_ERR_INVALID_ARGUMENT,
                     "chunk_bytes must be a multiple of 1024 up to 65536 (got %d)", z.chunk_bytes);
+    if (z.flags & ~CREDIT_FLAG_NO_REGISTER_PATH)
+        return fail(CREDIT_ERR_INVALID_ARGUMENT, "unknown flags 0x%x", z.flags);
     if (z.variant == CREDIT_VARIANT_BLOCK_SMEM || z.variant == CREDIT_VARIANT_BLOCK_READ) {
         if (z.cluster_size > 1)
             return fail(CREDIT_ERR_INVALID_ARGUMENT, "block variants run with cluster_size 1 (got %d)",
@@ -254,84 +257,22 @@ int check_opts(const credit_launch_opts* o, credit_launch_opts* out) {
 }
 
 // ---------------------------------------------------------------------------
-// kernel tables
+// kernel selection (the tables live in one translation unit per kernel family)
 // ---------------------------------------------------------------------------
-template <typename T>
-const void* rmsnorm_func(int threads, bool aligned) {
-    if (threads == 512)
-        return aligned ? (const void*)rmsnorm_fwd_kernel<T, 512, true>
-                       : (const void*)rmsnorm_fwd_kernel<T, 512, false>;
-    return aligned ? (const void*)rmsnorm_fwd_kernel<T, 256, true>
-                   : (const void*)rmsnorm_fwd_kernel<T, 256, false>;
-}
-
-template <typename T>
-const void* layernorm_fwd_func(int threads, bool aligned) {
-    if (threads == 512)
-        return aligned ? (const void*)layernorm_fwd_kernel<T, 512, true>
-                       : (const void*)layernorm_fwd_kernel<T, 512, false>;
-    return aligned ? (const void*)layernorm_fwd_kernel<T, 256, true>
-                   : (const void*)layernorm_fwd_kernel<T, 256, false>;
-}
-
-// dx only; statistics recomputed (has_stats=false) or given.
-template <typename T>
-const void* layernorm_bwd_dx_func(int threads, bool aligned, bool has_stats) {
-    if (has_stats) {
-        if (threads == 512)
-            return aligned ? (const void*)layernorm_bwd_kernel<T, 512, 1, true, true, false>
-                           : (const void*)layernorm_bwd_kernel<T, 512, 1, false, true, false>;
-        return aligned ? (const void*)layernorm_bwd_kernel<T, 256, 1, true, true, false>
-                       : (const void*)layernorm_bwd_kernel<T, 256, 1, false, true, false>;
-    }
-    if (threads == 512)
-        return aligned ? (const void*)layernorm_bwd_kernel<T, 512, 1, true, false, false>
-                       : (const void*)layernorm_bwd_kernel<T, 512, 1, false, false, false>;
-    return aligned ? (const void*)layernorm_bwd_kernel<T, 256, 1, true, false, false>
-                   : (const void*)layernorm_bwd_kernel<T, 256, 1, false, false, false>;
-}
-
-template <typename T>
-const void* layernorm_bwd_grads_func(int threads, int vpt) {
-    if (threads == 512) {
-        if (vpt == 1) return (const void*)layernorm_bwd_kernel<T, 512, 1, true, true, true>;
-        if (vpt == 2) return (const void*)layernorm_bwd_kernel<T, 512, 2, true, true, true>;
-        return (const void*)layernorm_bwd_kernel<T, 512, 4, true, true, true>;
-    }
-    if (vpt == 1) return (const void*)layernorm_bwd_kernel<T, 256, 1, true, true, true>;
-    if (vpt == 2) return (const void*)layernorm_bwd_kernel<T, 256, 2, true, true, true>;
-    return (const void*)layernorm_bwd_kernel<T, 256, 4, true, true, true>;
-}
-
-const void* row_reduce_func(int load_path, int threads, bool aligned) {
-    if (load_path == CREDIT_LOAD_TMA)
-        return threads == 512 ? (const void*)row_reduce_tma_kernel<512>
-                              : (const void*)row_reduce_tma_kernel<256>;
-    if (!aligned) return (const void*)row_reduce_ldg_kernel<256, 1, false>;
-    return threads == 512 ? (const void*)row_reduce_ldg_kernel<512, 4, true>
-                          : (const void*)row_reduce_ldg_kernel<256, 8, true>;
-}
-
-const void* workload_func(int workload, int dtype, const credit_plan_info& p) {
-    const bool f32 = dtype == CREDIT_F32;
+const void* workload_func(int workload, int dtype, const credit_plan_info& p, bool want_grads) {
     const bool al = p.aligned != 0;
+    const int vpt = p.vectors_per_thread;
     switch (workload) {
         case CREDIT_WL_RMSNORM_FORWARD:
-            return f32 ? rmsnorm_func<float>(p.threads, al) : rmsnorm_func<__nv_bfloat16>(p.threads, al);
+            return rmsnorm_kernel_for(dtype, p.threads, vpt, al);
         case CREDIT_WL_ROW_REDUCE:
-            return row_reduce_func(p.load_path, p.threads, al);
+            return row_reduce_kernel_for(p.load_path, p.threads, al);
         case CREDIT_WL_LAYERNORM_FORWARD:
-            return f32 ? layernorm_fwd_func<float>(p.threads, al)
-                       : layernorm_fwd_func<__nv_bfloat16>(p.threads, al);
+            return layernorm_fwd_kernel_for(dtype, p.threads, vpt, al);
         case CREDIT_WL_LAYERNORM_BACKWARD:
-            return f32 ? layernorm_bwd_dx_func<float>(p.threads, al, false)
-                       : layernorm_bwd_dx_func<__nv_bfloat16>(p.threads, al, false);
+            return layernorm_bwd_kernel_for(dtype, p.threads, vpt, al, false, false);
         case CREDIT_WL_LAYERNORM_BACKWARD_STATS:
-            if (p.vectors_per_thread > 0)
-                return f32 ? layernorm_bwd_grads_func<float>(p.threads, p.vectors_per_thread)
-                           : layernorm_bwd_grads_func<__nv_bfloat16>(p.threads, p.vectors_per_thread);
-            return f32 ? layernorm_bwd_dx_func<float>(p.threads, al, true)
-                       : layernorm_bwd_dx_func<__nv_bfloat16>(p.threads, al, true);
+            return layernorm_bwd_kernel_for(dtype, p.threads, vpt, al, true, want_grads);
         default:
             return nullptr;
     }
@@ -344,6 +285,18 @@ constexpr int kColsumRowsPerBlock = 128;   // fallback column-sum kernel: rows p
 constexpr int kColsumMaxBlocks = 1024;     // ... unless that would make more partials than this
 constexpr int kAutoStageBytes = 32 * 1024; // automatic cluster size aims at this much per stage
 constexpr int kAutoRingBytes = 96 * 1024;  // and at this much ring per CTA
+
+// Row elements a thread of the register path may own: what it keeps per element
+// in registers (raw data, gamma/beta, xhat and g, running column sums) bounds it.
+int max_elems_per_thread(int workload, bool grads) {
+    switch (workload) {
+        case CREDIT_WL_RMSNORM_FORWARD: return 32;
+        case CREDIT_WL_LAYERNORM_FORWARD: return 32;
+        case CREDIT_WL_LAYERNORM_BACKWARD: return 16;
+        case CREDIT_WL_LAYERNORM_BACKWARD_STATS: return grads ? 16 : 16;
+        default: return 0;
+    }
+}
 
 int inputs_staged(int workload) {
     return (workload == CREDIT_WL_LAYERNORM_BACKWARD || workload == CREDIT_WL_LAYERNORM_BACKWARD_STATS)
@@ -422,8 +375,17 @@ int plan_static(int workload, const Shape& s, int dtype, const credit_launch_opt
     };
     int cluster = o.cluster_size;
     if (cluster == 0) {
+        // Smallest cluster whose slice fits the stage budget and, for aligned rows,
+        // the register path at 512 threads.
         cluster = o.variant == CREDIT_VARIANT_CLUSTER_SMEM ? 2 : 1;
-        while (cluster < max_cluster && stage_bytes_for(cluster) > kAutoStageBytes) cluster *= 2;
+        auto fits = [&](int c) {
+            if (stage_bytes_for(c) > kAutoStageBytes) return false;
+            if (!p->aligned || (o.flags & CREDIT_FLAG_NO_REGISTER_PATH)) return true;
+            const int nvec = round_up((s.cols + c - 1) / c, 64) / s.vec_elems;
+            const int threads = o.threads ? o.threads : 512;
+            return nvec <= threads * (max_elems_per_thread(workload, grads) / s.vec_elems);
+        };
+        while (cluster < max_cluster && !fits(cluster)) cluster *= 2;
     }
     if (cluster > max_cluster)
         return fail(CREDIT_ERR_UNSUPPORTED, "cluster size %d not available on this device", cluster);
@@ -437,24 +399,25 @@ int plan_static(int workload, const Shape& s, int dtype, const credit_launch_opt
 
     p->threads = o.threads ? o.threads : 256;
     p->vectors_per_thread = 0;
-    if (grads && p->aligned) {
+    if (p->aligned && !(o.flags & CREDIT_FLAG_NO_REGISTER_PATH)) {
+        // Register path: the slice must fit `vpt` 16-byte vectors per thread, with
+        // vpt bounded by the registers the workload keeps per element.
+        const int max_vpt = max_elems_per_thread(workload, grads) / s.vec_elems;
         const int nvec = p->slice_elems / s.vec_elems;
         int threads = o.threads;
-        if (threads == 0) threads = nvec > 512 ? 512 : 256;
-        int vpt = (nvec + threads - 1) / threads;
-        if (vpt == 3) vpt = 4;
-        if (vpt <= 4) {
+        if (threads == 0) threads = nvec > 256 * max_vpt ? 512 : 256;
+        int vpt = 1;
+        while (vpt * threads < nvec) vpt *= 2;
+        if (vpt <= max_vpt) {
             p->threads = threads;
             p->vectors_per_thread = vpt;
         }
-        // otherwise: dx kernel + separate column-sum kernel
     }
 
     p->schedule = o.schedule;
     if (p->schedule == CREDIT_SCHEDULE_AUTO)
-        p->schedule = (p->aligned || p->vectors_per_thread > 0) ? CREDIT_SCHEDULE_PERSISTENT
-                                                                : CREDIT_SCHEDULE_ROW_PER_CLUSTER;
-    if (p->vectors_per_thread > 0 && p->schedule != CREDIT_SCHEDULE_PERSISTENT)
+        p->schedule = p->aligned ? CREDIT_SCHEDULE_PERSISTENT : CREDIT_SCHEDULE_ROW_PER_CLUSTER;
+    if (grads && p->vectors_per_thread > 0 && p->schedule != CREDIT_SCHEDULE_PERSISTENT)
         return fail(CREDIT_ERR_INVALID_ARGUMENT,
                     "column sums are accumulated by persistent clusters; schedule must be persistent");
 
@@ -520,7 +483,7 @@ int resolve(int workload, int64_t rows, int64_t cols, int dtype, const credit_la
     if (rc != CREDIT_OK) return rc;
     rc = plan_static(workload, r->shape, dtype, o, pointers_aligned, want_grads, r->dev->info, &r->plan);
     if (rc != CREDIT_OK) return rc;
-    r->func = workload_func(workload, dtype, r->plan);
+    r->func = workload_func(workload, dtype, r->plan, want_grads);
     if (r->func == nullptr) return fail(CREDIT_ERR_INVALID_ARGUMENT, "no kernel for workload %d", workload);
     rc = prepare_function(r->device, r->func, r->dev->info.max_dynamic_smem_per_block);
     if (rc != CREDIT_OK) return rc;
@@ -528,7 +491,7 @@ int resolve(int workload, int64_t rows, int64_t cols, int dtype, const credit_la
     if (rc != CREDIT_OK) return rc;
     if (workload == CREDIT_WL_LAYERNORM_BACKWARD_STATS && want_grads) {
         r->plan.workspace_bytes = grads_workspace_bytes(r->shape, r->plan);
-        r->plan.kernel_launches = r->plan.vectors_per_thread > 0 ? 2 : 3;
+        r->plan.kernel_launches = r->plan.vectors_per_thread > 0 ? 2 : 3;  // (+ column sums) + finish
     }
     return CREDIT_OK;
 }
@@ -601,7 +564,7 @@ int credit_plan(int workload, int64_t rows, int64_t cols, int dtype, const credi
 
 int credit_rmsnorm_forward(const void* x, const float* gamma, void* y, int64_t rows, int64_t cols,
                            float eps, int dtype, const credit_launch_opts* opts, void* stream) {
-    if (x == nullptr || gamma == nullptr || y == nullptr)
+    if (rows != 0 && (x == nullptr || gamma == nullptr || y == nullptr))
         return fail(CREDIT_ERR_INVALID_ARGUMENT, "x, gamma and y must not be NULL");
     Resolved r;
     int rc = resolve(CREDIT_WL_RMSNORM_FORWARD, rows, cols, dtype, opts,
@@ -615,7 +578,7 @@ int credit_rmsnorm_forward(const void* x, const float* gamma, void* y, int64_t r
 
 int credit_row_reduce(const float* x, float* out_sum, float* out_max, int64_t* out_argmax,
                       int64_t rows, int64_t cols, const credit_launch_opts* opts, void* stream) {
-    if (x == nullptr || out_sum == nullptr || out_max == nullptr || out_argmax == nullptr)
+    if (rows != 0 && (x == nullptr || out_sum == nullptr || out_max == nullptr || out_argmax == nullptr))
         return fail(CREDIT_ERR_INVALID_ARGUMENT, "x and the three outputs must not be NULL");
     Resolved r;
     int rc = resolve(CREDIT_WL_ROW_REDUCE, rows, cols, CREDIT_F32, opts, aligned16(x), false, &r);
@@ -637,8 +600,8 @@ int credit_row_reduce(const float* x, float* out_sum, float* out_max, int64_t* o
 int credit_layernorm_forward(const void* x, const float* gamma, const float* beta, void* y,
                              float* mean, float* rstd, int64_t rows, int64_t cols, float eps,
                              int dtype, const credit_launch_opts* opts, void* stream) {
-    if (x == nullptr || gamma == nullptr || beta == nullptr || y == nullptr || mean == nullptr ||
-        rstd == nullptr)
+    if (rows != 0 && (x == nullptr || gamma == nullptr || beta == nullptr || y == nullptr ||
+                      mean == nullptr || rstd == nullptr))
         return fail(CREDIT_ERR_INVALID_ARGUMENT, "x, gamma, beta, y, mean and rstd must not be NULL");
     Resolved r;
     int rc = resolve(CREDIT_WL_LAYERNORM_FORWARD, rows, cols, dtype, opts,
@@ -653,7 +616,7 @@ int credit_layernorm_forward(const void* x, const float* gamma, const float* bet
 int credit_layernorm_backward(const void* x, const void* dy, const float* gamma, void* dx,
                               int64_t rows, int64_t cols, float eps, int dtype,
                               const credit_launch_opts* opts, void* stream) {
-    if (x == nullptr || dy == nullptr || gamma == nullptr || dx == nullptr)
+    if (rows != 0 && (x == nullptr || dy == nullptr || gamma == nullptr || dx == nullptr))
         return fail(CREDIT_ERR_INVALID_ARGUMENT, "x, dy, gamma and dx must not be NULL");
     Resolved r;
     int rc = resolve(CREDIT_WL_LAYERNORM_BACKWARD, rows, cols, dtype, opts,
@@ -663,7 +626,11 @@ int credit_layernorm_backward(const void* x, const void* dy, const float* gamma,
     StagedArgs a = staged_args(r);
     const float* no_stats = nullptr;
     float* no_partials = nullptr;
-    void* args[] = {&x, &dy, &gamma, &no_stats, &no_stats, &dx, &no_partials, &eps, &a};
+    if (r.plan.vectors_per_thread > 0) {
+        void* args[] = {&x, &dy, &gamma, &no_stats, &no_stats, &dx, &no_partials, &eps, &a};
+        return launch_cluster_kernel(make_launch(r, stream), args);
+    }
+    void* args[] = {&x, &dy, &gamma, &no_stats, &no_stats, &dx, &eps, &a};
     return launch_cluster_kernel(make_launch(r, stream), args);
 }
 
@@ -685,8 +652,8 @@ int credit_layernorm_backward_stats(const void* x, const void* dy, const float* 
                                     float* dbeta, int64_t rows, int64_t cols, int dtype,
                                     const credit_launch_opts* opts, void* workspace,
                                     size_t workspace_bytes, void* stream) {
-    if (x == nullptr || dy == nullptr || gamma == nullptr || mean == nullptr || rstd == nullptr ||
-        dx == nullptr)
+    if (rows != 0 && (x == nullptr || dy == nullptr || gamma == nullptr || mean == nullptr ||
+                      rstd == nullptr || dx == nullptr))
         return fail(CREDIT_ERR_INVALID_ARGUMENT, "x, dy, gamma, mean, rstd and dx must not be NULL");
     if ((dgamma == nullptr) != (dbeta == nullptr))
         return fail(CREDIT_ERR_INVALID_ARGUMENT, "dgamma and dbeta must both be given or both be NULL");
@@ -713,30 +680,134 @@ int credit_layernorm_backward_stats(const void* x, const void* dy, const float* 
     StagedArgs a = staged_args(r);
     float* partials = static_cast<float*>(workspace);
     float eps = 0.0f;
-    void* args[] = {&x, &dy, &gamma, &mean, &rstd, &dx, &partials, &eps, &a};
-    rc = launch_cluster_kernel(make_launch(r, stream), args);
+    if (r.plan.vectors_per_thread > 0) {
+        void* args[] = {&x, &dy, &gamma, &mean, &rstd, &dx, &partials, &eps, &a};
+        rc = launch_cluster_kernel(make_launch(r, stream), args);
+    } else {
+        void* args[] = {&x, &dy, &gamma, &mean, &rstd, &dx, &eps, &a};
+        rc = launch_cluster_kernel(make_launch(r, stream), args);
+    }
     if (rc != CREDIT_OK) return rc;
     if (!want_grads) return CREDIT_OK;
 
     int num_partials = r.plan.num_clusters;
-    const int col_blocks = (r.shape.cols + 255) / 256;
     if (r.plan.vectors_per_thread == 0) {
         num_partials = colsum_blocks(r.shape.rows);
-        const int rows_per_block = (r.shape.rows + num_partials - 1) / num_partials;
-        dim3 grid(static_cast<unsigned>(col_blocks), static_cast<unsigned>(num_partials));
-        if (dtype == CREDIT_F32)
-            layernorm_bwd_colsum_kernel<float><<<grid, 256, 0, s>>>(
-                static_cast<const float*>(x), static_cast<const float*>(dy), mean, rstd, partials,
-                r.shape.rows, r.shape.cols, rows_per_block);
-        else
-            layernorm_bwd_colsum_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(
-                static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(dy), mean,
-                rstd, partials, r.shape.rows, r.shape.cols, rows_per_block);
-        CREDIT_CUDA_TRY(cudaGetLastError());
+        CREDIT_CUDA_TRY(launch_layernorm_bwd_colsum(dtype, x, dy, mean, rstd, partials, r.shape.rows,
+                                                    r.shape.cols, num_partials, s));
     }
-    layernorm_bwd_finish_kernel<<<col_blocks, 256, 0, s>>>(partials, dgamma, dbeta, r.shape.cols,
-                                                           num_partials);
-    CREDIT_CUDA_TRY(cudaGetLastError());
+    CREDIT_CUDA_TRY(launch_layernorm_bwd_finish(partials, dgamma, dbeta, r.shape.cols, num_partials, s));
+    return CREDIT_OK;
+}
+
+// ---------------------------------------------------------------------------
+// host-buffer path
+// ---------------------------------------------------------------------------
+namespace {
+
+struct HostPipe {
+    bool ready = false;
+    cudaStream_t copy_stream = nullptr;
+    cudaEvent_t loaded[2] = {nullptr, nullptr};   // block is on the device
+    cudaEvent_t consumed[2] = {nullptr, nullptr}; // block has been reduced
+};
+std::map<int, HostPipe> g_host_pipes;
+
+int host_pipe(int device, HostPipe** out) {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    HostPipe& hp = g_host_pipes[device];
+    if (!hp.ready) {
+        CREDIT_CUDA_TRY(cudaStreamCreateWithFlags(&hp.copy_stream, cudaStreamNonBlocking));
+        for (int i = 0; i < 2; ++i) {
+            CREDIT_CUDA_TRY(cudaEventCreateWithFlags(&hp.loaded[i], cudaEventDisableTiming));
+            CREDIT_CUDA_TRY(cudaEventCreateWithFlags(&hp.consumed[i], cudaEventDisableTiming));
+        }
+        hp.ready = true;
+    }
+    *out = &hp;
+    return CREDIT_OK;
+}
+
+constexpr size_t kHostOutAlign = 256;
+size_t host_out_bytes(int64_t rows) {
+    // sum, max (fp32) and argmax (int64) on the device, each 256-byte aligned
+    const size_t a = (static_cast<size_t>(rows) * 4 + kHostOutAlign - 1) / kHostOutAlign * kHostOutAlign;
+    const size_t b = (static_cast<size_t>(rows) * 8 + kHostOutAlign - 1) / kHostOutAlign * kHostOutAlign;
+    return 2 * a + b;
+}
+constexpr int64_t kHostMinBlockBytes = 32ll << 20;
+
+}  // namespace
+
+size_t credit_row_reduce_host_scratch_bytes(int64_t rows, int64_t cols) {
+    if (rows <= 0 || cols <= 0) return 0;
+    const int64_t row_bytes = cols * 4;
+    int64_t block_rows = std::max<int64_t>(1, kHostMinBlockBytes / row_bytes);
+    block_rows = std::min(block_rows, rows);
+    const size_t in_bytes = (static_cast<size_t>(block_rows * row_bytes) + 255) / 256 * 256;
+    return 2 * in_bytes + host_out_bytes(rows);
+}
+
+int credit_row_reduce_host(const float* x_host, float* out_sum_host, float* out_max_host,
+                           int64_t* out_argmax_host, int64_t rows, int64_t cols,
+                           const credit_launch_opts* opts, void* scratch, size_t scratch_bytes,
+                           void* stream) {
+    if (x_host == nullptr || out_sum_host == nullptr || out_max_host == nullptr ||
+        out_argmax_host == nullptr)
+        return fail(CREDIT_ERR_INVALID_ARGUMENT, "host input and outputs must not be NULL");
+    Shape shape;
+    int rc = check_shape(rows, cols, CREDIT_F32, &shape);
+    if (rc != CREDIT_OK) return rc;
+    if (rows == 0) return CREDIT_OK;
+    const size_t need = credit_row_reduce_host_scratch_bytes(rows, cols);
+    if (scratch == nullptr || scratch_bytes < need || !aligned16(scratch))
+        return fail(CREDIT_ERR_WORKSPACE, "scratch of %zu B given, %zu B (16-byte aligned) needed",
+                    scratch_bytes, need);
+    int device = 0;
+    CREDIT_CUDA_TRY(cudaGetDevice(&device));
+    HostPipe* hp = nullptr;
+    rc = host_pipe(device, &hp);
+    if (rc != CREDIT_OK) return rc;
+    cudaStream_t compute = static_cast<cudaStream_t>(stream);
+
+    const size_t out_bytes = host_out_bytes(rows);
+    const size_t row_bytes = static_cast<size_t>(cols) * 4;
+    const size_t per_buffer = ((scratch_bytes - out_bytes) / 2) / 256 * 256;
+    int64_t block_rows = std::min<int64_t>(rows, static_cast<int64_t>(per_buffer / row_bytes));
+    if (block_rows < 1) return fail(CREDIT_ERR_WORKSPACE, "scratch cannot hold one row twice");
+    char* base = static_cast<char*>(scratch);
+    float* in_buf[2] = {reinterpret_cast<float*>(base), reinterpret_cast<float*>(base + per_buffer)};
+    char* outs = base + 2 * per_buffer;
+    const size_t a = (static_cast<size_t>(rows) * 4 + kHostOutAlign - 1) / kHostOutAlign * kHostOutAlign;
+    float* d_sum = reinterpret_cast<float*>(outs);
+    float* d_max = reinterpret_cast<float*>(outs + a);
+    int64_t* d_arg = reinterpret_cast<int64_t*>(outs + 2 * a);
+
+    int block = 0;
+    for (int64_t r0 = 0; r0 < rows; r0 += block_rows, ++block) {
+        const int64_t n = std::min(block_rows, rows - r0);
+        const int b = block & 1;
+        if (block >= 2) CREDIT_CUDA_TRY(cudaStreamWaitEvent(hp->copy_stream, hp->consumed[b], 0));
+        CREDIT_CUDA_TRY(cudaMemcpyAsync(in_buf[b], x_host + static_cast<size_t>(r0) * cols,
+                                        static_cast<size_t>(n) * row_bytes, cudaMemcpyHostToDevice,
+                                        hp->copy_stream));
+        CREDIT_CUDA_TRY(cudaEventRecord(hp->loaded[b], hp->copy_stream));
+        CREDIT_CUDA_TRY(cudaStreamWaitEvent(compute, hp->loaded[b], 0));
+        rc = credit_row_reduce(in_buf[b], d_sum + r0, d_max + r0, d_arg + r0, n, cols, opts, stream);
+        if (rc != CREDIT_OK) {
+            cudaStreamSynchronize(hp->copy_stream);
+            cudaStreamSynchronize(compute);
+            return rc;
+        }
+        CREDIT_CUDA_TRY(cudaEventRecord(hp->consumed[b], compute));
+    }
+    CREDIT_CUDA_TRY(cudaMemcpyAsync(out_sum_host, d_sum, static_cast<size_t>(rows) * 4,
+                                    cudaMemcpyDeviceToHost, compute));
+    CREDIT_CUDA_TRY(cudaMemcpyAsync(out_max_host, d_max, static_cast<size_t>(rows) * 4,
+                                    cudaMemcpyDeviceToHost, compute));
+    CREDIT_CUDA_TRY(cudaMemcpyAsync(out_argmax_host, d_arg, static_cast<size_t>(rows) * 8,
+                                    cudaMemcpyDeviceToHost, compute));
+    CREDIT_CUDA_TRY(cudaStreamSynchronize(compute));
     return CREDIT_OK;
 }
 

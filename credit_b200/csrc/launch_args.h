@@ -1,0 +1,39 @@
+// Constants and kernel-argument structs shared by the host launcher and the
+// device code.
+#pragma once
+
+namespace credit {
+
+constexpr int kMaxClusterSize = 16;   // 8 portable, 16 with the non-portable opt-in
+constexpr int kMaxWarpsPerCta = 32;
+constexpr int kMaxStages = 8;
+// Bytes reserved at the start of dynamic shared memory for barriers and
+// reduction scratch; row data starts after it (keeps 1024-byte alignment).
+constexpr int kControlBytes = 4096;
+
+// Bits of the device status word (see credit_device_status in the C ABI).
+constexpr int kStatusWaitTimeout = 1;      // an mbarrier wait ran out of patience
+constexpr int kStatusBadGeometry = 2;      // a kernel saw a launch shape it cannot handle
+
+// Geometry shared by the staged kernels.
+struct StagedArgs {
+    int rows;
+    int cols;
+    int slice_elems;    // columns per CTA (multiple of 64); stage stride in elements
+    int num_clusters;   // clusters in the grid; cluster c handles rows c, c+num_clusters, ...
+    int stages;         // ring depth (1 for the scalar-fill path)
+    int* status;        // device status word
+};
+
+// Geometry of the streaming row reduction.
+struct ReduceArgs {
+    int rows;
+    int cols;
+    int slice_elems;    // columns per CTA, multiple of 64
+    int num_clusters;
+    int stages;         // ring depth (TMA variant)
+    int chunk_elems;    // columns per ring chunk, multiple of 4 (TMA variant)
+    int* status;
+};
+
+}  // namespace credit

@@ -23,16 +23,6 @@ struct alignas(16) StagedControl {
     ReduceScratch<K> red;
 };
 
-// Geometry shared by the staged kernels.
-struct StagedArgs {
-    int rows;
-    int cols;
-    int slice_elems;    // columns per CTA (multiple of 64); stage stride in elements
-    int num_clusters;   // clusters in the grid; cluster c handles rows c, c+num_clusters, ...
-    int stages;         // ring depth (1 for the scalar-fill path)
-    int* status;        // device status word
-};
-
 // Issues the bulk copies that bring NIN slices of `row` into ring stage `stage`.
 // Called by one thread.
 template <typename T, int NIN>
@@ -366,29 +356,22 @@ layernorm_fwd_kernel(const T* __restrict__ x, const float* __restrict__ gamma,
 }
 
 // ---------------------------------------------------------------------------
-// LayerNorm backward.
+// LayerNorm backward, generic form (any width, any alignment): dx only.
 //   xhat = (x - mean) * rstd,  g = dy * gamma
 //   dx   = (g - mean_row(g) - xhat * mean_row(g * xhat)) * rstd
-//   dgamma[c] = sum_rows dy * xhat,  dbeta[c] = sum_rows dy      (PARAM_GRADS)
 // HAS_STATS: mean/rstd are inputs (one DSMEM stage); otherwise they are
 // recomputed from the staged x slice first (two DSMEM stages), which is the form
 // of the reference kernel (src/workloads/layernorm_backward.cu:401-437) and of
 // dsmem_eval/workloads.py:53-61. Both x and dy are staged, so dy is read from
-// HBM once (the reference reads it twice, :418 and :434).
-//
-// PARAM_GRADS needs the aligned path and a slice of at most VPT*THREADS vectors:
-// thread t owns vectors t, t+THREADS, ... of the slice for every row its cluster
-// handles, keeps gamma for them and the running column sums in registers, and at
-// the end writes them to `partials` laid out [num_clusters][2][cols] (fp32); a
-// finishing kernel adds the clusters in a fixed order.
+// HBM once (the reference reads it twice, :418 and :434). The column sums
+// dgamma/dbeta of shapes that end up here come from layernorm_bwd_colsum_kernel.
 // ---------------------------------------------------------------------------
-template <typename T, int THREADS, int VPT, bool ALIGNED, bool HAS_STATS, bool PARAM_GRADS>
+template <typename T, int THREADS, bool ALIGNED, bool HAS_STATS>
 __global__ void __launch_bounds__(THREADS)
 layernorm_bwd_kernel(const T* __restrict__ x, const T* __restrict__ dy,
                      const float* __restrict__ gamma, const float* __restrict__ mean_in,
-                     const float* __restrict__ rstd_in, T* __restrict__ dx,
-                     float* __restrict__ partials, float eps, StagedArgs a) {
-    static_assert(!PARAM_GRADS || ALIGNED, "column sums use the vector path");
+                     const float* __restrict__ rstd_in, T* __restrict__ dx, float eps,
+                     StagedArgs a) {
     extern __shared__ __align__(1024) unsigned char smem[];
     auto& ctl = *reinterpret_cast<StagedControl<2>*>(smem);
     unsigned char* data = smem + kControlBytes;
@@ -406,30 +389,6 @@ layernorm_bwd_kernel(const T* __restrict__ x, const T* __restrict__ dy,
     uint32_t red_parity = 0;
     const int nvec = g.local / E;
     const float inv_cols = 1.0f / static_cast<float>(a.cols);
-
-    // Per-thread state of the column sums (PARAM_GRADS only).
-    float gam[PARAM_GRADS ? VPT : 1][E];
-    float dgam[PARAM_GRADS ? VPT : 1][E];
-    float dbet[PARAM_GRADS ? VPT : 1][E];
-    if (PARAM_GRADS) {
-        if (nvec > VPT * THREADS) {
-            if (threadIdx.x == 0) atomicOr(a.status, kStatusBadGeometry);
-        }
-#pragma unroll
-        for (int i = 0; i < VPT; ++i) {
-            const int v = threadIdx.x + i * THREADS;
-#pragma unroll
-            for (int j = 0; j < E; ++j) {
-                gam[i][j] = 0.0f;
-                dgam[i][j] = 0.0f;
-                dbet[i][j] = 0.0f;
-            }
-            if (v < nvec) {
-#pragma unroll
-                for (int j = 0; j < E; j += 4) ldg_f32x4(gamma + g.start + v * E + j, &gam[i][j]);
-            }
-        }
-    }
 
     for (int row = cluster; row < a.rows; row += a.num_clusters) {
         float mean = 0.0f, rstd = 0.0f;
@@ -454,28 +413,9 @@ layernorm_bwd_kernel(const T* __restrict__ x, const T* __restrict__ dy,
         }
         const float shift = -mean * rstd;
 
-        // pass 1: row sums of g and g*xhat (and the column sums)
+        // pass 1: row sums of g and g*xhat
         float part[2] = {0.0f, 0.0f};
-        if (PARAM_GRADS) {
-#pragma unroll
-            for (int i = 0; i < VPT; ++i) {
-                const int v = threadIdx.x + i * THREADS;
-                if (v < nvec) {
-                    float xv[E], dv[E];
-                    RowVec<T>::from_smem(xt, v, xv);
-                    RowVec<T>::from_smem(dyt, v, dv);
-#pragma unroll
-                    for (int j = 0; j < E; ++j) {
-                        const float xhat = fmaf(xv[j], rstd, shift);
-                        const float gg = dv[j] * gam[i][j];
-                        part[0] += gg;
-                        part[1] = fmaf(gg, xhat, part[1]);
-                        dgam[i][j] = fmaf(dv[j], xhat, dgam[i][j]);
-                        dbet[i][j] += dv[j];
-                    }
-                }
-            }
-        } else if (ALIGNED) {
+        if (ALIGNED) {
             float acc0[E], acc1[E];
 #pragma unroll
             for (int j = 0; j < E; ++j) { acc0[j] = 0.0f; acc1[j] = 0.0f; }
@@ -511,24 +451,7 @@ layernorm_bwd_kernel(const T* __restrict__ x, const T* __restrict__ dy,
 
         // pass 2: dx from the staged slices
         const size_t out_base = static_cast<size_t>(row) * a.cols + g.start;
-        if (PARAM_GRADS) {
-#pragma unroll
-            for (int i = 0; i < VPT; ++i) {
-                const int v = threadIdx.x + i * THREADS;
-                if (v < nvec) {
-                    float xv[E], dv[E];
-                    RowVec<T>::from_smem(xt, v, xv);
-                    RowVec<T>::from_smem(dyt, v, dv);
-#pragma unroll
-                    for (int j = 0; j < E; ++j) {
-                        const float xhat = fmaf(xv[j], rstd, shift);
-                        const float gg = dv[j] * gam[i][j];
-                        xv[j] = (gg - mean_g - xhat * mean_gx) * rstd;
-                    }
-                    RowVec<T>::to_global(dx + out_base + static_cast<size_t>(v) * E, xv);
-                }
-            }
-        } else if (ALIGNED) {
+        if (ALIGNED) {
 #pragma unroll 2
             for (int v = threadIdx.x; v < nvec; v += THREADS) {
                 float xv[E], dv[E], gv[E];
@@ -554,68 +477,6 @@ layernorm_bwd_kernel(const T* __restrict__ x, const T* __restrict__ dy,
         staged_release<T, 2, 2, ALIGNED>(ctl, src, data, cur.stage, row, a, g);
         cur.advance(a.stages);
     }
-
-    if (PARAM_GRADS) {
-        float* out_g = partials + (static_cast<size_t>(cluster) * 2 + 0) * a.cols + g.start;
-        float* out_b = partials + (static_cast<size_t>(cluster) * 2 + 1) * a.cols + g.start;
-#pragma unroll
-        for (int i = 0; i < VPT; ++i) {
-            const int v = threadIdx.x + i * THREADS;
-            if (v < nvec) {
-#pragma unroll
-                for (int j = 0; j < E; j += 4) {
-                    *reinterpret_cast<float4*>(out_g + v * E + j) =
-                        make_float4(dgam[i][j], dgam[i][j + 1], dgam[i][j + 2], dgam[i][j + 3]);
-                    *reinterpret_cast<float4*>(out_b + v * E + j) =
-                        make_float4(dbet[i][j], dbet[i][j + 1], dbet[i][j + 2], dbet[i][j + 3]);
-                }
-            }
-        }
-    }
-}
-
-// Column sums for shapes the register-accumulator kernel cannot take (rows not
-// 16-byte aligned, or slices wider than its register budget): one CTA per
-// (row block, 32*4-column tile) writes a [2][cols] partial per row block into the
-// same `partials` layout, so the same finishing kernel applies.
-template <typename T>
-__global__ void __launch_bounds__(256)
-layernorm_bwd_colsum_kernel(const T* __restrict__ x, const T* __restrict__ dy,
-                            const float* __restrict__ mean_in, const float* __restrict__ rstd_in,
-                            float* __restrict__ partials, int rows, int cols, int rows_per_block) {
-    const int col = blockIdx.x * 256 + threadIdx.x;
-    const int block = blockIdx.y;
-    const int r0 = block * rows_per_block;
-    const int r1 = min(rows, r0 + rows_per_block);
-    if (col >= cols) return;
-    float sg = 0.0f, sb = 0.0f;
-    for (int r = r0; r < r1; ++r) {
-        const float m = __ldg(mean_in + r);
-        const float rs = __ldg(rstd_in + r);
-        const size_t idx = static_cast<size_t>(r) * cols + col;
-        const float xv = RowVec<T>::to_float(x[idx]);
-        const float dv = RowVec<T>::to_float(dy[idx]);
-        sg = fmaf(dv, (xv - m) * rs, sg);
-        sb += dv;
-    }
-    partials[(static_cast<size_t>(block) * 2 + 0) * cols + col] = sg;
-    partials[(static_cast<size_t>(block) * 2 + 1) * cols + col] = sb;
-}
-
-// dgamma[c] = sum_k partials[k][0][c], dbeta[c] = sum_k partials[k][1][c], k in
-// fixed order: deterministic, no atomics.
-__global__ void __launch_bounds__(256)
-layernorm_bwd_finish_kernel(const float* __restrict__ partials, float* __restrict__ dgamma,
-                            float* __restrict__ dbeta, int cols, int num_partials) {
-    const int col = blockIdx.x * 256 + threadIdx.x;
-    if (col >= cols) return;
-    float sg = 0.0f, sb = 0.0f;
-    for (int k = 0; k < num_partials; ++k) {
-        sg += partials[(static_cast<size_t>(k) * 2 + 0) * cols + col];
-        sb += partials[(static_cast<size_t>(k) * 2 + 1) * cols + col];
-    }
-    dgamma[col] = sg;
-    dbeta[col] = sb;
 }
 
 }  // namespace credit

@@ -71,16 +71,6 @@ struct ReduceControl {
     int slot_idx[2][kMaxClusterSize];
 };
 
-struct ReduceArgs {
-    int rows;
-    int cols;
-    int slice_elems;    // columns per CTA, multiple of 64
-    int num_clusters;
-    int stages;         // ring depth (TMA variant)
-    int chunk_elems;    // columns per ring chunk, multiple of 4 (TMA variant)
-    int* status;
-};
-
 // CTA partials -> rank 0 of the cluster -> outputs. Called by all threads once
 // per row, after the slice has been folded into (sum4, best).
 template <int THREADS>

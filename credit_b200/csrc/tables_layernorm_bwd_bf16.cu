@@ -1,0 +1,41 @@
+// LayerNorm backward, bf16 rows: register-path kernel instantiations.
+#include <cuda_bf16.h>
+
+#include "../../include/credit_b200.h"
+#include "kernel_tables.h"
+#include "norm_kernels.cuh"
+#include "register_row_kernels.cuh"
+
+namespace credit {
+namespace {
+
+#define CREDIT_PICK_VPT(KERNEL, T, THREADS, ...)                       \
+    switch (vpt) {                                                     \
+        case 1: return (const void*)KERNEL<T, THREADS, 1 __VA_ARGS__>; \
+        case 2: return (const void*)KERNEL<T, THREADS, 2 __VA_ARGS__>; \
+        case 4: return (const void*)KERNEL<T, THREADS, 4 __VA_ARGS__>; \
+        default: return nullptr;                                       \
+    }
+#define CREDIT_COMMA ,
+
+template <typename T>
+const void* reg_func(int threads, int vpt, bool has_stats, bool grads) {
+    if (!has_stats) {
+        if (threads == 512) { CREDIT_PICK_VPT(layernorm_bwd_reg_kernel, T, 512, CREDIT_COMMA false CREDIT_COMMA false) }
+        CREDIT_PICK_VPT(layernorm_bwd_reg_kernel, T, 256, CREDIT_COMMA false CREDIT_COMMA false)
+    }
+    if (!grads) {
+        if (threads == 512) { CREDIT_PICK_VPT(layernorm_bwd_reg_kernel, T, 512, CREDIT_COMMA true CREDIT_COMMA false) }
+        CREDIT_PICK_VPT(layernorm_bwd_reg_kernel, T, 256, CREDIT_COMMA true CREDIT_COMMA false)
+    }
+    if (threads == 512) { CREDIT_PICK_VPT(layernorm_bwd_reg_kernel, T, 512, CREDIT_COMMA true CREDIT_COMMA true) }
+    CREDIT_PICK_VPT(layernorm_bwd_reg_kernel, T, 256, CREDIT_COMMA true CREDIT_COMMA true)
+}
+
+}  // namespace
+
+const void* layernorm_bwd_reg_kernel_bf16(int threads, int vpt, bool has_stats, bool grads) {
+    return reg_func<__nv_bfloat16>(threads, vpt, has_stats, grads);
+}
+
+}  // namespace credit

@@ -68,6 +68,12 @@ typedef enum credit_schedule {
     CREDIT_SCHEDULE_PERSISTENT = 2       /* grid = resident clusters, each walks many rows */
 } credit_schedule;
 
+typedef enum credit_launch_flags {
+    /* Keep aligned rows on the generic shared-memory kernels (every pass re-reads the
+     * staged slice, cluster barrier exchange) instead of the register-resident ones. */
+    CREDIT_FLAG_NO_REGISTER_PATH = 1
+} credit_launch_flags;
+
 typedef struct credit_launch_opts {
     int cluster_size; /* CTAs per row: 1,2,4,8,16; 0 = automatic */
     int variant;      /* credit_variant */
@@ -76,7 +82,7 @@ typedef struct credit_launch_opts {
     int schedule;     /* credit_schedule */
     int load_path;    /* credit_load_path (streaming kernels) */
     int chunk_bytes;  /* ring chunk of the streaming kernels, multiple of 1024; 0 = automatic */
-    int reserved;
+    int flags;        /* credit_launch_flags, OR-ed */
 } credit_launch_opts;
 
 /* The fields of DeviceInfo in the reference binaries
@@ -116,7 +122,7 @@ typedef struct credit_plan_info {
     int aligned;            /* 1 = 16-byte path */
     int slice_elems;        /* columns per CTA */
     int chunk_elems;        /* streaming kernels: columns per ring chunk */
-    int vectors_per_thread; /* LayerNorm backward with column sums */
+    int vectors_per_thread; /* register path: 16-byte vectors each thread owns; 0 = generic path */
     int num_clusters;       /* clusters in the grid */
     int grid_ctas;
     int smem_bytes;         /* dynamic shared memory per CTA */
@@ -188,6 +194,25 @@ int credit_layernorm_backward_stats(const void* x, const void* dy, const float* 
                                     float* dbeta, int64_t rows, int64_t cols, int dtype,
                                     const credit_launch_opts* opts, void* workspace,
                                     size_t workspace_bytes, void* stream);
+
+/* Host-buffer entry point ------------------------------------------------ */
+
+/* credit_row_reduce on HOST data: x_host [rows, cols] fp32 is copied to the device
+ * in row blocks through `scratch` (two input buffers, so the copy of one block
+ * overlaps the reduction of the previous one), reduced there, and the three
+ * result vectors are copied back to out_*_host. Pinned host memory makes the
+ * copies asynchronous to each other; pageable memory works but serialises.
+ * `scratch` is caller-owned device memory of at least
+ * credit_row_reduce_host_scratch_bytes(rows, cols) bytes (more lets the blocks
+ * grow, up to the whole matrix). The call returns after the results are in host
+ * memory (it synchronises `stream`). This is the shape of the reference
+ * executables' run_shape (layernorm_backward.cu:767-805), which own their device
+ * buffers, with the allocation moved to the caller. */
+size_t credit_row_reduce_host_scratch_bytes(int64_t rows, int64_t cols);
+int credit_row_reduce_host(const float* x_host, float* out_sum_host, float* out_max_host,
+                           int64_t* out_argmax_host, int64_t rows, int64_t cols,
+                           const credit_launch_opts* opts, void* scratch, size_t scratch_bytes,
+                           void* stream);
 
 #ifdef __cplusplus
 }

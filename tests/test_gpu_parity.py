@@ -370,6 +370,73 @@ def test_layernorm_backward_stats_is_deterministic():
 
 
 # ---------------------------------------------------------------------------
+# Generic shared-memory kernels on aligned rows (the register path switched off),
+# and plans that land on each path
+# ---------------------------------------------------------------------------
+GENERIC = {"flags": N.FLAG_NO_REGISTER_PATH}
+
+
+@pytest.mark.parametrize("cluster_size", [1, 2, 8, 16])
+def test_generic_path_on_aligned_rows(cluster_size):
+    rows, cols = 300, 4096
+    x, gamma = W.make_rmsnorm_inputs(rows, cols, "cpu", seed=31)
+    (y,) = try_run("rmsnorm_forward", (x, gamma), cluster_size, GENERIC)
+    close(y, O.rmsnorm_forward(x, gamma, dtype=torch.float64), FP32_RTOL, what="y")
+
+    inputs = W.make_layernorm_forward_inputs(rows, cols, "cpu", seed=32)
+    check_layernorm_forward(inputs, try_run("layernorm_forward", inputs, cluster_size, GENERIC), BF16_RTOL)
+
+    inputs = W.make_layernorm_inputs(rows, cols, "cpu", seed=33)
+    (dx,) = try_run("layernorm_backward", inputs, cluster_size, GENERIC)
+    close(dx, O.layernorm_backward(*[t.double() for t in inputs]), FP32_RTOL, scale=2.0, what="dx")
+
+    inputs = W.make_layernorm_backward_stats_inputs(rows, cols, "cpu", seed=34)
+    check_backward_stats(inputs, try_run("layernorm_backward_stats", inputs, cluster_size, GENERIC),
+                         BF16_RTOL)
+
+
+def test_generic_path_persistent_ring():
+    rows, cols = 2500, 2048
+    opts = dict(GENERIC, schedule=N.SCHEDULE_PERSISTENT, stages=3)
+    x, gamma = W.make_rmsnorm_inputs(rows, cols, "cpu", seed=35)
+    (y,) = run("rmsnorm_forward", (x, gamma), 2, opts)
+    close(y, O.rmsnorm_forward(x, gamma, dtype=torch.float64), FP32_RTOL, what="y")
+
+
+def test_plans_choose_the_expected_path():
+    # aligned rows: register path; the flag or a ragged width: generic path
+    assert N.plan(N.WL_RMSNORM_FORWARD, 1024, 32768, N.F32).vectors_per_thread > 0
+    assert N.plan(N.WL_RMSNORM_FORWARD, 1024, 32768, N.F32, GENERIC).vectors_per_thread == 0
+    assert N.plan(N.WL_RMSNORM_FORWARD, 8, 1001, N.F32).vectors_per_thread == 0
+    assert N.plan(N.WL_LAYERNORM_FORWARD, 4096, 131072, N.BF16).vectors_per_thread > 0
+    # a slice too wide for the registers of one CTA falls back to the generic kernel
+    p = N.plan(N.WL_LAYERNORM_BACKWARD_STATS, 64, 65536, N.BF16, {"cluster_size": 2})
+    assert p.vectors_per_thread == 0 and p.kernel_launches == 3
+
+
+def test_wide_slice_column_sums_use_the_fallback_kernels():
+    rows, cols = 300, 16384
+    inputs = W.make_layernorm_backward_stats_inputs(rows, cols, "cpu", seed=36)
+    check_backward_stats(inputs, try_run("layernorm_backward_stats", inputs, 1), BF16_RTOL)
+
+
+@pytest.mark.parametrize("threads", [256, 512])
+@pytest.mark.parametrize("cluster_size", [1, 2, 4, 8, 16])
+def test_register_path_every_vector_count(cluster_size, threads):
+    """Sweeps vectors-per-thread 1..8 through the cluster size at a fixed width."""
+    rows, cols = 700, 8192
+    opts = {"threads": threads}
+    x, gamma = W.make_rmsnorm_inputs(rows, cols, "cpu", seed=41)
+    (y,) = try_run("rmsnorm_forward", (x, gamma), cluster_size, opts)
+    close(y, O.rmsnorm_forward(x, gamma, dtype=torch.float64), FP32_RTOL, what="y")
+    inputs = W.make_layernorm_forward_inputs(rows, cols, "cpu", seed=42, dtype=torch.float32)
+    check_layernorm_forward(inputs, try_run("layernorm_forward", inputs, cluster_size, opts), FP32_RTOL)
+    inputs = W.make_layernorm_inputs(rows, cols, "cpu", seed=43)
+    (dx,) = try_run("layernorm_backward", inputs, cluster_size, opts)
+    close(dx, O.layernorm_backward(*[t.double() for t in inputs]), FP32_RTOL, scale=2.0, what="dx")
+
+
+# ---------------------------------------------------------------------------
 # Argument checking and the launch plan
 # ---------------------------------------------------------------------------
 def test_bad_arguments_are_reported_not_fatal():
