@@ -91,6 +91,7 @@ class PlanInfo(Structure):
         ("slice_elems", c_int),
         ("chunk_elems", c_int),
         ("vectors_per_thread", c_int),
+        ("full_tiles", c_int),
         ("num_clusters", c_int),
         ("grid_ctas", c_int),
         ("smem_bytes", c_int),

@@ -34,8 +34,10 @@ LIB_SOURCES = [
     "tables_row_reduce.cu",
 ]
 OBJ_DIR = LIB_DIR / "obj"
-# name of the executable -> source
-CLI_SOURCES: dict[str, str] = {}
+# name of the executable -> (source, links against the shared library)
+CLI_SOURCES: dict[str, tuple[str, bool]] = {
+    "primitive_benchmark": ("primitive_benchmark.cu", False),
+}
 
 
 def nvcc_path() -> str:
@@ -91,16 +93,16 @@ def build_cli(force: bool = False, verbose: bool = False) -> list[Path]:
     BIN_DIR.mkdir(parents=True, exist_ok=True)
     build_library(force=force, verbose=verbose)
     built = []
-    for name, source in CLI_SOURCES.items():
+    for name, (source, needs_lib) in CLI_SOURCES.items():
         out = BIN_DIR / name
         src = CSRC / source
-        if not force and out.exists() and out.stat().st_mtime >= max(src.stat().st_mtime, LIB_PATH.stat().st_mtime):
+        newest = max(_newest_source_mtime(), LIB_PATH.stat().st_mtime if needs_lib else 0.0)
+        if not force and out.exists() and out.stat().st_mtime >= newest:
             built.append(out)
             continue
-        cmd = [
-            nvcc_path(), *COMMON_FLAGS, f"-DCREDIT_CLI_WORKLOAD_{name.upper()}=1", "-o", str(out), str(src),
-            f"-L{LIB_DIR}", "-lcredit_b200", "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN/../lib",
-        ]
+        cmd = [nvcc_path(), *COMMON_FLAGS, "-o", str(out), str(src)]
+        if needs_lib:
+            cmd += [f"-L{LIB_DIR}", "-lcredit_b200", "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN/../lib"]
         _run(cmd, verbose)
         built.append(out)
     return built

@@ -16,6 +16,31 @@
 namespace credit {
 
 // ---------------------------------------------------------------------------
+// optional timeline probe (development builds only, -DCREDIT_TRACE): two threads
+// of one CTA record (point, iteration, clock) triples
+// ---------------------------------------------------------------------------
+#ifdef CREDIT_TRACE
+constexpr int kTraceCapacity = 8192;
+static __device__ long long g_trace[2][kTraceCapacity][3];
+static __device__ int g_trace_count[2];
+__device__ __forceinline__ void trace_point(int id, int it) {
+    if (blockIdx.x != 0) return;
+    const int who = threadIdx.x == 0 ? 0 : (threadIdx.x == 96 ? 1 : -1);
+    if (who < 0) return;
+    const int n = g_trace_count[who];
+    if (n < kTraceCapacity) {
+        g_trace[who][n][0] = id;
+        g_trace[who][n][1] = it;
+        g_trace[who][n][2] = clock64();
+        g_trace_count[who] = n + 1;
+    }
+}
+#define CREDIT_TRACE_POINT(id, it) ::credit::trace_point((id), (it))
+#else
+#define CREDIT_TRACE_POINT(id, it) ((void)0)
+#endif
+
+// ---------------------------------------------------------------------------
 // addressing
 // ---------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -99,16 +124,18 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t byt
                  : "memory");
 }
 
+// One try: may suspend the thread (without issuing) for up to about a microsecond
+// while the phase is still pending.
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t done;
     asm volatile(
         "{\n\t"
         ".reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t"
         "}"
         : "=r"(done)
-        : "r"(bar), "r"(parity)
+        : "r"(bar), "r"(parity), "r"(1000u)
         : "memory");
     return done != 0;
 }

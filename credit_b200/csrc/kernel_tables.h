@@ -8,11 +8,13 @@
 namespace credit {
 
 // vpt > 0 selects the register-resident kernel with that many 16-byte vectors per
-// thread; vpt == 0 the generic shared-memory kernel (aligned or scalar).
-const void* rmsnorm_kernel_for(int dtype, int threads, int vpt, bool aligned);
-const void* layernorm_fwd_kernel_for(int dtype, int threads, int vpt, bool aligned);
-const void* layernorm_bwd_kernel_for(int dtype, int threads, int vpt, bool aligned, bool has_stats,
-                                     bool grads);
+// thread (full: every thread of every CTA owns exactly vpt vectors, so the kernel
+// carries no bounds checks); vpt == 0 the generic shared-memory kernel (aligned
+// or scalar).
+const void* rmsnorm_kernel_for(int dtype, int threads, int vpt, bool full, bool aligned);
+const void* layernorm_fwd_kernel_for(int dtype, int threads, int vpt, bool full, bool aligned);
+const void* layernorm_bwd_kernel_for(int dtype, int threads, int vpt, bool full, bool aligned,
+                                     bool has_stats, bool grads);
 const void* row_reduce_kernel_for(int load_path, int threads, bool aligned);
 
 // Column sums of LayerNorm backward for shapes outside the register path, and

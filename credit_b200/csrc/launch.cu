@@ -262,17 +262,18 @@ int check_opts(const credit_launch_opts* o, credit_launch_opts* out) {
 const void* workload_func(int workload, int dtype, const credit_plan_info& p, bool want_grads) {
     const bool al = p.aligned != 0;
     const int vpt = p.vectors_per_thread;
+    const bool full = p.full_tiles != 0;
     switch (workload) {
         case CREDIT_WL_RMSNORM_FORWARD:
-            return rmsnorm_kernel_for(dtype, p.threads, vpt, al);
+            return rmsnorm_kernel_for(dtype, p.threads, vpt, full, al);
         case CREDIT_WL_ROW_REDUCE:
             return row_reduce_kernel_for(p.load_path, p.threads, al);
         case CREDIT_WL_LAYERNORM_FORWARD:
-            return layernorm_fwd_kernel_for(dtype, p.threads, vpt, al);
+            return layernorm_fwd_kernel_for(dtype, p.threads, vpt, full, al);
         case CREDIT_WL_LAYERNORM_BACKWARD:
-            return layernorm_bwd_kernel_for(dtype, p.threads, vpt, al, false, false);
+            return layernorm_bwd_kernel_for(dtype, p.threads, vpt, full, al, false, false);
         case CREDIT_WL_LAYERNORM_BACKWARD_STATS:
-            return layernorm_bwd_kernel_for(dtype, p.threads, vpt, al, true, want_grads);
+            return layernorm_bwd_kernel_for(dtype, p.threads, vpt, full, al, true, want_grads);
         default:
             return nullptr;
     }
@@ -411,6 +412,7 @@ int plan_static(int workload, const Shape& s, int dtype, const credit_launch_opt
         if (vpt <= max_vpt) {
             p->threads = threads;
             p->vectors_per_thread = vpt;
+            p->full_tiles = (vpt * threads == nvec && 1ll * p->slice_elems * cluster == s.cols) ? 1 : 0;
         }
     }
 

@@ -9,19 +9,24 @@
 // Thread t owns vectors t, t+THREADS, ... of the slice for every row its cluster
 // handles, so gamma/beta (and the running dgamma/dbeta sums) for those columns
 // stay in registers for the whole kernel, and a ring stage is free again as soon
-// as its vectors are in registers: the refill for the row `stages` steps ahead
-// is issued before the statistics are even exchanged.
+// as its vectors are in registers.
 //
-// The exchange uses no cluster barrier and no fence. Every CTA owns two
+// The exchange uses no cluster barrier and no fence. Every CTA owns four
 // mbarriers (one per slot buffer); warp 0 pushes the CTA's partials into the
 // slot of every CTA of the cluster with st.async, which signals the receiver's
 // mbarrier by byte count; each CTA then waits on its own mbarrier only. (A
 // barrier.cluster.arrive.release has to drain the thread's outstanding global
 // stores first, which serialises the previous row's output with this row's
-// statistics.) Slot buffers and mbarrier phases alternate between successive
-// exchanges; a peer can only be two exchanges ahead after it has received this
-// CTA's contribution to the exchange in between, which this CTA sends after it
-// has read the older slots, so a buffer is never overwritten while it is read.
+// statistics.)
+//
+// Rows are software-pipelined two deep: a CTA loads row i+1 into a second
+// register set, reduces it and sends its partials BEFORE it waits for the
+// exchange of row i, so the DSMEM round trip of one row is covered by the
+// arithmetic and the stores of the other. Slot buffer and mbarrier of row i are
+// number i mod 4: a peer can run ahead of this CTA by at most three exchanges
+// (its exchange i+4 needs this CTA's contribution to i+2, which this CTA sends
+// only after it has read the slots of row i), so four buffers are never
+// overwritten while they are read.
 //
 // Same arithmetic as the reference's cluster_bwd_staged_kernel family
 // (src/workloads/layernorm_backward.cu:376-438), re-designed for sm_100a.
@@ -32,20 +37,14 @@
 
 namespace credit {
 
+constexpr int kExchangeBuffers = 4;
+
 template <int K>
 struct alignas(16) ExchangeScratch {
-    uint64_t bar[2];                          // one mbarrier per slot buffer
-    float warp_part[K][kMaxWarpsPerCta];
-    float slot[2][K][kMaxClusterSize];        // [buffer][partial][source rank]
-};
-
-struct ExchangeCursor {
-    uint32_t buf;
-    uint32_t phase;
-    __device__ __forceinline__ void advance() {
-        buf ^= 1u;
-        if (buf == 0u) phase ^= 1u;
-    }
+    uint64_t bar[kExchangeBuffers];                      // one mbarrier per slot buffer
+    float warp_part[2][K][kMaxWarpsPerCta];              // double-buffered by row parity
+    float slot[kExchangeBuffers][K][kMaxClusterSize];    // [buffer][partial][source rank]
+    float result[2][K];                                  // row totals, written by warp 0
 };
 
 __device__ __forceinline__ void st_async_f32(uint32_t remote_addr, float v, uint32_t remote_bar) {
@@ -57,101 +56,151 @@ __device__ __forceinline__ void st_async_f32(uint32_t remote_addr, float v, uint
 
 // Step 1 (all threads): warp sums into shared memory. Follow with __syncthreads().
 template <int K>
-__device__ __forceinline__ void exchange_local(float (&v)[K], ExchangeScratch<K>& s) {
+__device__ __forceinline__ void exchange_local(float (&v)[K], ExchangeScratch<K>& s, int it) {
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
 #pragma unroll
     for (int k = 0; k < K; ++k) v[k] = warp_sum(v[k]);
     if (lane == 0) {
 #pragma unroll
-        for (int k = 0; k < K; ++k) s.warp_part[k][warp] = v[k];
+        for (int k = 0; k < K; ++k) s.warp_part[it & 1][k][warp] = v[k];
     }
 }
 
 // Step 2 (warp 0, after the __syncthreads): CTA totals in every lane of warp 0.
 template <int K, int THREADS>
-__device__ __forceinline__ void exchange_fold(ExchangeScratch<K>& s, float (&total)[K]) {
+__device__ __forceinline__ void exchange_fold(ExchangeScratch<K>& s, int it, float (&total)[K]) {
     constexpr int kWarps = THREADS / 32;
     const int lane = threadIdx.x & 31;
 #pragma unroll
     for (int k = 0; k < K; ++k) {
-        const float t = lane < kWarps ? s.warp_part[k][lane] : 0.0f;
+        const float t = lane < kWarps ? s.warp_part[it & 1][k][lane] : 0.0f;
         total[k] = warp_sum(t);
     }
 }
 
-// Step 3 (warp 0): arm the local mbarrier for P*K floats and send this CTA's K
-// values to slot[buf][k][rank] of every CTA of the cluster.
+// Step 3 (warp 0): arm the local mbarrier of exchange `it` for P*K floats and send
+// this CTA's K values to slot[it % 4][k][rank] of every CTA of the cluster.
 template <int K>
-__device__ __forceinline__ void exchange_push(const float (&vals)[K], ExchangeScratch<K>& s,
-                                              const ExchangeCursor& cur, uint32_t rank,
-                                              uint32_t nranks) {
+__device__ __forceinline__ void exchange_push(const float (&vals)[K], ExchangeScratch<K>& s, int it,
+                                              uint32_t rank, uint32_t nranks) {
     const uint32_t lane = threadIdx.x & 31;
-    const uint32_t bar = smem_u32(&s.bar[cur.buf]);
+    const int buf = it & (kExchangeBuffers - 1);
+    const uint32_t bar = smem_u32(&s.bar[buf]);
     if (lane == 0) mbar_arrive_expect_tx(bar, nranks * K * static_cast<uint32_t>(sizeof(float)));
     if (lane < nranks) {
         const uint32_t remote_bar = map_to_rank(bar, lane);
 #pragma unroll
         for (int k = 0; k < K; ++k)
-            st_async_f32(map_to_rank(smem_u32(&s.slot[cur.buf][k][rank]), lane), vals[k], remote_bar);
+            st_async_f32(map_to_rank(smem_u32(&s.slot[buf][k][rank]), lane), vals[k], remote_bar);
     }
 }
 
-// Step 4 (all threads): wait until all P contributions have landed here.
-template <int K>
-__device__ __forceinline__ void exchange_wait(ExchangeScratch<K>& s, const ExchangeCursor& cur,
-                                              int* status) {
-    mbar_wait_bounded(smem_u32(&s.bar[cur.buf]), cur.phase, status);
+// Step 4: warp 0 alone waits until all P contributions of exchange `it` have
+// landed (the other warps block at the __syncthreads instead of spinning on the
+// mbarrier, which would take issue slots from the warps that still compute),
+// folds the P slots with `fold_slots` and leaves K row-level values in
+// result[it & 1]; after the __syncthreads every thread reads them.
+// `fold_slots(lane_vals, out)` runs in every lane of warp 0: lane r < P holds
+// slot[.][k][r] in lane_vals[k], other lanes hold zeros; it writes out[k] (valid in
+// lane 0 at least).
+template <int K, typename Fold>
+__device__ __forceinline__ void exchange_finish(ExchangeScratch<K>& s, int it, uint32_t nranks,
+                                                int* status, float (&row)[K], Fold fold_slots) {
+    if (threadIdx.x < 32) {
+        const int buf = it & (kExchangeBuffers - 1);
+        const uint32_t phase = (static_cast<uint32_t>(it) / kExchangeBuffers) & 1u;
+        CREDIT_TRACE_POINT(20, it);
+        mbar_wait_bounded(smem_u32(&s.bar[buf]), phase, status);
+        CREDIT_TRACE_POINT(21, it);
+        float vals[K], out[K];
+#pragma unroll
+        for (int k = 0; k < K; ++k) vals[k] = threadIdx.x < nranks ? s.slot[buf][k][threadIdx.x] : 0.0f;
+        fold_slots(vals, out);
+        if (threadIdx.x == 0) {
+#pragma unroll
+            for (int k = 0; k < K; ++k) s.result[it & 1][k] = out[k];
+        }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < K; ++k) row[k] = s.result[it & 1][k];
 }
 
-// Control block of the register-path kernels.
+// The plain fold: sum over ranks.
+template <int K>
+struct SumSlots {
+    __device__ __forceinline__ void operator()(const float (&vals)[K], float (&out)[K]) const {
+#pragma unroll
+        for (int k = 0; k < K; ++k) out[k] = warp_sum(vals[k]);
+    }
+};
+
+// Control block of the register-path kernels: ring barriers and up to two
+// exchange streams (the second only for kernels with two dependent reductions).
 template <int K>
 struct alignas(16) RegControl {
     uint64_t full[kMaxStages];
     ExchangeScratch<K> ex;
+    ExchangeScratch<K> ex2;
 };
+static_assert(sizeof(RegControl<2>) <= kControlBytes, "control block overflows its reservation");
 
+// A 16-byte vector of row elements as packed fp32 pairs, so that the elementwise
+// arithmetic can use the two-wide fp32 instructions of sm_100
+// (fma/add/mul.rn.f32x2 through __ffma2_rn, __fadd2_rn, __fmul2_rn): half the
+// issue slots of scalar fp32 for the same work.
 template <typename T>
-struct RawVec;
+struct PairVec;
 template <>
-struct RawVec<float> {
+struct PairVec<float> {
     static constexpr int kElems = 4;
-    __device__ __forceinline__ static void unpack(const uint4& r, float (&o)[4]) {
-        o[0] = __uint_as_float(r.x); o[1] = __uint_as_float(r.y);
-        o[2] = __uint_as_float(r.z); o[3] = __uint_as_float(r.w);
+    static constexpr int kPairs = 2;
+    __device__ __forceinline__ static void unpack(const uint4& r, float2 (&p)[2]) {
+        p[0] = make_float2(__uint_as_float(r.x), __uint_as_float(r.y));
+        p[1] = make_float2(__uint_as_float(r.z), __uint_as_float(r.w));
     }
-    __device__ __forceinline__ static uint4 pack(const float (&v)[4]) {
-        return make_uint4(__float_as_uint(v[0]), __float_as_uint(v[1]), __float_as_uint(v[2]),
-                          __float_as_uint(v[3]));
+    __device__ __forceinline__ static uint4 pack(const float2 (&p)[2]) {
+        return make_uint4(__float_as_uint(p[0].x), __float_as_uint(p[0].y), __float_as_uint(p[1].x),
+                          __float_as_uint(p[1].y));
     }
     __device__ __forceinline__ static float first(const void* tile) {
         return *reinterpret_cast<const float*>(tile);
     }
 };
 template <>
-struct RawVec<__nv_bfloat16> {
+struct PairVec<__nv_bfloat16> {
     static constexpr int kElems = 8;
-    __device__ __forceinline__ static void unpack(const uint4& r, float (&o)[8]) {
-        RowVec<__nv_bfloat16>::unpack(r, o);
+    static constexpr int kPairs = 4;
+    __device__ __forceinline__ static float2 widen(uint32_t w) {
+        return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
     }
-    __device__ __forceinline__ static uint4 pack(const float (&v)[8]) {
-        uint32_t w[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
-            w[i] = *reinterpret_cast<const uint32_t*>(&h);
-        }
-        return make_uint4(w[0], w[1], w[2], w[3]);
+    __device__ __forceinline__ static void unpack(const uint4& r, float2 (&p)[4]) {
+        p[0] = widen(r.x); p[1] = widen(r.y); p[2] = widen(r.z); p[3] = widen(r.w);
+    }
+    __device__ __forceinline__ static uint32_t narrow(const float2& v) {
+        const __nv_bfloat162 h = __floats2bfloat162_rn(v.x, v.y);
+        return *reinterpret_cast<const uint32_t*>(&h);
+    }
+    __device__ __forceinline__ static uint4 pack(const float2 (&p)[4]) {
+        return make_uint4(narrow(p[0]), narrow(p[1]), narrow(p[2]), narrow(p[3]));
     }
     __device__ __forceinline__ static float first(const void* tile) {
         return __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(tile));
     }
 };
 
-template <int E>
-__device__ __forceinline__ void load_params(const float* p, float (&out)[E]) {
+__device__ __forceinline__ float2 splat(float v) { return make_float2(v, v); }
+
+// gamma / beta of one vector as pairs.
+template <int PAIRS>
+__device__ __forceinline__ void load_param_pairs(const float* p, float2 (&out)[PAIRS]) {
 #pragma unroll
-    for (int j = 0; j < E; j += 4) ldg_f32x4(p + j, &out[j]);
+    for (int j = 0; j < PAIRS; j += 2) {
+        const float4 v = __ldg(reinterpret_cast<const float4*>(p + 2 * j));
+        out[j] = make_float2(v.x, v.y);
+        out[j + 1] = make_float2(v.z, v.w);
+    }
 }
 
 // Barriers initialised, cluster running, ring primed.
@@ -161,8 +210,10 @@ __device__ __forceinline__ void reg_prologue(RegControl<K>& ctl, const T* const 
                                              const SliceGeom& g) {
     if (threadIdx.x == 0) {
         for (int s = 0; s < a.stages; ++s) mbar_init(smem_u32(&ctl.full[s]), 1);
-        mbar_init(smem_u32(&ctl.ex.bar[0]), 1);
-        mbar_init(smem_u32(&ctl.ex.bar[1]), 1);
+        for (int b = 0; b < kExchangeBuffers; ++b) {
+            mbar_init(smem_u32(&ctl.ex.bar[b]), 1);
+            mbar_init(smem_u32(&ctl.ex2.bar[b]), 1);
+        }
         fence_mbar_init();
     }
     __syncthreads();
@@ -176,32 +227,47 @@ __device__ __forceinline__ void reg_prologue(RegControl<K>& ctl, const T* const 
     }
 }
 
-// Called by thread 0 once every thread has copied its vectors of `stage` to
-// registers (i.e. after a __syncthreads).
+// Refill of `stage` with the row `stages` steps after `row`. Called by ONE thread
+// after the __syncthreads that follows the copy of the stage into registers: every
+// value read from the stage has been used by then, so the bulk copy cannot
+// overtake a read. The caller is a thread outside warp 0, which is busy with the
+// exchange at that moment.
 template <typename T, int NIN, int K>
 __device__ __forceinline__ void reg_refill(RegControl<K>& ctl, const T* const (&src)[NIN],
                                            unsigned char* data, int stage, int row,
                                            const StagedArgs& a, const SliceGeom& g) {
     if (g.local > 0) {
         const long long next = static_cast<long long>(row) + 1ll * a.stages * a.num_clusters;
-        if (next < a.rows) {
-            fence_proxy_async_smem();
+        if (next < a.rows)
             issue_slice_fill<T, NIN>(src, data, ctl.full, stage, static_cast<int>(next), a, g);
-        }
+    }
+}
+
+constexpr int kRefillThread = 32;   // lane 0 of warp 1
+
+// Copies this thread's vectors of a staged slice into registers. FULL: every
+// thread owns exactly VPT vectors, no bounds checks.
+template <int THREADS, int VPT, bool FULL>
+__device__ __forceinline__ void load_raw(const uint4* tile, int nvec, uint4 (&raw)[VPT]) {
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+        const int v = threadIdx.x + i * THREADS;
+        raw[i] = (FULL || v < nvec) ? tile[v] : make_uint4(0u, 0u, 0u, 0u);
     }
 }
 
 // ---------------------------------------------------------------------------
 // RMSNorm forward
 // ---------------------------------------------------------------------------
-template <typename T, int THREADS, int VPT>
+template <typename T, int THREADS, int VPT, bool FULL>
 __global__ void __launch_bounds__(THREADS)
 rmsnorm_fwd_reg_kernel(const T* __restrict__ x, const float* __restrict__ gamma, T* __restrict__ y,
                        float eps, StagedArgs a) {
     extern __shared__ __align__(1024) unsigned char smem[];
     auto& ctl = *reinterpret_cast<RegControl<1>*>(smem);
     unsigned char* data = smem + kControlBytes;
-    constexpr int E = RawVec<T>::kElems;
+    constexpr int E = PairVec<T>::kElems;
+    constexpr int PAIRS = PairVec<T>::kPairs;
 
     const uint32_t rank = cluster_cta_rank();
     const uint32_t nranks = cluster_cta_count();
@@ -209,65 +275,79 @@ rmsnorm_fwd_reg_kernel(const T* __restrict__ x, const float* __restrict__ gamma,
     const SliceGeom g = slice_geometry(a.cols, a.slice_elems, rank);
     const int nvec = g.local / E;
     const T* const src[1] = {x};
-    if (nvec > VPT * THREADS && threadIdx.x == 0) atomicOr(a.status, kStatusBadGeometry);
+    if ((FULL ? nvec != VPT * THREADS : nvec > VPT * THREADS) && threadIdx.x == 0)
+        atomicOr(a.status, kStatusBadGeometry);
 
     reg_prologue<T, 1, 1>(ctl, src, data, cluster, a, g);
 
-    float gam[VPT][E];
+    float2 gam[VPT][PAIRS];
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
         const int v = threadIdx.x + i * THREADS;
-        if (v < nvec) load_params<E>(gamma + g.start + v * E, gam[i]);
+#pragma unroll
+        for (int j = 0; j < PAIRS; ++j) gam[i][j] = splat(0.0f);
+        if (FULL || v < nvec) load_param_pairs<PAIRS>(gamma + g.start + v * E, gam[i]);
     }
 
     RingCursor ring{0, 0u};
-    ExchangeCursor exc{0u, 0u};
     const float inv_cols = 1.0f / static_cast<float>(a.cols);
+    const int my_rows = cluster < a.rows ? (a.rows - cluster + a.num_clusters - 1) / a.num_clusters : 0;
 
-    for (int row = cluster; row < a.rows; row += a.num_clusters) {
+    // first half of a row: registers <- ring, partial sum of squares, send
+    auto front = [&](uint4 (&raw)[VPT], int it) {
+        const int row = cluster + it * a.num_clusters;
         if (g.local > 0) mbar_wait_bounded(smem_u32(&ctl.full[ring.stage]), ring.parity, a.status);
-        const uint4* tile = reinterpret_cast<const uint4*>(stage_tile<T, 1>(data, ring.stage, 0, a.slice_elems));
-        uint4 raw[VPT];
+        load_raw<THREADS, VPT, FULL>(
+            reinterpret_cast<const uint4*>(stage_tile<T, 1>(data, ring.stage, 0, a.slice_elems)), nvec, raw);
+        float2 q0 = splat(0.0f), q1 = splat(0.0f);
 #pragma unroll
         for (int i = 0; i < VPT; ++i) {
-            const int v = threadIdx.x + i * THREADS;
-            raw[i] = v < nvec ? tile[v] : make_uint4(0u, 0u, 0u, 0u);
-        }
-        float part[1] = {0.0f};
+            float2 xv[PAIRS];
+            PairVec<T>::unpack(raw[i], xv);
 #pragma unroll
-        for (int i = 0; i < VPT; ++i) {
-            float xv[E];
-            RawVec<T>::unpack(raw[i], xv);
-#pragma unroll
-            for (int j = 0; j < E; ++j) part[0] = fmaf(xv[j], xv[j], part[0]);
-        }
-        exchange_local<1>(part, ctl.ex);
-        __syncthreads();
-        if (threadIdx.x == 0) reg_refill<T, 1, 1>(ctl, src, data, ring.stage, row, a, g);
-        if (threadIdx.x < 32) {
-            float total[1];
-            exchange_fold<1, THREADS>(ctl.ex, total);
-            exchange_push<1>(total, ctl.ex, exc, rank, nranks);
-        }
-        exchange_wait<1>(ctl.ex, exc, a.status);
-        float sumsq = 0.0f;
-        for (uint32_t r = 0; r < nranks; ++r) sumsq += ctl.ex.slot[exc.buf][0][r];
-        exc.advance();
-        const float scale = rsqrtf(sumsq * inv_cols + eps);
-
-        T* out = y + static_cast<size_t>(row) * a.cols + g.start;
-#pragma unroll
-        for (int i = 0; i < VPT; ++i) {
-            const int v = threadIdx.x + i * THREADS;
-            if (v < nvec) {
-                float xv[E];
-                RawVec<T>::unpack(raw[i], xv);
-#pragma unroll
-                for (int j = 0; j < E; ++j) xv[j] = xv[j] * scale * gam[i][j];
-                __stcs(reinterpret_cast<uint4*>(out) + v, RawVec<T>::pack(xv));
+            for (int j = 0; j < PAIRS; j += 2) {
+                q0 = __ffma2_rn(xv[j], xv[j], q0);
+                q1 = __ffma2_rn(xv[j + 1], xv[j + 1], q1);
             }
         }
+        float part[1] = {(q0.x + q0.y) + (q1.x + q1.y)};
+        exchange_local<1>(part, ctl.ex, it);
+        __syncthreads();
+        if (threadIdx.x == kRefillThread) reg_refill<T, 1, 1>(ctl, src, data, ring.stage, row, a, g);
+        if (threadIdx.x < 32) {
+            float total[1];
+            exchange_fold<1, THREADS>(ctl.ex, it, total);
+            exchange_push<1>(total, ctl.ex, it, rank, nranks);
+        }
         ring.advance(a.stages);
+    };
+    // second half: row statistic from the slots, outputs from registers
+    auto back = [&](const uint4 (&raw)[VPT], int it) {
+        const int row = cluster + it * a.num_clusters;
+        float sumsq[1];
+        exchange_finish<1>(ctl.ex, it, nranks, a.status, sumsq, SumSlots<1>());
+        const float2 scale = splat(rsqrtf(sumsq[0] * inv_cols + eps));
+        uint4* out = reinterpret_cast<uint4*>(y + static_cast<size_t>(row) * a.cols + g.start);
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+            const int v = threadIdx.x + i * THREADS;
+            float2 xv[PAIRS];
+            PairVec<T>::unpack(raw[i], xv);
+#pragma unroll
+            for (int j = 0; j < PAIRS; ++j) xv[j] = __fmul2_rn(__fmul2_rn(xv[j], scale), gam[i][j]);
+            if (FULL || v < nvec) __stcs(out + v, PairVec<T>::pack(xv));
+        }
+    };
+
+    uint4 raw0[VPT], raw1[VPT];
+    if (my_rows > 0) front(raw0, 0);
+    for (int it = 0; it < my_rows; it += 2) {
+        if (it + 1 < my_rows) front(raw1, it + 1);
+        back(raw0, it);
+        if (it + 1 < my_rows) {
+            if (it + 2 < my_rows) front(raw0, it + 2);
+            back(raw1, it + 1);
+        }
     }
 }
 
@@ -275,26 +355,28 @@ rmsnorm_fwd_reg_kernel(const T* __restrict__ x, const float* __restrict__ gamma,
 // of the slice, accumulates sum(x-K) and sum((x-K)^2); K is within a few standard
 // deviations of the mean, so the later subtraction loses about one digit instead
 // of log10(mean^2/var). Outputs the per-thread partials.
-template <typename T, int THREADS, int VPT>
+template <typename T, int THREADS, int VPT, bool FULL>
 __device__ __forceinline__ void shifted_partials(const uint4 (&raw)[VPT], int nvec, float shift,
                                                  float& s, float& q) {
-    constexpr int E = RawVec<T>::kElems;
-    s = 0.0f;
-    q = 0.0f;
+    constexpr int PAIRS = PairVec<T>::kPairs;
+    const float2 neg_shift = splat(-shift);
+    float2 s2 = splat(0.0f), q2 = splat(0.0f);
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
         const int v = threadIdx.x + i * THREADS;
-        if (v < nvec) {
-            float xv[E];
-            RawVec<T>::unpack(raw[i], xv);
+        if (FULL || v < nvec) {
+            float2 xv[PAIRS];
+            PairVec<T>::unpack(raw[i], xv);
 #pragma unroll
-            for (int j = 0; j < E; ++j) {
-                const float d = xv[j] - shift;
-                s += d;
-                q = fmaf(d, d, q);
+            for (int j = 0; j < PAIRS; ++j) {
+                const float2 d = __fadd2_rn(xv[j], neg_shift);
+                s2 = __fadd2_rn(s2, d);
+                q2 = __ffma2_rn(d, d, q2);
             }
         }
     }
+    s = s2.x + s2.y;
+    q = q2.x + q2.y;
 }
 
 // Warp 0: CTA totals of (sum(x-K), sum((x-K)^2)) -> (slice mean, slice M2).
@@ -306,29 +388,26 @@ __device__ __forceinline__ void slice_moments(float (&tot)[2], float shift, int 
     tot[1] = m2;           // sum of squared deviations about it
 }
 
-// All threads: merge the P (mean_i, M2_i) pairs (parallel-variance formula).
-__device__ __forceinline__ void merge_moments(const float (&slot)[2][kMaxClusterSize], int cols,
-                                              int slice_elems, uint32_t nranks, float& mean,
-                                              float& var) {
-    float weighted = 0.0f;
-    for (uint32_t r = 0; r < nranks; ++r) {
-        const SliceGeom gr = slice_geometry(cols, slice_elems, r);
-        weighted += slot[0][r] * static_cast<float>(gr.local);
+// Warp 0: merge the P (mean_i, M2_i) pairs held one per lane (parallel-variance
+// formula) into (row mean, biased row variance).
+struct MergeMoments {
+    int cols;
+    int slice_elems;
+    __device__ __forceinline__ void operator()(const float (&vals)[2], float (&out)[2]) const {
+        const SliceGeom gr = slice_geometry(cols, slice_elems, threadIdx.x & 31);
+        const float n = static_cast<float>(gr.local);   // 0 for lanes past the last slice
+        const float mean = warp_sum(vals[0] * n) / static_cast<float>(cols);
+        const float d = vals[0] - mean;
+        const float m2 = warp_sum(n > 0.0f ? vals[1] + n * d * d : 0.0f);
+        out[0] = mean;
+        out[1] = m2 / static_cast<float>(cols);
     }
-    mean = weighted / static_cast<float>(cols);
-    float m2 = 0.0f;
-    for (uint32_t r = 0; r < nranks; ++r) {
-        const SliceGeom gr = slice_geometry(cols, slice_elems, r);
-        const float d = slot[0][r] - mean;
-        m2 += slot[1][r] + static_cast<float>(gr.local) * d * d;
-    }
-    var = m2 / static_cast<float>(cols);
-}
+};
 
 // ---------------------------------------------------------------------------
 // LayerNorm forward
 // ---------------------------------------------------------------------------
-template <typename T, int THREADS, int VPT>
+template <typename T, int THREADS, int VPT, bool FULL>
 __global__ void __launch_bounds__(THREADS)
 layernorm_fwd_reg_kernel(const T* __restrict__ x, const float* __restrict__ gamma,
                          const float* __restrict__ beta, T* __restrict__ y,
@@ -337,7 +416,8 @@ layernorm_fwd_reg_kernel(const T* __restrict__ x, const float* __restrict__ gamm
     extern __shared__ __align__(1024) unsigned char smem[];
     auto& ctl = *reinterpret_cast<RegControl<2>*>(smem);
     unsigned char* data = smem + kControlBytes;
-    constexpr int E = RawVec<T>::kElems;
+    constexpr int E = PairVec<T>::kElems;
+    constexpr int PAIRS = PairVec<T>::kPairs;
 
     const uint32_t rank = cluster_cta_rank();
     const uint32_t nranks = cluster_cta_count();
@@ -345,88 +425,102 @@ layernorm_fwd_reg_kernel(const T* __restrict__ x, const float* __restrict__ gamm
     const SliceGeom g = slice_geometry(a.cols, a.slice_elems, rank);
     const int nvec = g.local / E;
     const T* const src[1] = {x};
-    if (nvec > VPT * THREADS && threadIdx.x == 0) atomicOr(a.status, kStatusBadGeometry);
+    if ((FULL ? nvec != VPT * THREADS : nvec > VPT * THREADS) && threadIdx.x == 0)
+        atomicOr(a.status, kStatusBadGeometry);
 
     reg_prologue<T, 1, 2>(ctl, src, data, cluster, a, g);
 
-    float gam[VPT][E], bet[VPT][E];
+    float2 gam[VPT][PAIRS], bet[VPT][PAIRS];
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
         const int v = threadIdx.x + i * THREADS;
-        if (v < nvec) {
-            load_params<E>(gamma + g.start + v * E, gam[i]);
-            load_params<E>(beta + g.start + v * E, bet[i]);
+#pragma unroll
+        for (int j = 0; j < PAIRS; ++j) {
+            gam[i][j] = splat(0.0f);
+            bet[i][j] = splat(0.0f);
+        }
+        if (FULL || v < nvec) {
+            load_param_pairs<PAIRS>(gamma + g.start + v * E, gam[i]);
+            load_param_pairs<PAIRS>(beta + g.start + v * E, bet[i]);
         }
     }
 
     RingCursor ring{0, 0u};
-    ExchangeCursor exc{0u, 0u};
+    const int my_rows = cluster < a.rows ? (a.rows - cluster + a.num_clusters - 1) / a.num_clusters : 0;
 
-    for (int row = cluster; row < a.rows; row += a.num_clusters) {
+    auto front = [&](uint4 (&raw)[VPT], int it) {
+        const int row = cluster + it * a.num_clusters;
         if (g.local > 0) mbar_wait_bounded(smem_u32(&ctl.full[ring.stage]), ring.parity, a.status);
-        const void* tile_base = stage_tile<T, 1>(data, ring.stage, 0, a.slice_elems);
-        const uint4* tile = reinterpret_cast<const uint4*>(tile_base);
-        const float shift = g.local > 0 ? RawVec<T>::first(tile_base) : 0.0f;
-        uint4 raw[VPT];
-#pragma unroll
-        for (int i = 0; i < VPT; ++i) {
-            const int v = threadIdx.x + i * THREADS;
-            raw[i] = v < nvec ? tile[v] : make_uint4(0u, 0u, 0u, 0u);
-        }
+        const void* tile = stage_tile<T, 1>(data, ring.stage, 0, a.slice_elems);
+        const float shift = g.local > 0 ? PairVec<T>::first(tile) : 0.0f;
+        load_raw<THREADS, VPT, FULL>(reinterpret_cast<const uint4*>(tile), nvec, raw);
         float part[2];
-        shifted_partials<T, THREADS, VPT>(raw, nvec, shift, part[0], part[1]);
-        exchange_local<2>(part, ctl.ex);
+        shifted_partials<T, THREADS, VPT, FULL>(raw, nvec, shift, part[0], part[1]);
+        exchange_local<2>(part, ctl.ex, it);
         __syncthreads();
-        if (threadIdx.x == 0) reg_refill<T, 1, 2>(ctl, src, data, ring.stage, row, a, g);
+        if (threadIdx.x == kRefillThread) reg_refill<T, 1, 2>(ctl, src, data, ring.stage, row, a, g);
         if (threadIdx.x < 32) {
             float total[2];
-            exchange_fold<2, THREADS>(ctl.ex, total);
+            exchange_fold<2, THREADS>(ctl.ex, it, total);
             slice_moments(total, shift, g.local);
-            exchange_push<2>(total, ctl.ex, exc, rank, nranks);
+            exchange_push<2>(total, ctl.ex, it, rank, nranks);
         }
-        exchange_wait<2>(ctl.ex, exc, a.status);
-        float mean, var;
-        merge_moments(ctl.ex.slot[exc.buf], a.cols, a.slice_elems, nranks, mean, var);
-        exc.advance();
-        const float rstd = rsqrtf(var + eps);
+        ring.advance(a.stages);
+    };
+    auto back = [&](const uint4 (&raw)[VPT], int it) {
+        const int row = cluster + it * a.num_clusters;
+        float mv[2];
+        exchange_finish<2>(ctl.ex, it, nranks, a.status, mv, MergeMoments{a.cols, a.slice_elems});
+        const float mean = mv[0];
+        const float rstd = rsqrtf(mv[1] + eps);
         if (rank == 0 && threadIdx.x == 0) {
             mean_out[row] = mean;
             rstd_out[row] = rstd;
         }
-        const float offset = -mean * rstd;
-
-        T* out = y + static_cast<size_t>(row) * a.cols + g.start;
+        const float2 neg_mean = splat(-mean), rstd2 = splat(rstd);
+        uint4* out = reinterpret_cast<uint4*>(y + static_cast<size_t>(row) * a.cols + g.start);
 #pragma unroll
         for (int i = 0; i < VPT; ++i) {
             const int v = threadIdx.x + i * THREADS;
-            if (v < nvec) {
-                float xv[E];
-                RawVec<T>::unpack(raw[i], xv);
+            float2 xv[PAIRS];
+            PairVec<T>::unpack(raw[i], xv);
 #pragma unroll
-                for (int j = 0; j < E; ++j)
-                    xv[j] = fmaf(fmaf(xv[j], rstd, offset), gam[i][j], bet[i][j]);
-                __stcs(reinterpret_cast<uint4*>(out) + v, RawVec<T>::pack(xv));
+            for (int j = 0; j < PAIRS; ++j) {
+                const float2 xhat = __fmul2_rn(__fadd2_rn(xv[j], neg_mean), rstd2);
+                xv[j] = __ffma2_rn(xhat, gam[i][j], bet[i][j]);
             }
+            if (FULL || v < nvec) __stcs(out + v, PairVec<T>::pack(xv));
         }
-        ring.advance(a.stages);
+    };
+
+    uint4 raw0[VPT], raw1[VPT];
+    if (my_rows > 0) front(raw0, 0);
+    for (int it = 0; it < my_rows; it += 2) {
+        if (it + 1 < my_rows) front(raw1, it + 1);
+        back(raw0, it);
+        if (it + 1 < my_rows) {
+            if (it + 2 < my_rows) front(raw0, it + 2);
+            back(raw1, it + 1);
+        }
     }
 }
 
 // ---------------------------------------------------------------------------
-// LayerNorm backward
-//   xhat = (x - mean) * rstd,  g = dy * gamma
-//   dx   = (g - mean_row(g) - xhat * mean_row(g * xhat)) * rstd
-//        = fma(xhat, -rstd * mean_row(g xhat), fma(g, rstd, -rstd * mean_row(g)))
-//   dgamma[c] = sum_rows dy * xhat,  dbeta[c] = sum_rows dy           (PARAM_GRADS)
+// LayerNorm backward. With c = x - mean, xhat = c * rstd, g = dy * gamma,
+// S1 = sum_row g and S2 = sum_row g * c:
+//   dx = (g - mean_row(g) - xhat * mean_row(g * xhat)) * rstd
+//      = g * rstd + c * (-rstd^3 * S2 / N) + (-rstd * S1 / N)
+//   dgamma[col] = sum_rows dy * c * rstd,  dbeta[col] = sum_rows dy    (PARAM_GRADS)
 // HAS_STATS: mean/rstd are inputs (one exchange per row); otherwise they are
-// computed from the staged x first (two exchanges), the form of the reference
-// kernel (layernorm_backward.cu:401-437) and of dsmem_eval/workloads.py:53-61.
-// x and dy are both staged, so dy crosses HBM once (the reference reads it twice,
-// :418 and :434). Column sums live in registers and are written at the end to
-// `partials` laid out [num_clusters][2][cols]; a finishing kernel adds the
-// clusters in a fixed order (deterministic, no atomics).
+// computed from the staged x first (two dependent exchanges per row, each covered
+// by work on the neighbouring row), the form of the reference kernel
+// (layernorm_backward.cu:401-437) and of dsmem_eval/workloads.py:53-61. x and dy
+// are both staged, so dy crosses HBM once (the reference reads it twice, :418 and
+// :434). Column sums live in registers and are written at the end to `partials`
+// laid out [num_clusters][2][cols]; a finishing kernel adds the clusters in a
+// fixed order (deterministic, no atomics).
 // ---------------------------------------------------------------------------
-template <typename T, int THREADS, int VPT, bool HAS_STATS, bool PARAM_GRADS>
+template <typename T, int THREADS, int VPT, bool FULL, bool HAS_STATS, bool PARAM_GRADS>
 __global__ void __launch_bounds__(THREADS)
 layernorm_bwd_reg_kernel(const T* __restrict__ x, const T* __restrict__ dy,
                          const float* __restrict__ gamma, const float* __restrict__ mean_in,
@@ -435,7 +529,8 @@ layernorm_bwd_reg_kernel(const T* __restrict__ x, const T* __restrict__ dy,
     extern __shared__ __align__(1024) unsigned char smem[];
     auto& ctl = *reinterpret_cast<RegControl<2>*>(smem);
     unsigned char* data = smem + kControlBytes;
-    constexpr int E = RawVec<T>::kElems;
+    constexpr int E = PairVec<T>::kElems;
+    constexpr int PAIRS = PairVec<T>::kPairs;
 
     const uint32_t rank = cluster_cta_rank();
     const uint32_t nranks = cluster_cta_count();
@@ -443,123 +538,157 @@ layernorm_bwd_reg_kernel(const T* __restrict__ x, const T* __restrict__ dy,
     const SliceGeom g = slice_geometry(a.cols, a.slice_elems, rank);
     const int nvec = g.local / E;
     const T* const src[2] = {x, dy};
-    if (nvec > VPT * THREADS && threadIdx.x == 0) atomicOr(a.status, kStatusBadGeometry);
+    if ((FULL ? nvec != VPT * THREADS : nvec > VPT * THREADS) && threadIdx.x == 0)
+        atomicOr(a.status, kStatusBadGeometry);
 
     reg_prologue<T, 2, 2>(ctl, src, data, cluster, a, g);
 
-    float gam[VPT][E];
-    float dgam[PARAM_GRADS ? VPT : 1][E];
-    float dbet[PARAM_GRADS ? VPT : 1][E];
+    float2 gam[VPT][PAIRS];
+    float2 dgam[PARAM_GRADS ? VPT : 1][PAIRS];
+    float2 dbet[PARAM_GRADS ? VPT : 1][PAIRS];
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
         const int v = threadIdx.x + i * THREADS;
 #pragma unroll
-        for (int j = 0; j < E; ++j) gam[i][j] = 0.0f;
-        if (v < nvec) load_params<E>(gamma + g.start + v * E, gam[i]);
+        for (int j = 0; j < PAIRS; ++j) gam[i][j] = splat(0.0f);
+        if (FULL || v < nvec) load_param_pairs<PAIRS>(gamma + g.start + v * E, gam[i]);
         if (PARAM_GRADS) {
 #pragma unroll
-            for (int j = 0; j < E; ++j) {
-                dgam[i][j] = 0.0f;
-                dbet[i][j] = 0.0f;
+            for (int j = 0; j < PAIRS; ++j) {
+                dgam[i][j] = splat(0.0f);
+                dbet[i][j] = splat(0.0f);
             }
         }
     }
 
     RingCursor ring{0, 0u};
-    ExchangeCursor exc{0u, 0u};
     const float inv_cols = 1.0f / static_cast<float>(a.cols);
+    const int my_rows = cluster < a.rows ? (a.rows - cluster + a.num_clusters - 1) / a.num_clusters : 0;
 
-    for (int row = cluster; row < a.rows; row += a.num_clusters) {
-        float mean = 0.0f, rstd = 0.0f;
+    struct RowRegs {
+        uint4 x[VPT];
+        uint4 dy[VPT];
+        float mean;
+        float rstd;
+    };
+
+    // per-thread partials of S1 = sum g and S2 = sum g * (x - mean)
+    auto sums_of_g = [&](const RowRegs& r, float (&part)[2]) {
+        const float2 neg_mean = splat(-r.mean);
+        float2 s1 = splat(0.0f), s2 = splat(0.0f);
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+            float2 xv[PAIRS], dv[PAIRS];
+            PairVec<T>::unpack(r.x[i], xv);
+            PairVec<T>::unpack(r.dy[i], dv);
+#pragma unroll
+            for (int j = 0; j < PAIRS; ++j) {
+                const float2 gg = __fmul2_rn(dv[j], gam[i][j]);   // 0 past the slice: dy = gamma = 0
+                s1 = __fadd2_rn(s1, gg);
+                s2 = __ffma2_rn(gg, __fadd2_rn(xv[j], neg_mean), s2);
+            }
+        }
+        part[0] = s1.x + s1.y;
+        part[1] = s2.x + s2.y;
+    };
+    // registers <- ring; then either the statistics exchange (stats recomputed) or
+    // straight the exchange of S1, S2 (stats given)
+    auto front = [&](RowRegs& r, int it) {
+        const int row = cluster + it * a.num_clusters;
+        CREDIT_TRACE_POINT(1, it);
         if (HAS_STATS) {
-            mean = __ldg(mean_in + row);
-            rstd = __ldg(rstd_in + row);
+            r.mean = __ldg(mean_in + row);
+            r.rstd = __ldg(rstd_in + row);
         }
         if (g.local > 0) mbar_wait_bounded(smem_u32(&ctl.full[ring.stage]), ring.parity, a.status);
-        const void* x_base = stage_tile<T, 2>(data, ring.stage, 0, a.slice_elems);
-        const uint4* xt = reinterpret_cast<const uint4*>(x_base);
-        const uint4* dyt = reinterpret_cast<const uint4*>(stage_tile<T, 2>(data, ring.stage, 1, a.slice_elems));
-        uint4 xraw[VPT], dyraw[VPT];
-#pragma unroll
-        for (int i = 0; i < VPT; ++i) {
-            const int v = threadIdx.x + i * THREADS;
-            xraw[i] = v < nvec ? xt[v] : make_uint4(0u, 0u, 0u, 0u);
-            dyraw[i] = v < nvec ? dyt[v] : make_uint4(0u, 0u, 0u, 0u);
+        CREDIT_TRACE_POINT(2, it);
+        const void* x_tile = stage_tile<T, 2>(data, ring.stage, 0, a.slice_elems);
+        load_raw<THREADS, VPT, FULL>(reinterpret_cast<const uint4*>(x_tile), nvec, r.x);
+        load_raw<THREADS, VPT, FULL>(
+            reinterpret_cast<const uint4*>(stage_tile<T, 2>(data, ring.stage, 1, a.slice_elems)), nvec, r.dy);
+        float part[2];
+        float shift = 0.0f;
+        if (HAS_STATS) {
+            sums_of_g(r, part);
+        } else {
+            shift = g.local > 0 ? PairVec<T>::first(x_tile) : 0.0f;
+            shifted_partials<T, THREADS, VPT, FULL>(r.x, nvec, shift, part[0], part[1]);
         }
-        bool stage_released = false;
-        if (!HAS_STATS) {
-            const float shift = g.local > 0 ? RawVec<T>::first(x_base) : 0.0f;
-            float sp[2];
-            shifted_partials<T, THREADS, VPT>(xraw, nvec, shift, sp[0], sp[1]);
-            exchange_local<2>(sp, ctl.ex);
-            __syncthreads();
-            if (threadIdx.x == 0) reg_refill<T, 2, 2>(ctl, src, data, ring.stage, row, a, g);
-            stage_released = true;
-            if (threadIdx.x < 32) {
-                float total[2];
-                exchange_fold<2, THREADS>(ctl.ex, total);
-                slice_moments(total, shift, g.local);
-                exchange_push<2>(total, ctl.ex, exc, rank, nranks);
-            }
-            exchange_wait<2>(ctl.ex, exc, a.status);
-            float var;
-            merge_moments(ctl.ex.slot[exc.buf], a.cols, a.slice_elems, nranks, mean, var);
-            exc.advance();
-            rstd = rsqrtf(var + eps);
-        }
-        const float offset = -mean * rstd;
-
-        // xhat and g for this thread's columns stay in registers for the dx pass
-        float xh[VPT][E], gg[VPT][E];
-        float part[2] = {0.0f, 0.0f};
-#pragma unroll
-        for (int i = 0; i < VPT; ++i) {
-            float xv[E], dv[E];
-            RawVec<T>::unpack(xraw[i], xv);
-            RawVec<T>::unpack(dyraw[i], dv);
-#pragma unroll
-            for (int j = 0; j < E; ++j) {
-                xh[i][j] = fmaf(xv[j], rstd, offset);
-                gg[i][j] = dv[j] * gam[i][j];     // 0 for vectors past the slice (dy = gamma = 0)
-                part[0] += gg[i][j];
-                part[1] = fmaf(gg[i][j], xh[i][j], part[1]);
-                if (PARAM_GRADS) {
-                    dgam[i][j] = fmaf(dv[j], xh[i][j], dgam[i][j]);
-                    dbet[i][j] += dv[j];
-                }
-            }
-        }
-        exchange_local<2>(part, ctl.ex);
+        CREDIT_TRACE_POINT(3, it);
+        exchange_local<2>(part, ctl.ex, it);
+        CREDIT_TRACE_POINT(4, it);
         __syncthreads();
-        if (!stage_released && threadIdx.x == 0)
-            reg_refill<T, 2, 2>(ctl, src, data, ring.stage, row, a, g);
+        CREDIT_TRACE_POINT(5, it);
+        if (threadIdx.x == kRefillThread) reg_refill<T, 2, 2>(ctl, src, data, ring.stage, row, a, g);
         if (threadIdx.x < 32) {
             float total[2];
-            exchange_fold<2, THREADS>(ctl.ex, total);
-            exchange_push<2>(total, ctl.ex, exc, rank, nranks);
+            exchange_fold<2, THREADS>(ctl.ex, it, total);
+            if (!HAS_STATS) slice_moments(total, shift, g.local);
+            exchange_push<2>(total, ctl.ex, it, rank, nranks);
         }
-        exchange_wait<2>(ctl.ex, exc, a.status);
-        float sum_g = 0.0f, sum_gx = 0.0f;
-        for (uint32_t r = 0; r < nranks; ++r) {
-            sum_g += ctl.ex.slot[exc.buf][0][r];
-            sum_gx += ctl.ex.slot[exc.buf][1][r];
+        CREDIT_TRACE_POINT(6, it);
+        ring.advance(a.stages);
+    };
+    // stats recomputed only: finish the statistics, start the exchange of S1, S2
+    auto middle = [&](RowRegs& r, int it) {
+        float mv[2];
+        exchange_finish<2>(ctl.ex, it, nranks, a.status, mv, MergeMoments{a.cols, a.slice_elems});
+        r.mean = mv[0];
+        r.rstd = rsqrtf(mv[1] + eps);
+        float part[2];
+        sums_of_g(r, part);
+        exchange_local<2>(part, ctl.ex2, it);
+        __syncthreads();
+        if (threadIdx.x < 32) {
+            float total[2];
+            exchange_fold<2, THREADS>(ctl.ex2, it, total);
+            exchange_push<2>(total, ctl.ex2, it, rank, nranks);
         }
-        exc.advance();
-        const float c1 = -rstd * (sum_g * inv_cols);
-        const float c2 = -rstd * (sum_gx * inv_cols);
-
-        T* out = dx + static_cast<size_t>(row) * a.cols + g.start;
+    };
+    auto back = [&](const RowRegs& r, int it) {
+        const int row = cluster + it * a.num_clusters;
+        ExchangeScratch<2>& ex = HAS_STATS ? ctl.ex : ctl.ex2;
+        float sums[2];
+        CREDIT_TRACE_POINT(7, it);
+        exchange_finish<2>(ex, it, nranks, a.status, sums, SumSlots<2>());
+        CREDIT_TRACE_POINT(8, it);
+        const float2 neg_mean = splat(-r.mean), rstd2 = splat(r.rstd);
+        const float2 ca = splat(-r.rstd * r.rstd * r.rstd * (sums[1] * inv_cols));
+        const float2 cb = splat(-r.rstd * (sums[0] * inv_cols));
+        uint4* out = reinterpret_cast<uint4*>(dx + static_cast<size_t>(row) * a.cols + g.start);
 #pragma unroll
         for (int i = 0; i < VPT; ++i) {
             const int v = threadIdx.x + i * THREADS;
-            if (v < nvec) {
-                float o[E];
+            float2 xv[PAIRS], dv[PAIRS], o[PAIRS];
+            PairVec<T>::unpack(r.x[i], xv);
+            PairVec<T>::unpack(r.dy[i], dv);
 #pragma unroll
-                for (int j = 0; j < E; ++j) o[j] = fmaf(xh[i][j], c2, fmaf(gg[i][j], rstd, c1));
-                __stcs(reinterpret_cast<uint4*>(out) + v, RawVec<T>::pack(o));
+            for (int j = 0; j < PAIRS; ++j) {
+                const float2 c = __fadd2_rn(xv[j], neg_mean);
+                const float2 gg = __fmul2_rn(dv[j], gam[i][j]);
+                o[j] = __ffma2_rn(c, ca, __ffma2_rn(gg, rstd2, cb));
+                if (PARAM_GRADS) {
+                    dgam[i][j] = __ffma2_rn(__fmul2_rn(dv[j], c), rstd2, dgam[i][j]);   // dy = 0 past the slice
+                    dbet[i][j] = __fadd2_rn(dbet[i][j], dv[j]);
+                }
             }
+            if (FULL || v < nvec) __stcs(out + v, PairVec<T>::pack(o));
         }
-        ring.advance(a.stages);
+        CREDIT_TRACE_POINT(9, it);
+    };
+
+    RowRegs r0, r1;
+    r0.mean = r0.rstd = r1.mean = r1.rstd = 0.0f;
+    if (my_rows > 0) front(r0, 0);
+    for (int it = 0; it < my_rows; it += 2) {
+        if (!HAS_STATS) middle(r0, it);
+        if (it + 1 < my_rows) front(r1, it + 1);
+        back(r0, it);
+        if (it + 1 < my_rows) {
+            if (!HAS_STATS) middle(r1, it + 1);
+            if (it + 2 < my_rows) front(r0, it + 2);
+            back(r1, it + 1);
+        }
     }
 
     if (PARAM_GRADS) {
@@ -568,13 +697,13 @@ layernorm_bwd_reg_kernel(const T* __restrict__ x, const T* __restrict__ dy,
 #pragma unroll
         for (int i = 0; i < VPT; ++i) {
             const int v = threadIdx.x + i * THREADS;
-            if (v < nvec) {
+            if (FULL || v < nvec) {
 #pragma unroll
-                for (int j = 0; j < E; j += 4) {
-                    *reinterpret_cast<float4*>(out_g + v * E + j) =
-                        make_float4(dgam[i][j], dgam[i][j + 1], dgam[i][j + 2], dgam[i][j + 3]);
-                    *reinterpret_cast<float4*>(out_b + v * E + j) =
-                        make_float4(dbet[i][j], dbet[i][j + 1], dbet[i][j + 2], dbet[i][j + 3]);
+                for (int j = 0; j < PAIRS; j += 2) {
+                    *reinterpret_cast<float4*>(out_g + v * E + 2 * j) =
+                        make_float4(dgam[i][j].x, dgam[i][j].y, dgam[i][j + 1].x, dgam[i][j + 1].y);
+                    *reinterpret_cast<float4*>(out_b + v * E + 2 * j) =
+                        make_float4(dbet[i][j].x, dbet[i][j].y, dbet[i][j + 1].x, dbet[i][j + 1].y);
                 }
             }
         }

@@ -73,15 +73,15 @@ const void* generic_func(int threads, bool aligned, bool has_stats) {
 
 }  // namespace
 
-const void* layernorm_bwd_reg_kernel_f32(int threads, int vpt, bool has_stats, bool grads);
-const void* layernorm_bwd_reg_kernel_bf16(int threads, int vpt, bool has_stats, bool grads);
+const void* layernorm_bwd_reg_kernel_f32(int threads, int vpt, bool full, bool has_stats, bool grads);
+const void* layernorm_bwd_reg_kernel_bf16(int threads, int vpt, bool full, bool has_stats, bool grads);
 
-const void* layernorm_bwd_kernel_for(int dtype, int threads, int vpt, bool aligned, bool has_stats,
-                                     bool grads) {
+const void* layernorm_bwd_kernel_for(int dtype, int threads, int vpt, bool full, bool aligned,
+                                     bool has_stats, bool grads) {
     const bool f32 = dtype == CREDIT_F32;
     if (vpt > 0)
-        return f32 ? layernorm_bwd_reg_kernel_f32(threads, vpt, has_stats, grads)
-                   : layernorm_bwd_reg_kernel_bf16(threads, vpt, has_stats, grads);
+        return f32 ? layernorm_bwd_reg_kernel_f32(threads, vpt, full, has_stats, grads)
+                   : layernorm_bwd_reg_kernel_bf16(threads, vpt, full, has_stats, grads);
     return f32 ? generic_func<float>(threads, aligned, has_stats)
                : generic_func<__nv_bfloat16>(threads, aligned, has_stats);
 }

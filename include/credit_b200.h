@@ -123,6 +123,7 @@ typedef struct credit_plan_info {
     int slice_elems;        /* columns per CTA */
     int chunk_elems;        /* streaming kernels: columns per ring chunk */
     int vectors_per_thread; /* register path: 16-byte vectors each thread owns; 0 = generic path */
+    int full_tiles;         /* register path: every thread owns exactly that many (no bounds checks) */
     int num_clusters;       /* clusters in the grid */
     int grid_ctas;
     int smem_bytes;         /* dynamic shared memory per CTA */

@@ -38,7 +38,7 @@ def test_ctypes_prototypes_cover_the_header():
 def test_struct_sizes_match_the_header_layout():
     assert ctypes.sizeof(_native.LaunchOpts) == 8 * 4
     assert ctypes.sizeof(_native.DeviceInfo) == 256 + 11 * 4
-    assert ctypes.sizeof(_native.PlanInfo) == 14 * 4 + 8
+    assert ctypes.sizeof(_native.PlanInfo) == 16 * 4 + 8
     fields = [n for n, _ in _native.LaunchOpts._fields_]
     header = HEADER.read_text()
     block = header[header.index("typedef struct credit_launch_opts"):header.index("} credit_launch_opts;")]
