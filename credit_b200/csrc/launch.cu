@@ -423,15 +423,18 @@ int plan_static(int workload, const Shape& s, int dtype, const credit_launch_opt
         return fail(CREDIT_ERR_INVALID_ARGUMENT,
                     "column sums are accumulated by persistent clusters; schedule must be persistent");
 
+    const int control_bytes = kControlBytes;
     int stages = o.stages;
     if (!p->aligned || p->schedule == CREDIT_SCHEDULE_ROW_PER_CLUSTER) {
         stages = 1;
     } else if (stages == 0) {
-        stages = std::max(1, std::min(4, kAutoRingBytes / stage_bytes));
-        while (stages > 1 && kControlBytes + stages * stage_bytes > max_smem) --stages;
+        // measured on B200: two stages are best when two arrays are staged, three otherwise
+        stages = p->vectors_per_thread > 0 ? (nin == 2 ? 2 : 3)
+                                           : std::max(1, std::min(4, kAutoRingBytes / stage_bytes));
+        while (stages > 1 && control_bytes + stages * stage_bytes > max_smem) --stages;
     }
     p->stages = stages;
-    p->smem_bytes = kControlBytes + stages * stage_bytes;
+    p->smem_bytes = control_bytes + stages * stage_bytes;
     if (p->smem_bytes > max_smem)
         return fail(CREDIT_ERR_UNSUPPORTED, "%d stages of %d B exceed %d B of shared memory", stages,
                     stage_bytes, max_smem);
@@ -443,7 +446,8 @@ int plan_grid(int device, const void* func, const Shape& s, credit_plan_info* p)
     int clusters = s.rows;
     if (p->schedule == CREDIT_SCHEDULE_PERSISTENT && s.rows > 0) {
         int resident = 0;
-        int rc = max_active_clusters(device, func, p->cluster_size, p->smem_bytes, p->threads, &resident);
+        int rc = max_active_clusters(device, func, p->cluster_size, p->smem_bytes, p->threads,
+                                     &resident);
         if (rc != CREDIT_OK) return rc;
         clusters = std::min(s.rows, resident);
     }

@@ -7,26 +7,34 @@
 //   registers --> partial statistics --> DSMEM exchange --> outputs from
 //   registers --128-bit stores--> HBM
 // Thread t owns vectors t, t+THREADS, ... of the slice for every row its cluster
-// handles, so gamma/beta (and the running dgamma/dbeta sums) for those columns
-// stay in registers for the whole kernel, and a ring stage is free again as soon
-// as its vectors are in registers.
+// handles, so gamma/beta (and the running dgamma/dbeta sums)
+// for those columns stay in registers for the whole kernel.
 //
-// The exchange uses no cluster barrier and no fence. Every CTA owns four
-// mbarriers (one per slot buffer); warp 0 pushes the CTA's partials into the
-// slot of every CTA of the cluster with st.async, which signals the receiver's
-// mbarrier by byte count; each CTA then waits on its own mbarrier only. (A
-// barrier.cluster.arrive.release has to drain the thread's outstanding global
-// stores first, which serialises the previous row's output with this row's
-// statistics.)
-//
-// Rows are software-pipelined two deep: a CTA loads row i+1 into a second
-// register set, reduces it and sends its partials BEFORE it waits for the
-// exchange of row i, so the DSMEM round trip of one row is covered by the
-// arithmetic and the stores of the other. Slot buffer and mbarrier of row i are
-// number i mod 4: a peer can run ahead of this CTA by at most three exchanges
-// (its exchange i+4 needs this CTA's contribution to i+2, which this CTA sends
-// only after it has read the slots of row i), so four buffers are never
-// overwritten while they are read.
+// Nothing in the row loop is a block-wide or cluster-wide barrier; every warp runs
+// its own pipeline and only meets the others through mbarriers:
+//   * one lane of the last warp keeps the ring full: before the warp starts row i
+//     it waits on empty[stage of row i-1] (one arrival per warp, made as soon as a
+//     warp has its vectors of that row in registers) and issues the bulk copies of
+//     row i-1+stages, which complete on full[stage];
+//   * every warp reduces its partials with shuffles, leaves them in shared memory
+//     and arrives on a CTA-local mbarrier; warp 0 alone waits for the W arrivals,
+//     folds the W values and pushes the CTA's totals into slot[row % 4][k][rank] of
+//     EVERY CTA of the cluster with st.async, which signals the receiver's mbarrier
+//     by byte count (no barrier.cluster, whose release has to drain the thread's
+//     outstanding global stores, and no fence);
+//   * a warp waits on its own CTA's mbarrier until all P contributions of the row
+//     have landed, folds them itself (same order in every warp of every CTA, so all
+//     agree bit for bit) and produces its outputs.
+// Rows are software-pipelined two deep per warp: the partials of row i+1 are sent
+// before the warp waits for row i, so the DSMEM round trip, the shuffle trees and
+// the shared-memory reads of one row overlap the arithmetic and stores of another
+// row and of other warps. Slot buffer and mbarrier of row i are number i mod 4: a
+// warp can only start row i+4 after it has seen row i+2 complete, i.e. after
+// every CTA has sent row i+2, which its warp 0 does after all its warps have
+// delivered their partials of row i+2, which each does after reading the slots of
+// row i; so a buffer is never overwritten while it is read, and its mbarrier is
+// never re-armed before its previous phase has completed. The same argument, one
+// level down, covers the two CTA-local partial buffers.
 //
 // Same arithmetic as the reference's cluster_bwd_staged_kernel family
 // (src/workloads/layernorm_backward.cu:376-438), re-designed for sm_100a.
@@ -40,12 +48,22 @@ namespace credit {
 constexpr int kExchangeBuffers = 4;
 
 template <int K>
-struct alignas(16) ExchangeScratch {
-    uint64_t bar[kExchangeBuffers];                      // one mbarrier per slot buffer
-    float warp_part[2][K][kMaxWarpsPerCta];              // double-buffered by row parity
+struct alignas(16) ExchangeStream {
+    uint64_t bar[kExchangeBuffers];                      // cluster level: one mbarrier per slot buffer
+    uint64_t local_bar[2];                               // CTA level: W arrivals per row
+    float warp_part[2][K][kMaxWarpsPerCta];              // [row parity][partial][warp]
     float slot[kExchangeBuffers][K][kMaxClusterSize];    // [buffer][partial][source rank]
-    float result[2][K];                                  // row totals, written by warp 0
 };
+
+// Control block at the start of dynamic shared memory (kControlBytes reserved).
+template <int K>
+struct alignas(16) AsyncControl {
+    uint64_t full[kMaxStages];    // stage has landed (1 arrival + transaction bytes)
+    uint64_t empty[kMaxStages];   // stage is in registers everywhere (W arrivals)
+    ExchangeStream<K> ex;
+    ExchangeStream<K> ex2;        // second reduction of kernels with two dependent ones
+};
+static_assert(sizeof(AsyncControl<2>) <= kControlBytes, "control block overflows its reservation");
 
 __device__ __forceinline__ void st_async_f32(uint32_t remote_addr, float v, uint32_t remote_bar) {
     asm volatile("st.async.shared::cluster.mbarrier::complete_tx::bytes.f32 [%0], %1, [%2];" ::"r"(
@@ -54,97 +72,61 @@ __device__ __forceinline__ void st_async_f32(uint32_t remote_addr, float v, uint
                  : "memory");
 }
 
-// Step 1 (all threads): warp sums into shared memory. Follow with __syncthreads().
-template <int K>
-__device__ __forceinline__ void exchange_local(float (&v)[K], ExchangeScratch<K>& s, int it) {
-    const int lane = threadIdx.x & 31;
-    const int warp = threadIdx.x >> 5;
-#pragma unroll
-    for (int k = 0; k < K; ++k) v[k] = warp_sum(v[k]);
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+// Delivers this warp's K warp-reduced partials of row `it`; warp 0 then collects
+// the W deliveries of the CTA, folds them and sends the CTA's totals to every CTA
+// of the cluster (arming its own mbarrier for the P * K floats it will receive).
+// Called by all 32 lanes of every warp; only warp 0 waits, and only for the
+// partials of this same row from its own CTA.
+template <int K, int W>
+__device__ __forceinline__ void exchange_send(const float (&vals)[K], ExchangeStream<K>& s, int it,
+                                              uint32_t rank, uint32_t nranks, int* status) {
+    const uint32_t lane = threadIdx.x & 31;
+    const uint32_t warp = threadIdx.x >> 5;
+    const int par = it & 1;
+    const uint32_t local_bar = smem_u32(&s.local_bar[par]);
     if (lane == 0) {
 #pragma unroll
-        for (int k = 0; k < K; ++k) s.warp_part[it & 1][k][warp] = v[k];
+        for (int k = 0; k < K; ++k) s.warp_part[par][k][warp] = vals[k];
+        mbar_arrive(local_bar);   // release: the partials are visible to whoever sees the phase complete
     }
-}
-
-// Step 2 (warp 0, after the __syncthreads): CTA totals in every lane of warp 0.
-template <int K, int THREADS>
-__device__ __forceinline__ void exchange_fold(ExchangeScratch<K>& s, int it, float (&total)[K]) {
-    constexpr int kWarps = THREADS / 32;
-    const int lane = threadIdx.x & 31;
-#pragma unroll
-    for (int k = 0; k < K; ++k) {
-        const float t = lane < kWarps ? s.warp_part[it & 1][k][lane] : 0.0f;
-        total[k] = warp_sum(t);
-    }
-}
-
-// Step 3 (warp 0): arm the local mbarrier of exchange `it` for P*K floats and send
-// this CTA's K values to slot[it % 4][k][rank] of every CTA of the cluster.
-template <int K>
-__device__ __forceinline__ void exchange_push(const float (&vals)[K], ExchangeScratch<K>& s, int it,
-                                              uint32_t rank, uint32_t nranks) {
-    const uint32_t lane = threadIdx.x & 31;
+    if (warp != 0) return;
+    mbar_wait_bounded(local_bar, (static_cast<uint32_t>(it) >> 1) & 1u, status);
     const int buf = it & (kExchangeBuffers - 1);
     const uint32_t bar = smem_u32(&s.bar[buf]);
     if (lane == 0) mbar_arrive_expect_tx(bar, nranks * K * static_cast<uint32_t>(sizeof(float)));
-    if (lane < nranks) {
-        const uint32_t remote_bar = map_to_rank(bar, lane);
+    const uint32_t remote_bar = map_to_rank(bar, lane < nranks ? lane : 0);
 #pragma unroll
-        for (int k = 0; k < K; ++k)
-            st_async_f32(map_to_rank(smem_u32(&s.slot[buf][k][rank]), lane), vals[k], remote_bar);
+    for (int k = 0; k < K; ++k) {
+        float t = lane < W ? s.warp_part[par][k][lane] : 0.0f;
+#pragma unroll
+        for (int offset = (W > 16 ? 16 : W / 2); offset > 0; offset >>= 1) t += __shfl_xor_sync(0xffffffffu, t, offset);
+        t = __shfl_sync(0xffffffffu, t, 0);
+        if (lane < nranks)
+            st_async_f32(map_to_rank(smem_u32(&s.slot[buf][k][rank]), lane), t, remote_bar);
     }
 }
 
-// Step 4: warp 0 alone waits until all P contributions of exchange `it` have
-// landed (the other warps block at the __syncthreads instead of spinning on the
-// mbarrier, which would take issue slots from the warps that still compute),
-// folds the P slots with `fold_slots` and leaves K row-level values in
-// result[it & 1]; after the __syncthreads every thread reads them.
-// `fold_slots(lane_vals, out)` runs in every lane of warp 0: lane r < P holds
-// slot[.][k][r] in lane_vals[k], other lanes hold zeros; it writes out[k] (valid in
-// lane 0 at least).
-template <int K, typename Fold>
-__device__ __forceinline__ void exchange_finish(ExchangeScratch<K>& s, int it, uint32_t nranks,
-                                                int* status, float (&row)[K], Fold fold_slots) {
-    if (threadIdx.x < 32) {
-        const int buf = it & (kExchangeBuffers - 1);
-        const uint32_t phase = (static_cast<uint32_t>(it) / kExchangeBuffers) & 1u;
-        CREDIT_TRACE_POINT(20, it);
-        mbar_wait_bounded(smem_u32(&s.bar[buf]), phase, status);
-        CREDIT_TRACE_POINT(21, it);
-        float vals[K], out[K];
+// Waits until the P contributions of row `it` have landed in this CTA and returns
+// the K sums over them (identical in every lane, warp and CTA).
+template <int K>
+__device__ __forceinline__ void exchange_receive(ExchangeStream<K>& s, int it, uint32_t nranks,
+                                                 int* status, float (&total)[K]) {
+    const int buf = it & (kExchangeBuffers - 1);
+    const uint32_t phase = (static_cast<uint32_t>(it) / kExchangeBuffers) & 1u;
+    mbar_wait_bounded(smem_u32(&s.bar[buf]), phase, status);
+    const uint32_t lane = threadIdx.x & 31;
 #pragma unroll
-        for (int k = 0; k < K; ++k) vals[k] = threadIdx.x < nranks ? s.slot[buf][k][threadIdx.x] : 0.0f;
-        fold_slots(vals, out);
-        if (threadIdx.x == 0) {
+    for (int k = 0; k < K; ++k) {
+        float t = lane < nranks ? s.slot[buf][k][lane] : 0.0f;
 #pragma unroll
-            for (int k = 0; k < K; ++k) s.result[it & 1][k] = out[k];
-        }
+        for (int offset = kMaxClusterSize / 2; offset > 0; offset >>= 1) t += __shfl_xor_sync(0xffffffffu, t, offset);
+        total[k] = __shfl_sync(0xffffffffu, t, 0);
     }
-    __syncthreads();
-#pragma unroll
-    for (int k = 0; k < K; ++k) row[k] = s.result[it & 1][k];
 }
-
-// The plain fold: sum over ranks.
-template <int K>
-struct SumSlots {
-    __device__ __forceinline__ void operator()(const float (&vals)[K], float (&out)[K]) const {
-#pragma unroll
-        for (int k = 0; k < K; ++k) out[k] = warp_sum(vals[k]);
-    }
-};
-
-// Control block of the register-path kernels: ring barriers and up to two
-// exchange streams (the second only for kernels with two dependent reductions).
-template <int K>
-struct alignas(16) RegControl {
-    uint64_t full[kMaxStages];
-    ExchangeScratch<K> ex;
-    ExchangeScratch<K> ex2;
-};
-static_assert(sizeof(RegControl<2>) <= kControlBytes, "control block overflows its reservation");
 
 // A 16-byte vector of row elements as packed fp32 pairs, so that the elementwise
 // arithmetic can use the two-wide fp32 instructions of sm_100
@@ -203,47 +185,59 @@ __device__ __forceinline__ void load_param_pairs(const float* p, float2 (&out)[P
     }
 }
 
-// Barriers initialised, cluster running, ring primed.
-template <typename T, int NIN, int K>
-__device__ __forceinline__ void reg_prologue(RegControl<K>& ctl, const T* const (&src)[NIN],
-                                             unsigned char* data, int cluster, const StagedArgs& a,
-                                             const SliceGeom& g) {
+// Barriers initialised and every CTA of the cluster running (a CTA's shared memory
+// may only be written by its peers once it has started). All threads call this.
+template <int K, int W>
+__device__ __forceinline__ void async_prologue(AsyncControl<K>& ctl, int stages) {
     if (threadIdx.x == 0) {
-        for (int s = 0; s < a.stages; ++s) mbar_init(smem_u32(&ctl.full[s]), 1);
+        for (int s = 0; s < stages; ++s) {
+            mbar_init(smem_u32(&ctl.full[s]), 1);
+            mbar_init(smem_u32(&ctl.empty[s]), W);
+        }
         for (int b = 0; b < kExchangeBuffers; ++b) {
             mbar_init(smem_u32(&ctl.ex.bar[b]), 1);
             mbar_init(smem_u32(&ctl.ex2.bar[b]), 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(smem_u32(&ctl.ex.local_bar[b]), W);
+            mbar_init(smem_u32(&ctl.ex2.local_bar[b]), W);
         }
         fence_mbar_init();
     }
     __syncthreads();
     cluster_sync_all();
-    if (threadIdx.x == 0 && g.local > 0) {
-        for (int s = 0; s < a.stages; ++s) {
-            const long long row = static_cast<long long>(cluster) + 1ll * s * a.num_clusters;
-            if (row < a.rows)
-                issue_slice_fill<T, NIN>(src, data, ctl.full, s, static_cast<int>(row), a, g);
-        }
-    }
 }
 
-// Refill of `stage` with the row `stages` steps after `row`. Called by ONE thread
-// after the __syncthreads that follows the copy of the stage into registers: every
-// value read from the stage has been used by then, so the bulk copy cannot
-// overtake a read. The caller is a thread outside warp 0, which is busy with the
-// exchange at that moment.
+// Ring maintenance, done by lane 0 of the last warp. prime: the first `stages` rows.
+// recycle(it), called before that warp starts row `it` >= 1: the stage that held
+// row it-1 is refilled with row it-1+stages once every warp has arrived on its
+// empty barrier (its vectors are in registers and every value read has been used,
+// so the bulk copy cannot overtake a read). The warps this waits for never wait for
+// this warp's row `it`, so the wait always ends.
 template <typename T, int NIN, int K>
-__device__ __forceinline__ void reg_refill(RegControl<K>& ctl, const T* const (&src)[NIN],
-                                           unsigned char* data, int stage, int row,
-                                           const StagedArgs& a, const SliceGeom& g) {
-    if (g.local > 0) {
-        const long long next = static_cast<long long>(row) + 1ll * a.stages * a.num_clusters;
-        if (next < a.rows)
-            issue_slice_fill<T, NIN>(src, data, ctl.full, stage, static_cast<int>(next), a, g);
-    }
-}
+struct RingFiller {
+    AsyncControl<K>& ctl;
+    const T* const (&src)[NIN];
+    unsigned char* data;
+    int cluster;
+    int my_rows;
+    const StagedArgs& a;
+    const SliceGeom& g;
 
-constexpr int kRefillThread = 32;   // lane 0 of warp 1
+    __device__ __forceinline__ void prime() const {
+        if (g.local == 0) return;
+        for (int n = 0; n < a.stages && n < my_rows; ++n)
+            issue_slice_fill<T, NIN>(src, data, ctl.full, n, cluster + n * a.num_clusters, a, g);
+    }
+    __device__ __forceinline__ void recycle(int it) const {
+        const int n = it - 1 + a.stages;
+        if (g.local == 0 || n >= my_rows) return;
+        const int stage = (it - 1) % a.stages;
+        const uint32_t parity = static_cast<uint32_t>((it - 1) / a.stages) & 1u;
+        mbar_wait_bounded(smem_u32(&ctl.empty[stage]), parity, a.status);
+        issue_slice_fill<T, NIN>(src, data, ctl.full, stage, cluster + n * a.num_clusters, a, g);
+    }
+};
 
 // Copies this thread's vectors of a staged slice into registers. FULL: every
 // thread owns exactly VPT vectors, no bounds checks.
@@ -256,6 +250,31 @@ __device__ __forceinline__ void load_raw(const uint4* tile, int nvec, uint4 (&ra
     }
 }
 
+// The two-deep software pipeline every compute warp runs:
+//   front(0); { front(i+1); back(i); } ...
+// `front` ends with the row's partials on their way, `back` starts by waiting for
+// them. MIDDLE (kernels with two dependent reductions) runs between them.
+template <bool MIDDLE, typename Regs, typename Front, typename Middle, typename Back>
+__device__ __forceinline__ void pipeline_rows(int my_rows, Regs& r0, Regs& r1, Front front,
+                                              Middle middle, Back back) {
+    if (my_rows > 0) front(r0, 0);
+    for (int it = 0; it < my_rows; it += 2) {
+        if (MIDDLE) middle(r0, it);
+        if (it + 1 < my_rows) front(r1, it + 1);
+        back(r0, it);
+        if (it + 1 < my_rows) {
+            if (MIDDLE) middle(r1, it + 1);
+            if (it + 2 < my_rows) front(r0, it + 2);
+            back(r1, it + 1);
+        }
+    }
+}
+
+struct NoMiddle {
+    template <typename Regs>
+    __device__ __forceinline__ void operator()(Regs&, int) const {}
+};
+
 // ---------------------------------------------------------------------------
 // RMSNorm forward
 // ---------------------------------------------------------------------------
@@ -264,10 +283,11 @@ __global__ void __launch_bounds__(THREADS)
 rmsnorm_fwd_reg_kernel(const T* __restrict__ x, const float* __restrict__ gamma, T* __restrict__ y,
                        float eps, StagedArgs a) {
     extern __shared__ __align__(1024) unsigned char smem[];
-    auto& ctl = *reinterpret_cast<RegControl<1>*>(smem);
+    auto& ctl = *reinterpret_cast<AsyncControl<1>*>(smem);
     unsigned char* data = smem + kControlBytes;
     constexpr int E = PairVec<T>::kElems;
     constexpr int PAIRS = PairVec<T>::kPairs;
+    constexpr int W = THREADS / 32;
 
     const uint32_t rank = cluster_cta_rank();
     const uint32_t nranks = cluster_cta_count();
@@ -275,10 +295,14 @@ rmsnorm_fwd_reg_kernel(const T* __restrict__ x, const float* __restrict__ gamma,
     const SliceGeom g = slice_geometry(a.cols, a.slice_elems, rank);
     const int nvec = g.local / E;
     const T* const src[1] = {x};
+    const int my_rows = cluster < a.rows ? (a.rows - cluster + a.num_clusters - 1) / a.num_clusters : 0;
     if ((FULL ? nvec != VPT * THREADS : nvec > VPT * THREADS) && threadIdx.x == 0)
         atomicOr(a.status, kStatusBadGeometry);
 
-    reg_prologue<T, 1, 1>(ctl, src, data, cluster, a, g);
+    async_prologue<1, W>(ctl, a.stages);
+    const RingFiller<T, 1, 1> filler{ctl, src, data, cluster, my_rows, a, g};
+    const bool fills_ring = threadIdx.x == THREADS - 32;
+    if (fills_ring) filler.prime();
 
     float2 gam[VPT][PAIRS];
 #pragma unroll
@@ -291,69 +315,53 @@ rmsnorm_fwd_reg_kernel(const T* __restrict__ x, const float* __restrict__ gamma,
 
     RingCursor ring{0, 0u};
     const float inv_cols = 1.0f / static_cast<float>(a.cols);
-    const int my_rows = cluster < a.rows ? (a.rows - cluster + a.num_clusters - 1) / a.num_clusters : 0;
+    struct Regs { uint4 raw[VPT]; };
 
-    // first half of a row: registers <- ring, partial sum of squares, send
-    auto front = [&](uint4 (&raw)[VPT], int it) {
-        const int row = cluster + it * a.num_clusters;
+    auto front = [&](Regs& r, int it) {
+        if (fills_ring && it > 0) filler.recycle(it);
         if (g.local > 0) mbar_wait_bounded(smem_u32(&ctl.full[ring.stage]), ring.parity, a.status);
         load_raw<THREADS, VPT, FULL>(
-            reinterpret_cast<const uint4*>(stage_tile<T, 1>(data, ring.stage, 0, a.slice_elems)), nvec, raw);
+            reinterpret_cast<const uint4*>(stage_tile<T, 1>(data, ring.stage, 0, a.slice_elems)), nvec, r.raw);
         float2 q0 = splat(0.0f), q1 = splat(0.0f);
 #pragma unroll
         for (int i = 0; i < VPT; ++i) {
             float2 xv[PAIRS];
-            PairVec<T>::unpack(raw[i], xv);
+            PairVec<T>::unpack(r.raw[i], xv);
 #pragma unroll
             for (int j = 0; j < PAIRS; j += 2) {
                 q0 = __ffma2_rn(xv[j], xv[j], q0);
                 q1 = __ffma2_rn(xv[j + 1], xv[j + 1], q1);
             }
         }
-        float part[1] = {(q0.x + q0.y) + (q1.x + q1.y)};
-        exchange_local<1>(part, ctl.ex, it);
-        __syncthreads();
-        if (threadIdx.x == kRefillThread) reg_refill<T, 1, 1>(ctl, src, data, ring.stage, row, a, g);
-        if (threadIdx.x < 32) {
-            float total[1];
-            exchange_fold<1, THREADS>(ctl.ex, it, total);
-            exchange_push<1>(total, ctl.ex, it, rank, nranks);
-        }
+        float part[1] = {warp_sum((q0.x + q0.y) + (q1.x + q1.y))};
+        if (g.local > 0 && (threadIdx.x & 31) == 0) mbar_arrive(smem_u32(&ctl.empty[ring.stage]));
+        exchange_send<1, W>(part, ctl.ex, it, rank, nranks, a.status);
         ring.advance(a.stages);
     };
-    // second half: row statistic from the slots, outputs from registers
-    auto back = [&](const uint4 (&raw)[VPT], int it) {
+    auto back = [&](const Regs& r, int it) {
         const int row = cluster + it * a.num_clusters;
         float sumsq[1];
-        exchange_finish<1>(ctl.ex, it, nranks, a.status, sumsq, SumSlots<1>());
+        exchange_receive<1>(ctl.ex, it, nranks, a.status, sumsq);
         const float2 scale = splat(rsqrtf(sumsq[0] * inv_cols + eps));
         uint4* out = reinterpret_cast<uint4*>(y + static_cast<size_t>(row) * a.cols + g.start);
 #pragma unroll
         for (int i = 0; i < VPT; ++i) {
             const int v = threadIdx.x + i * THREADS;
             float2 xv[PAIRS];
-            PairVec<T>::unpack(raw[i], xv);
+            PairVec<T>::unpack(r.raw[i], xv);
 #pragma unroll
             for (int j = 0; j < PAIRS; ++j) xv[j] = __fmul2_rn(__fmul2_rn(xv[j], scale), gam[i][j]);
             if (FULL || v < nvec) __stcs(out + v, PairVec<T>::pack(xv));
         }
     };
-
-    uint4 raw0[VPT], raw1[VPT];
-    if (my_rows > 0) front(raw0, 0);
-    for (int it = 0; it < my_rows; it += 2) {
-        if (it + 1 < my_rows) front(raw1, it + 1);
-        back(raw0, it);
-        if (it + 1 < my_rows) {
-            if (it + 2 < my_rows) front(raw0, it + 2);
-            back(raw1, it + 1);
-        }
-    }
+    Regs r0, r1;
+    pipeline_rows<false>(my_rows, r0, r1, front, NoMiddle(), back);
 }
 
-// Shifted one-pass statistics of the slice held in `raw`: with K = first element
-// of the slice, accumulates sum(x-K) and sum((x-K)^2); K is within a few standard
-// deviations of the mean, so the later subtraction loses about one digit instead
+// Shifted one-pass statistics of the vectors held in `raw`: with K = the first
+// element of the ROW (the same K in every CTA, so the partials of all CTAs simply
+// add), accumulates sum(x-K) and sum((x-K)^2). K is within a few standard
+// deviations of the mean, so the final subtraction loses about one digit instead
 // of log10(mean^2/var). Outputs the per-thread partials.
 template <typename T, int THREADS, int VPT, bool FULL>
 __device__ __forceinline__ void shifted_partials(const uint4 (&raw)[VPT], int nvec, float shift,
@@ -379,30 +387,19 @@ __device__ __forceinline__ void shifted_partials(const uint4 (&raw)[VPT], int nv
     q = q2.x + q2.y;
 }
 
-// Warp 0: CTA totals of (sum(x-K), sum((x-K)^2)) -> (slice mean, slice M2).
-__device__ __forceinline__ void slice_moments(float (&tot)[2], float shift, int local) {
-    const float n = static_cast<float>(local > 0 ? local : 1);
-    const float ds = tot[0] / n;
-    const float m2 = fmaxf(tot[1] - tot[0] * ds, 0.0f);
-    tot[0] = shift + ds;   // slice mean
-    tot[1] = m2;           // sum of squared deviations about it
+// Row mean and biased variance from the cluster-wide sums S = sum(x-K), Q = sum((x-K)^2).
+__device__ __forceinline__ void moments_from_shifted(float S, float Q, float shift, int cols,
+                                                     float& mean, float& var) {
+    const float inv_n = 1.0f / static_cast<float>(cols);
+    const float ds = S * inv_n;
+    mean = shift + ds;
+    var = fmaxf(Q * inv_n - ds * ds, 0.0f);
 }
 
-// Warp 0: merge the P (mean_i, M2_i) pairs held one per lane (parallel-variance
-// formula) into (row mean, biased row variance).
-struct MergeMoments {
-    int cols;
-    int slice_elems;
-    __device__ __forceinline__ void operator()(const float (&vals)[2], float (&out)[2]) const {
-        const SliceGeom gr = slice_geometry(cols, slice_elems, threadIdx.x & 31);
-        const float n = static_cast<float>(gr.local);   // 0 for lanes past the last slice
-        const float mean = warp_sum(vals[0] * n) / static_cast<float>(cols);
-        const float d = vals[0] - mean;
-        const float m2 = warp_sum(n > 0.0f ? vals[1] + n * d * d : 0.0f);
-        out[0] = mean;
-        out[1] = m2 / static_cast<float>(cols);
-    }
-};
+template <typename T>
+__device__ __forceinline__ float row_first_element(const T* x, int row, int cols) {
+    return RowVec<T>::to_float(__ldg(x + static_cast<size_t>(row) * cols));
+}
 
 // ---------------------------------------------------------------------------
 // LayerNorm forward
@@ -414,10 +411,11 @@ layernorm_fwd_reg_kernel(const T* __restrict__ x, const float* __restrict__ gamm
                          float* __restrict__ mean_out, float* __restrict__ rstd_out, float eps,
                          StagedArgs a) {
     extern __shared__ __align__(1024) unsigned char smem[];
-    auto& ctl = *reinterpret_cast<RegControl<2>*>(smem);
+    auto& ctl = *reinterpret_cast<AsyncControl<2>*>(smem);
     unsigned char* data = smem + kControlBytes;
     constexpr int E = PairVec<T>::kElems;
     constexpr int PAIRS = PairVec<T>::kPairs;
+    constexpr int W = THREADS / 32;
 
     const uint32_t rank = cluster_cta_rank();
     const uint32_t nranks = cluster_cta_count();
@@ -425,10 +423,14 @@ layernorm_fwd_reg_kernel(const T* __restrict__ x, const float* __restrict__ gamm
     const SliceGeom g = slice_geometry(a.cols, a.slice_elems, rank);
     const int nvec = g.local / E;
     const T* const src[1] = {x};
+    const int my_rows = cluster < a.rows ? (a.rows - cluster + a.num_clusters - 1) / a.num_clusters : 0;
     if ((FULL ? nvec != VPT * THREADS : nvec > VPT * THREADS) && threadIdx.x == 0)
         atomicOr(a.status, kStatusBadGeometry);
 
-    reg_prologue<T, 1, 2>(ctl, src, data, cluster, a, g);
+    async_prologue<2, W>(ctl, a.stages);
+    const RingFiller<T, 1, 2> filler{ctl, src, data, cluster, my_rows, a, g};
+    const bool fills_ring = threadIdx.x == THREADS - 32;
+    if (fills_ring) filler.prime();
 
     float2 gam[VPT][PAIRS], bet[VPT][PAIRS];
 #pragma unroll
@@ -446,33 +448,32 @@ layernorm_fwd_reg_kernel(const T* __restrict__ x, const float* __restrict__ gamm
     }
 
     RingCursor ring{0, 0u};
-    const int my_rows = cluster < a.rows ? (a.rows - cluster + a.num_clusters - 1) / a.num_clusters : 0;
+    struct Regs { uint4 raw[VPT]; float shift; };
+    // the shift of the next row is fetched one step ahead so its latency is hidden
+    float next_shift = my_rows > 0 ? row_first_element(x, cluster, a.cols) : 0.0f;
 
-    auto front = [&](uint4 (&raw)[VPT], int it) {
-        const int row = cluster + it * a.num_clusters;
+    auto front = [&](Regs& r, int it) {
+        if (fills_ring && it > 0) filler.recycle(it);
+        r.shift = next_shift;
+        if (it + 1 < my_rows) next_shift = row_first_element(x, cluster + (it + 1) * a.num_clusters, a.cols);
         if (g.local > 0) mbar_wait_bounded(smem_u32(&ctl.full[ring.stage]), ring.parity, a.status);
-        const void* tile = stage_tile<T, 1>(data, ring.stage, 0, a.slice_elems);
-        const float shift = g.local > 0 ? PairVec<T>::first(tile) : 0.0f;
-        load_raw<THREADS, VPT, FULL>(reinterpret_cast<const uint4*>(tile), nvec, raw);
+        load_raw<THREADS, VPT, FULL>(
+            reinterpret_cast<const uint4*>(stage_tile<T, 1>(data, ring.stage, 0, a.slice_elems)), nvec, r.raw);
         float part[2];
-        shifted_partials<T, THREADS, VPT, FULL>(raw, nvec, shift, part[0], part[1]);
-        exchange_local<2>(part, ctl.ex, it);
-        __syncthreads();
-        if (threadIdx.x == kRefillThread) reg_refill<T, 1, 2>(ctl, src, data, ring.stage, row, a, g);
-        if (threadIdx.x < 32) {
-            float total[2];
-            exchange_fold<2, THREADS>(ctl.ex, it, total);
-            slice_moments(total, shift, g.local);
-            exchange_push<2>(total, ctl.ex, it, rank, nranks);
-        }
+        shifted_partials<T, THREADS, VPT, FULL>(r.raw, nvec, r.shift, part[0], part[1]);
+        part[0] = warp_sum(part[0]);
+        part[1] = warp_sum(part[1]);
+        if (g.local > 0 && (threadIdx.x & 31) == 0) mbar_arrive(smem_u32(&ctl.empty[ring.stage]));
+        exchange_send<2, W>(part, ctl.ex, it, rank, nranks, a.status);
         ring.advance(a.stages);
     };
-    auto back = [&](const uint4 (&raw)[VPT], int it) {
+    auto back = [&](const Regs& r, int it) {
         const int row = cluster + it * a.num_clusters;
-        float mv[2];
-        exchange_finish<2>(ctl.ex, it, nranks, a.status, mv, MergeMoments{a.cols, a.slice_elems});
-        const float mean = mv[0];
-        const float rstd = rsqrtf(mv[1] + eps);
+        float sq[2];
+        exchange_receive<2>(ctl.ex, it, nranks, a.status, sq);
+        float mean, var;
+        moments_from_shifted(sq[0], sq[1], r.shift, a.cols, mean, var);
+        const float rstd = rsqrtf(var + eps);
         if (rank == 0 && threadIdx.x == 0) {
             mean_out[row] = mean;
             rstd_out[row] = rstd;
@@ -483,7 +484,7 @@ layernorm_fwd_reg_kernel(const T* __restrict__ x, const float* __restrict__ gamm
         for (int i = 0; i < VPT; ++i) {
             const int v = threadIdx.x + i * THREADS;
             float2 xv[PAIRS];
-            PairVec<T>::unpack(raw[i], xv);
+            PairVec<T>::unpack(r.raw[i], xv);
 #pragma unroll
             for (int j = 0; j < PAIRS; ++j) {
                 const float2 xhat = __fmul2_rn(__fadd2_rn(xv[j], neg_mean), rstd2);
@@ -492,17 +493,8 @@ layernorm_fwd_reg_kernel(const T* __restrict__ x, const float* __restrict__ gamm
             if (FULL || v < nvec) __stcs(out + v, PairVec<T>::pack(xv));
         }
     };
-
-    uint4 raw0[VPT], raw1[VPT];
-    if (my_rows > 0) front(raw0, 0);
-    for (int it = 0; it < my_rows; it += 2) {
-        if (it + 1 < my_rows) front(raw1, it + 1);
-        back(raw0, it);
-        if (it + 1 < my_rows) {
-            if (it + 2 < my_rows) front(raw0, it + 2);
-            back(raw1, it + 1);
-        }
-    }
+    Regs r0, r1;
+    pipeline_rows<false>(my_rows, r0, r1, front, NoMiddle(), back);
 }
 
 // ---------------------------------------------------------------------------
@@ -527,10 +519,11 @@ layernorm_bwd_reg_kernel(const T* __restrict__ x, const T* __restrict__ dy,
                          const float* __restrict__ rstd_in, T* __restrict__ dx,
                          float* __restrict__ partials, float eps, StagedArgs a) {
     extern __shared__ __align__(1024) unsigned char smem[];
-    auto& ctl = *reinterpret_cast<RegControl<2>*>(smem);
+    auto& ctl = *reinterpret_cast<AsyncControl<2>*>(smem);
     unsigned char* data = smem + kControlBytes;
     constexpr int E = PairVec<T>::kElems;
     constexpr int PAIRS = PairVec<T>::kPairs;
+    constexpr int W = THREADS / 32;
 
     const uint32_t rank = cluster_cta_rank();
     const uint32_t nranks = cluster_cta_count();
@@ -538,10 +531,14 @@ layernorm_bwd_reg_kernel(const T* __restrict__ x, const T* __restrict__ dy,
     const SliceGeom g = slice_geometry(a.cols, a.slice_elems, rank);
     const int nvec = g.local / E;
     const T* const src[2] = {x, dy};
+    const int my_rows = cluster < a.rows ? (a.rows - cluster + a.num_clusters - 1) / a.num_clusters : 0;
     if ((FULL ? nvec != VPT * THREADS : nvec > VPT * THREADS) && threadIdx.x == 0)
         atomicOr(a.status, kStatusBadGeometry);
 
-    reg_prologue<T, 2, 2>(ctl, src, data, cluster, a, g);
+    async_prologue<2, W>(ctl, a.stages);
+    const RingFiller<T, 2, 2> filler{ctl, src, data, cluster, my_rows, a, g};
+    const bool fills_ring = threadIdx.x == THREADS - 32;
+    if (fills_ring) filler.prime();
 
     float2 gam[VPT][PAIRS];
     float2 dgam[PARAM_GRADS ? VPT : 1][PAIRS];
@@ -563,17 +560,17 @@ layernorm_bwd_reg_kernel(const T* __restrict__ x, const T* __restrict__ dy,
 
     RingCursor ring{0, 0u};
     const float inv_cols = 1.0f / static_cast<float>(a.cols);
-    const int my_rows = cluster < a.rows ? (a.rows - cluster + a.num_clusters - 1) / a.num_clusters : 0;
 
-    struct RowRegs {
+    struct Regs {
         uint4 x[VPT];
         uint4 dy[VPT];
-        float mean;
+        float mean;    // HAS_STATS: given; else the shift first, the mean after `middle`
         float rstd;
     };
+    float next_shift = (!HAS_STATS && my_rows > 0) ? row_first_element(x, cluster, a.cols) : 0.0f;
 
-    // per-thread partials of S1 = sum g and S2 = sum g * (x - mean)
-    auto sums_of_g = [&](const RowRegs& r, float (&part)[2]) {
+    // warp-reduced S1 = sum g and S2 = sum g * (x - mean) over this warp's columns
+    auto sums_of_g = [&](const Regs& r, float (&part)[2]) {
         const float2 neg_mean = splat(-r.mean);
         float2 s1 = splat(0.0f), s2 = splat(0.0f);
 #pragma unroll
@@ -588,70 +585,52 @@ layernorm_bwd_reg_kernel(const T* __restrict__ x, const T* __restrict__ dy,
                 s2 = __ffma2_rn(gg, __fadd2_rn(xv[j], neg_mean), s2);
             }
         }
-        part[0] = s1.x + s1.y;
-        part[1] = s2.x + s2.y;
+        part[0] = warp_sum(s1.x + s1.y);
+        part[1] = warp_sum(s2.x + s2.y);
     };
-    // registers <- ring; then either the statistics exchange (stats recomputed) or
-    // straight the exchange of S1, S2 (stats given)
-    auto front = [&](RowRegs& r, int it) {
+    auto front = [&](Regs& r, int it) {
         const int row = cluster + it * a.num_clusters;
-        CREDIT_TRACE_POINT(1, it);
+        if (fills_ring && it > 0) filler.recycle(it);
         if (HAS_STATS) {
             r.mean = __ldg(mean_in + row);
             r.rstd = __ldg(rstd_in + row);
+        } else {
+            r.mean = next_shift;
+            if (it + 1 < my_rows) next_shift = row_first_element(x, row + a.num_clusters, a.cols);
         }
         if (g.local > 0) mbar_wait_bounded(smem_u32(&ctl.full[ring.stage]), ring.parity, a.status);
-        CREDIT_TRACE_POINT(2, it);
-        const void* x_tile = stage_tile<T, 2>(data, ring.stage, 0, a.slice_elems);
-        load_raw<THREADS, VPT, FULL>(reinterpret_cast<const uint4*>(x_tile), nvec, r.x);
+        load_raw<THREADS, VPT, FULL>(
+            reinterpret_cast<const uint4*>(stage_tile<T, 2>(data, ring.stage, 0, a.slice_elems)), nvec, r.x);
         load_raw<THREADS, VPT, FULL>(
             reinterpret_cast<const uint4*>(stage_tile<T, 2>(data, ring.stage, 1, a.slice_elems)), nvec, r.dy);
         float part[2];
-        float shift = 0.0f;
         if (HAS_STATS) {
             sums_of_g(r, part);
         } else {
-            shift = g.local > 0 ? PairVec<T>::first(x_tile) : 0.0f;
-            shifted_partials<T, THREADS, VPT, FULL>(r.x, nvec, shift, part[0], part[1]);
+            shifted_partials<T, THREADS, VPT, FULL>(r.x, nvec, r.mean, part[0], part[1]);
+            part[0] = warp_sum(part[0]);
+            part[1] = warp_sum(part[1]);
         }
-        CREDIT_TRACE_POINT(3, it);
-        exchange_local<2>(part, ctl.ex, it);
-        CREDIT_TRACE_POINT(4, it);
-        __syncthreads();
-        CREDIT_TRACE_POINT(5, it);
-        if (threadIdx.x == kRefillThread) reg_refill<T, 2, 2>(ctl, src, data, ring.stage, row, a, g);
-        if (threadIdx.x < 32) {
-            float total[2];
-            exchange_fold<2, THREADS>(ctl.ex, it, total);
-            if (!HAS_STATS) slice_moments(total, shift, g.local);
-            exchange_push<2>(total, ctl.ex, it, rank, nranks);
-        }
-        CREDIT_TRACE_POINT(6, it);
+        if (g.local > 0 && (threadIdx.x & 31) == 0) mbar_arrive(smem_u32(&ctl.empty[ring.stage]));
+        exchange_send<2, W>(part, ctl.ex, it, rank, nranks, a.status);
         ring.advance(a.stages);
     };
     // stats recomputed only: finish the statistics, start the exchange of S1, S2
-    auto middle = [&](RowRegs& r, int it) {
-        float mv[2];
-        exchange_finish<2>(ctl.ex, it, nranks, a.status, mv, MergeMoments{a.cols, a.slice_elems});
-        r.mean = mv[0];
-        r.rstd = rsqrtf(mv[1] + eps);
+    auto middle = [&](Regs& r, int it) {
+        float sq[2];
+        exchange_receive<2>(ctl.ex, it, nranks, a.status, sq);
+        float mean, var;
+        moments_from_shifted(sq[0], sq[1], r.mean, a.cols, mean, var);
+        r.mean = mean;
+        r.rstd = rsqrtf(var + eps);
         float part[2];
         sums_of_g(r, part);
-        exchange_local<2>(part, ctl.ex2, it);
-        __syncthreads();
-        if (threadIdx.x < 32) {
-            float total[2];
-            exchange_fold<2, THREADS>(ctl.ex2, it, total);
-            exchange_push<2>(total, ctl.ex2, it, rank, nranks);
-        }
+        exchange_send<2, W>(part, ctl.ex2, it, rank, nranks, a.status);
     };
-    auto back = [&](const RowRegs& r, int it) {
+    auto back = [&](const Regs& r, int it) {
         const int row = cluster + it * a.num_clusters;
-        ExchangeScratch<2>& ex = HAS_STATS ? ctl.ex : ctl.ex2;
         float sums[2];
-        CREDIT_TRACE_POINT(7, it);
-        exchange_finish<2>(ex, it, nranks, a.status, sums, SumSlots<2>());
-        CREDIT_TRACE_POINT(8, it);
+        exchange_receive<2>(HAS_STATS ? ctl.ex : ctl.ex2, it, nranks, a.status, sums);
         const float2 neg_mean = splat(-r.mean), rstd2 = splat(r.rstd);
         const float2 ca = splat(-r.rstd * r.rstd * r.rstd * (sums[1] * inv_cols));
         const float2 cb = splat(-r.rstd * (sums[0] * inv_cols));
@@ -674,22 +653,11 @@ layernorm_bwd_reg_kernel(const T* __restrict__ x, const T* __restrict__ dy,
             }
             if (FULL || v < nvec) __stcs(out + v, PairVec<T>::pack(o));
         }
-        CREDIT_TRACE_POINT(9, it);
     };
 
-    RowRegs r0, r1;
+    Regs r0, r1;
     r0.mean = r0.rstd = r1.mean = r1.rstd = 0.0f;
-    if (my_rows > 0) front(r0, 0);
-    for (int it = 0; it < my_rows; it += 2) {
-        if (!HAS_STATS) middle(r0, it);
-        if (it + 1 < my_rows) front(r1, it + 1);
-        back(r0, it);
-        if (it + 1 < my_rows) {
-            if (!HAS_STATS) middle(r1, it + 1);
-            if (it + 2 < my_rows) front(r0, it + 2);
-            back(r1, it + 1);
-        }
-    }
+    pipeline_rows<!HAS_STATS>(my_rows, r0, r1, front, middle, back);
 
     if (PARAM_GRADS) {
         float* out_g = partials + (static_cast<size_t>(cluster) * 2 + 0) * a.cols + g.start;
