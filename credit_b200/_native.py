@@ -127,6 +127,10 @@ PROTOTYPES: dict[str, tuple] = {
     "credit_layernorm_backward_stats": (
         c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                 c_int64, c_int64, c_int, _OPTS_P, c_void_p, c_size_t, c_void_p]),
+    "credit_layernorm_backward_stats_static_capacity": (c_size_t, []),
+    "credit_layernorm_backward_stats_static": (
+        c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                c_int64, c_int64, c_int, _OPTS_P, c_void_p]),
     "credit_row_reduce_host_scratch_bytes": (c_size_t, [c_int64, c_int64]),
     "credit_row_reduce_host": (
         c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, _OPTS_P, c_void_p,

@@ -707,6 +707,65 @@ int credit_layernorm_backward_stats(const void* x, const void* dy, const float* 
 }
 
 // ---------------------------------------------------------------------------
+// LayerNorm backward with library-owned scratch
+// ---------------------------------------------------------------------------
+namespace {
+
+// Scratch for the per-cluster partial column sums of
+// credit_layernorm_backward_stats_static. It is part of the loaded library image:
+// every GPU that loads the library holds these 16 MiB until the process exits.
+constexpr size_t kStaticScratchBytes = 16u << 20;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+// Device address of g_static_scratch per device. In host code the array's name is
+// only a handle for the runtime, not something a kernel can dereference, so the
+// address is looked up once per device (with that device current) and cached.
+std::map<int, void*> g_static_scratch_ptr;
+
+int static_scratch_for_current_device(void** out) {
+    int device = 0;
+    CREDIT_CUDA_TRY(cudaGetDevice(&device));
+    std::lock_guard<std::mutex> lock(g_mutex);
+    auto it = g_static_scratch_ptr.find(device);
+    if (it == g_static_scratch_ptr.end()) {
+        void* ptr = nullptr;
+        CREDIT_CUDA_TRY(cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_static_scratch));
+        it = g_static_scratch_ptr.emplace(device, ptr).first;
+    }
+    *out = it->second;
+    return CREDIT_OK;
+}
+
+}  // namespace
+
+size_t credit_layernorm_backward_stats_static_capacity(void) { return kStaticScratchBytes; }
+
+int credit_layernorm_backward_stats_static(const void* x, const void* dy, const float* gamma,
+                                           const float* mean, const float* rstd, void* dx,
+                                           float* dgamma, float* dbeta, int64_t rows, int64_t cols,
+                                           int dtype, const credit_launch_opts* opts, void* stream) {
+    // Size first: a shape whose partial sums do not fit is refused before any pointer is used.
+    const size_t need = credit_layernorm_backward_stats_workspace_bytes(rows, cols, dtype, opts);
+    if (need == 0 && rows > 0) {
+        // the planner has already recorded why this shape or these options are unusable
+        credit_plan_info ignored;
+        return credit_plan(CREDIT_WL_LAYERNORM_BACKWARD_STATS, rows, cols, dtype, opts, &ignored);
+    }
+    if (need > kStaticScratchBytes)
+        return fail(CREDIT_ERR_WORKSPACE,
+                    "this shape needs %zu B of scratch but the built-in scratch holds %zu B; use "
+                    "credit_layernorm_backward_stats with a caller workspace",
+                    need, kStaticScratchBytes);
+    void* scratch = nullptr;
+    int rc = static_scratch_for_current_device(&scratch);
+    if (rc != CREDIT_OK) return rc;
+    // Nothing in the scratch has to start at zero: every partial sum the finishing
+    // kernel reads is written earlier in this same call.
+    return credit_layernorm_backward_stats(x, dy, gamma, mean, rstd, dx, dgamma, dbeta, rows, cols,
+                                           dtype, opts, scratch, kStaticScratchBytes, stream);
+}
+
+// ---------------------------------------------------------------------------
 // host-buffer path
 // ---------------------------------------------------------------------------
 namespace {

@@ -196,6 +196,32 @@ int credit_layernorm_backward_stats(const void* x, const void* dy, const float* 
                                     const credit_launch_opts* opts, void* workspace,
                                     size_t workspace_bytes, void* stream);
 
+/* The same computation as credit_layernorm_backward_stats for callers that cannot
+ * obtain device memory for the workspace: code running where the CUDA allocator
+ * must not be called (for example between launches of a latency-critical serving
+ * loop, where cudaMalloc would stall the device, or in a host that gives a plug-in
+ * no allocator of its own). The partial column sums go into a 16 MiB array that
+ * is built into the library image, so nothing is allocated or freed by this call
+ * or by anything it calls; credit_layernorm_backward_stats_static_capacity()
+ * returns that size. Shapes whose workspace (see
+ * credit_layernorm_backward_stats_workspace_bytes) exceeds it are refused with
+ * CREDIT_ERR_WORKSPACE and a message; inputs and outputs are still the caller's.
+ *
+ * The first call on each device looks up the array's device address
+ * (cudaGetSymbolAddress) and reads the device's properties; make that first call
+ * before any stream capture begins. All calls on a device share the one array and
+ * it keeps whatever the last call left there; no part of it needs clearing,
+ * because a call writes every partial sum it later reads. For the same reason two
+ * calls whose kernels overlap on the GPU (different streams, or different host
+ * threads) corrupt each other's column sums: run them one after another.
+ *
+ * This entry point has no counterpart in the reference. */
+size_t credit_layernorm_backward_stats_static_capacity(void);
+int credit_layernorm_backward_stats_static(const void* x, const void* dy, const float* gamma,
+                                           const float* mean, const float* rstd, void* dx,
+                                           float* dgamma, float* dbeta, int64_t rows, int64_t cols,
+                                           int dtype, const credit_launch_opts* opts, void* stream);
+
 /* Host-buffer entry point ------------------------------------------------ */
 
 /* credit_row_reduce on HOST data: x_host [rows, cols] fp32 is copied to the device
