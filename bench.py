@@ -358,6 +358,38 @@ def main() -> None:
     e2e_launches = e2e_steps * -(-ROWS // block_rows)
     del scratch
 
+    # ---- the path's only collective (N > 1): LayerNorm backward on this rank's rows,
+    # then the all-reduce of dgamma/dbeta over NVLink, timed together on the device
+    collective_result = {}
+    if world > 1 and not args.no_others:
+        from credit_b200 import sharding
+        c_rows, c_cols = 8192, 65536
+        ins = W.make_layernorm_backward_stats_inputs(c_rows, c_cols, dev, seed=rank)
+        dx = torch.empty_like(ins[0])
+        both, _, _ = sharding.allocate_param_grads(c_cols, dev)
+        ws = torch.empty(L.layernorm_backward_stats_workspace_bytes(c_rows, c_cols, ins[0].dtype),
+                         dtype=torch.uint8, device=dev)
+        for _ in range(3):
+            sharding.layernorm_backward_stats_sharded(ins, dx, both, workspace=ws)
+        torch.cuda.synchronize()
+        dist.barrier()
+        c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        c_iters = 6
+        c0.record(stream)
+        for _ in range(c_iters):
+            sharding.layernorm_backward_stats_sharded(ins, dx, both, workspace=ws)
+        c1.record(stream)
+        c1.synchronize()
+        tc = torch.tensor([c0.elapsed_time(c1) / c_iters], device=dev, dtype=torch.float64)
+        dist.all_reduce(tc, op=dist.ReduceOp.MAX)
+        collective_result["layernorm_backward_stats_sharded"] = {
+            "shape_per_gpu": [c_rows, c_cols], "dtype": "bfloat16", "ms": round(float(tc.item()), 4),
+            "rows_per_s": round(world * c_rows / float(tc.item()) * 1e3, 1),
+            "allreduce": f"dgamma/dbeta, {2 * c_cols * 4} B fp32 over NCCL, in place, same stream",
+        }
+        del ins, dx, ws
+        torch.cuda.empty_cache()
+
     sampler.stop()
     clocks = sampler.summary([(t_w0, t_w1), (t_e0, t_e1)])
 
@@ -366,7 +398,7 @@ def main() -> None:
         ms_per_launch = elapsed_ms / args.steps
         alg_bytes = W.algorithmic_bytes("row_reduce", ROWS, COLS)
         achieved = alg_bytes / (ms_per_launch * 1e-3) / 1e9
-        others = {}
+        others = dict(collective_result)
         baseline = None
         if world == 1:
             baseline = cpu_baseline()
