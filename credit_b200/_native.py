@@ -127,6 +127,11 @@ PROTOTYPES: dict[str, tuple] = {
     "credit_layernorm_backward_stats": (
         c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                 c_int64, c_int64, c_int, _OPTS_P, c_void_p, c_size_t, c_void_p]),
+    "credit_ffn_pack_weight": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_void_p]),
+    "credit_ffn_workspace_bytes": (c_size_t, [c_int64, c_int64, c_int64]),
+    "credit_ffn_forward": (
+        c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_float,
+                c_void_p, c_size_t, c_void_p]),
     "credit_layernorm_backward_stats_static_capacity": (c_size_t, []),
     "credit_layernorm_backward_stats_static": (
         c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,

@@ -32,6 +32,7 @@ LIB_SOURCES = [
     "tables_layernorm_bwd_f32.cu",
     "tables_layernorm_bwd_bf16.cu",
     "tables_row_reduce.cu",
+    "ffn_kernels.cu",
 ]
 OBJ_DIR = LIB_DIR / "obj"
 # name of the executable -> (source, links against the shared library)

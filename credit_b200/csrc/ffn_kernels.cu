@@ -1,0 +1,453 @@
+// Fused FFN for sm_100a: two bf16 GEMMs on the 5th-generation tensor cores
+// (tcgen05.mma, accumulators in tensor memory), operands staged by TMA,
+//   H = GELU(X W1)                      (erf GELU, b1 = 0)
+//   Y = RMSNorm(H W2 + X) * gamma       (row statistics over the full width d)
+// The second GEMM is launched as clusters of d / 256 CTAs along N, so one cluster
+// owns complete output rows: after the mainloop every thread holds one row of its
+// CTA's 128 x 256 accumulator tile, adds the residual, sums z^2 over its 256
+// columns, and the d / 256 per-CTA partials of each row are exchanged through
+// distributed shared memory (st.shared::cluster + one cluster barrier) before the
+// normalised row is written. The reference project has no GEMM; this file follows
+// the cluster/DSMEM reduction scheme of its row kernels
+// (src/workloads/layernorm_backward.cu:217-251) in a GEMM epilogue.
+//
+// Layout: X [m, d], H [m, h], Y [m, d] row-major bf16; weights are taken PACKED
+// K-major (W1p [h, d], W2p [d, h], i.e. transposed once by credit_ffn_pack_weight),
+// so both operands of both GEMMs are K-major tiles of 64 bf16 (128 bytes) per row,
+// the shape the 128-byte swizzle of TMA and of the MMA shared-memory descriptors
+// is made for. Every CTA loads its own tiles (no TMA multicast anywhere).
+//
+// Kernel structure (one 128 x 256 output tile per CTA, 192 threads):
+//   warp 0   : TMA producer, 4-stage ring of (A 128x64, B 256x64) tiles
+//   warp 1   : allocates 256 TMEM columns, issues tcgen05.mma, commits to mbarriers
+//   warps 2-5: epilogue, tcgen05.ld 32 lanes x 32 columns at a time
+// Every mbarrier wait is bounded; a timeout sets the device status word and the
+// kernel still releases its tensor memory.
+
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <mutex>
+
+#include "../../include/credit_b200.h"
+#include "cluster_primitives.cuh"
+#include "kernel_tables.h"
+
+namespace credit {
+namespace {
+
+constexpr int kBM = 128;
+constexpr int kBN = 256;
+constexpr int kBK = 64;                 // 64 bf16 = 128 bytes = one swizzle row
+constexpr int kStages = 4;
+constexpr int kUmmaK = 16;
+constexpr int kTmemCols = 256;
+constexpr int kATileBytes = kBM * kBK * 2;   // 16 KiB
+constexpr int kBTileBytes = kBN * kBK * 2;   // 32 KiB
+constexpr int kStageBytes = kATileBytes + kBTileBytes;
+constexpr int kFfnThreads = 192;
+constexpr int kFfnControlBytes = 1024;
+constexpr int kMaxRowClusters = 16;
+// ring + control + alignment slack + row-partial slots of the second GEMM
+constexpr int kFfnSmemBytes = kStages * kStageBytes + kFfnControlBytes + 1024 +
+                              kBM * kMaxRowClusters * static_cast<int>(sizeof(float));
+
+struct FfnControl {
+    uint64_t full[kStages];
+    uint64_t empty[kStages];
+    uint64_t tmem_full;
+    uint32_t tmem_base;
+};
+
+// ---- PTX wrappers --------------------------------------------------------------
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x,
+                                            int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::
+            "r"(dst),
+        "l"(map), "r"(bar), "r"(x), "r"(y)
+        : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(cols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before_sync() {
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after_sync() {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+
+// D[tmem] (+)= A[smem] * B[smem]; issued by one thread.
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                          uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
+        "}" ::"r"(tmem_d),
+        "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+// The mbarrier gets one arrival when every MMA issued so far by this thread is done.
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
+                 : "memory");
+}
+
+// 32 lanes x 32 consecutive fp32 columns: lane i of the warp gets row (lane base + i).
+__device__ __forceinline__ void tmem_load_32x32(uint32_t taddr, float (&v)[32]) {
+    uint32_t r[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]),
+          "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]),
+          "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]),
+          "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes
+// (64 bf16), 128-byte swizzled: 8-row groups 1024 bytes apart; version 1 (sm_100),
+// layout type 2 (SWIZZLE_128B).
+__device__ __forceinline__ uint64_t smem_desc_k_major_sw128(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((smem_addr >> 4) & 0x3fffu);
+    d |= static_cast<uint64_t>(1) << 16;                    // leading byte offset (unused with swizzle)
+    d |= static_cast<uint64_t>(1024 >> 4) << 32;            // stride between 8-row groups
+    d |= static_cast<uint64_t>(1) << 46;                    // descriptor version
+    d |= static_cast<uint64_t>(2) << 61;                    // SWIZZLE_128B
+    return d;
+}
+
+// Instruction descriptor: D = fp32, A = B = bf16, both K-major, M x N tile.
+__host__ __device__ constexpr uint32_t instr_desc(int m, int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(n >> 3) << 17) |
+           (static_cast<uint32_t>(m >> 4) << 24);
+}
+
+__device__ __forceinline__ float gelu_erf(float v) { return 0.5f * v * (1.0f + erff(v * 0.70710678118654752f)); }
+
+__device__ __forceinline__ uint4 pack8(const float* v) {
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+        w[i] = *reinterpret_cast<const uint32_t*>(&h);
+    }
+    return make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+__device__ __forceinline__ void unpack8(const uint4& r, float* o) {
+    const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        o[2 * i] = __uint_as_float(w[i] << 16);
+        o[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+}
+
+// ---- the GEMM kernel -------------------------------------------------------------
+// C tile (m_tile = blockIdx.y, n_tile = blockIdx.x) of A [M, K] x B^T with B packed [N, K].
+// NORM_EPILOGUE == false: out = GELU(acc) as bf16 [M, N].
+// NORM_EPILOGUE == true : cluster of gridDim.x CTAs along N covers whole rows;
+//                         out = (acc + residual) * rsqrt(mean_row((acc+residual)^2) + eps) * gamma.
+template <bool NORM_EPILOGUE>
+__global__ void __launch_bounds__(kFfnThreads)
+ffn_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                __nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ residual,
+                const float* __restrict__ gamma, int n_total, int k_total, float eps, int* status) {
+    extern __shared__ unsigned char smem_raw[];
+    // tiles need 1024-byte alignment for the 128-byte swizzle
+    unsigned char* smem = reinterpret_cast<unsigned char*>(
+        (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    unsigned char* tiles = smem;
+    FfnControl& ctl = *reinterpret_cast<FfnControl*>(smem + kStages * kStageBytes);
+    float* row_slots = reinterpret_cast<float*>(smem + kStages * kStageBytes + kFfnControlBytes);  // [kBM][16]
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int n_tile = blockIdx.x;
+    const int m_tile = blockIdx.y;
+    const int k_blocks = k_total / kBK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(smem_u32(&ctl.full[s]), 1);
+            mbar_init(smem_u32(&ctl.empty[s]), 1);
+        }
+        mbar_init(smem_u32(&ctl.tmem_full), 1);
+        fence_mbar_init();
+    }
+    if (warp == 1) tmem_alloc(smem_u32(&ctl.tmem_base), kTmemCols);
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = ctl.tmem_base;
+    if (NORM_EPILOGUE) cluster_sync_all();   // peers' shared memory may be written once they run
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t parity = 1;   // a fresh barrier passes a wait on the "previous" phase
+            for (int kb = 0; kb < k_blocks; ++kb) {
+                mbar_wait_bounded(smem_u32(&ctl.empty[stage]), parity, status);
+                const uint32_t bar = smem_u32(&ctl.full[stage]);
+                mbar_arrive_expect_tx(bar, kStageBytes);
+                const uint32_t a_dst = smem_u32(tiles + stage * kStageBytes);
+                tma_load_2d(a_dst, &map_a, bar, kb * kBK, m_tile * kBM);
+                tma_load_2d(a_dst + kATileBytes, &map_b, bar, kb * kBK, n_tile * kBN);
+                if (++stage == kStages) {
+                    stage = 0;
+                    parity ^= 1u;
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = instr_desc(kBM, kBN);
+            int stage = 0;
+            uint32_t parity = 0;
+            for (int kb = 0; kb < k_blocks; ++kb) {
+                mbar_wait_bounded(smem_u32(&ctl.full[stage]), parity, status);
+                tc_fence_after_sync();
+                const uint32_t a_addr = smem_u32(tiles + stage * kStageBytes);
+                const uint64_t desc_a = smem_desc_k_major_sw128(a_addr);
+                const uint64_t desc_b = smem_desc_k_major_sw128(a_addr + kATileBytes);
+#pragma unroll
+                for (int k = 0; k < kBK / kUmmaK; ++k) {
+                    // advance 16 bf16 = 32 bytes inside the swizzle row: +2 in the address field
+                    umma_bf16(tmem_base, desc_a + 2u * k, desc_b + 2u * k, idesc, (kb | k) != 0 ? 1u : 0u);
+                }
+                umma_commit(smem_u32(&ctl.empty[stage]));   // stage reusable when these MMAs are done
+                if (++stage == kStages) {
+                    stage = 0;
+                    parity ^= 1u;
+                }
+            }
+            umma_commit(smem_u32(&ctl.tmem_full));          // accumulator complete
+        }
+        __syncwarp();
+    } else {
+        // epilogue warps 2..5: warp w may touch TMEM lanes 32 * (w % 4) .. +31
+        const int quarter = warp & 3;
+        const int row_in_tile = quarter * 32 + lane;
+        const size_t row = static_cast<size_t>(m_tile) * kBM + row_in_tile;
+        const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+        mbar_wait_bounded(smem_u32(&ctl.tmem_full), 0, status);
+        tc_fence_after_sync();
+
+        if (!NORM_EPILOGUE) {
+            __nv_bfloat16* dst = out + row * n_total + static_cast<size_t>(n_tile) * kBN;
+#pragma unroll 1
+            for (int c = 0; c < kBN; c += 32) {
+                float v[32];
+                tmem_load_32x32(lane_base + c, v);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) v[i] = gelu_erf(v[i]);
+#pragma unroll
+                for (int i = 0; i < 32; i += 8) *reinterpret_cast<uint4*>(dst + c + i) = pack8(v + i);
+            }
+        } else {
+            const uint32_t rank = cluster_cta_rank();
+            const uint32_t nranks = cluster_cta_count();
+            const size_t col0 = static_cast<size_t>(n_tile) * kBN;
+            const __nv_bfloat16* res = residual + row * n_total + col0;
+            // pass 1: sum of squares of z = acc + residual over this CTA's 256 columns of the row
+            float ss = 0.0f;
+#pragma unroll 1
+            for (int c = 0; c < kBN; c += 32) {
+                float v[32];
+                tmem_load_32x32(lane_base + c, v);
+#pragma unroll
+                for (int i = 0; i < 32; i += 8) {
+                    float r8[8];
+                    unpack8(__ldg(reinterpret_cast<const uint4*>(res + c + i)), r8);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const float z = v[i + j] + r8[j];
+                        ss = fmaf(z, z, ss);
+                    }
+                }
+            }
+            // every CTA of the cluster gets every CTA's partial of every row
+            for (uint32_t p = 0; p < nranks; ++p)
+                st_cluster_f32(map_to_rank(smem_u32(&row_slots[row_in_tile * kMaxRowClusters + rank]), p), ss);
+        }
+    }
+
+    if (NORM_EPILOGUE) {
+        cluster_sync_all();   // all partials have landed everywhere (release / acquire)
+        if (warp >= 2) {
+            const int quarter = warp & 3;
+            const int row_in_tile = quarter * 32 + lane;
+            const size_t row = static_cast<size_t>(m_tile) * kBM + row_in_tile;
+            const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+            const uint32_t nranks = cluster_cta_count();
+            const size_t col0 = static_cast<size_t>(n_tile) * kBN;
+            float total = 0.0f;
+            for (uint32_t p = 0; p < nranks; ++p) total += row_slots[row_in_tile * kMaxRowClusters + p];
+            const float scale = rsqrtf(total / static_cast<float>(n_total) + eps);
+            const __nv_bfloat16* res = residual + row * n_total + col0;
+            __nv_bfloat16* dst = out + row * n_total + col0;
+            tc_fence_after_sync();
+#pragma unroll 1
+            for (int c = 0; c < kBN; c += 32) {
+                float v[32];
+                tmem_load_32x32(lane_base + c, v);
+#pragma unroll
+                for (int i = 0; i < 32; i += 8) {
+                    float r8[8], g8[8];
+                    unpack8(__ldg(reinterpret_cast<const uint4*>(res + c + i)), r8);
+                    ldg_f32x4(gamma + col0 + c + i, g8);
+                    ldg_f32x4(gamma + col0 + c + i + 4, g8 + 4);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) v[i + j] = (v[i + j] + r8[j]) * scale * g8[j];
+                    *reinterpret_cast<uint4*>(dst + c + i) = pack8(v + i);
+                }
+            }
+        }
+    }
+
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
+}
+
+// Transposes a row-major [k, n] bf16 weight into the K-major [n, k] form the GEMMs take.
+__global__ void __launch_bounds__(256)
+pack_weight_kernel(const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ packed, int k, int n) {
+    __shared__ __nv_bfloat16 tile[32][33];
+    const int n0 = blockIdx.x * 32, k0 = blockIdx.y * 32;
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;   // 32 x 8
+    for (int j = ty; j < 32; j += 8)
+        if (k0 + j < k && n0 + tx < n) tile[j][tx] = w[static_cast<size_t>(k0 + j) * n + n0 + tx];
+    __syncthreads();
+    for (int j = ty; j < 32; j += 8)
+        if (n0 + j < n && k0 + tx < k) packed[static_cast<size_t>(n0 + j) * k + k0 + tx] = tile[tx][j];
+}
+
+// ---- host side ---------------------------------------------------------------------
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                   CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                   CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    });
+    return fn;
+}
+
+// Row-major [rows, k] bf16 matrix, boxes of box_rows x 64 elements, 128-byte swizzle.
+bool make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t k, int box_rows) {
+    EncodeTiledFn fn = encode_tiled();
+    if (fn == nullptr) return false;
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(k), static_cast<cuuint64_t>(rows)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(k) * 2};
+    const cuuint32_t box[2] = {static_cast<cuuint32_t>(kBK), static_cast<cuuint32_t>(box_rows)};
+    const cuuint32_t elem_strides[2] = {1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box,
+              elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+}  // namespace
+
+const char* ffn_check_shape(int64_t m, int64_t d, int64_t h) {
+    if (m <= 0 || d <= 0 || h <= 0) return "m, d and h must be positive";
+    if (m % kBM != 0) return "m must be a multiple of 128";
+    if (d % kBN != 0 || h % kBN != 0) return "d and h must be multiples of 256";
+    if (d / kBN > kMaxRowClusters) return "d must be at most 4096 (one cluster of up to 16 CTAs spans a row)";
+    if (d % kBK != 0 || h % kBK != 0) return "d and h must be multiples of 64";
+    if (m > (1 << 24) || d > (1 << 24) || h > (1 << 24)) return "shape too large";
+    return nullptr;
+}
+
+cudaError_t launch_ffn_pack_weight(const void* w, void* packed, int k, int n, cudaStream_t stream) {
+    dim3 grid(static_cast<unsigned>((n + 31) / 32), static_cast<unsigned>((k + 31) / 32));
+    pack_weight_kernel<<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(w),
+                                                static_cast<__nv_bfloat16*>(packed), k, n);
+    return cudaGetLastError();
+}
+
+// Returns cudaSuccess, or an error; *bad_map is set when a tensor map could not be encoded.
+cudaError_t launch_ffn_forward(const void* x, const void* w1p, const void* w2p, const float* gamma, void* y,
+                               void* hidden, int m, int d, int h, float eps, int* status,
+                               cudaStream_t stream, bool* bad_map) {
+    *bad_map = false;
+    CUtensorMap map_x, map_w1, map_h, map_w2;
+    if (!make_map(&map_x, x, m, d, kBM) || !make_map(&map_w1, w1p, h, d, kBN) ||
+        !make_map(&map_h, hidden, m, h, kBM) || !make_map(&map_w2, w2p, d, h, kBN)) {
+        *bad_map = true;
+        return cudaErrorInvalidValue;
+    }
+    static std::once_flag once;
+    static cudaError_t attr_err = cudaSuccess;
+    std::call_once(once, [] {
+        attr_err = cudaFuncSetAttribute(ffn_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        kFfnSmemBytes);
+        if (attr_err == cudaSuccess)
+            attr_err = cudaFuncSetAttribute(ffn_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                            kFfnSmemBytes);
+        if (attr_err == cudaSuccess)
+            attr_err = cudaFuncSetAttribute(ffn_gemm_kernel<true>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+    });
+    if (attr_err != cudaSuccess) return attr_err;
+
+    // GEMM 1: H = GELU(X W1), tiles over (h / 256, m / 128)
+    {
+        dim3 grid(static_cast<unsigned>(h / kBN), static_cast<unsigned>(m / kBM));
+        ffn_gemm_kernel<false><<<grid, kFfnThreads, kFfnSmemBytes, stream>>>(
+            map_x, map_w1, static_cast<__nv_bfloat16*>(hidden), nullptr, nullptr, h, d, 0.0f, status);
+        cudaError_t err = cudaGetLastError();
+        if (err != cudaSuccess) return err;
+    }
+    // GEMM 2: Y = RMSNorm(H W2 + X) gamma, one cluster of d / 256 CTAs per 128 rows
+    {
+        cudaLaunchConfig_t cfg{};
+        cfg.gridDim = dim3(static_cast<unsigned>(d / kBN), static_cast<unsigned>(m / kBM));
+        cfg.blockDim = dim3(kFfnThreads);
+        cfg.dynamicSmemBytes = kFfnSmemBytes;
+        cfg.stream = stream;
+        cudaLaunchAttribute attr{};
+        attr.id = cudaLaunchAttributeClusterDimension;
+        attr.val.clusterDim.x = static_cast<unsigned>(d / kBN);
+        attr.val.clusterDim.y = 1;
+        attr.val.clusterDim.z = 1;
+        cfg.attrs = &attr;
+        cfg.numAttrs = 1;
+        __nv_bfloat16* out = static_cast<__nv_bfloat16*>(y);
+        const __nv_bfloat16* res = static_cast<const __nv_bfloat16*>(x);
+        return cudaLaunchKernelEx(&cfg, ffn_gemm_kernel<true>, map_h, map_w2, out, res, gamma, d, h, eps, status);
+    }
+}
+
+}  // namespace credit

@@ -4,6 +4,7 @@
 #pragma once
 
 #include <cuda_runtime.h>
+#include <stdint.h>
 
 namespace credit {
 
@@ -24,5 +25,13 @@ cudaError_t launch_layernorm_bwd_colsum(int dtype, const void* x, const void* dy
                                         int num_blocks, cudaStream_t stream);
 cudaError_t launch_layernorm_bwd_finish(const float* partials, float* dgamma, float* dbeta, int cols,
                                         int num_partials, cudaStream_t stream);
+
+// Fused FFN (tcgen05 GEMMs). ffn_check_shape returns nullptr or the reason the
+// shape is not supported.
+const char* ffn_check_shape(int64_t m, int64_t d, int64_t h);
+cudaError_t launch_ffn_pack_weight(const void* w, void* packed, int k, int n, cudaStream_t stream);
+cudaError_t launch_ffn_forward(const void* x, const void* w1p, const void* w2p, const float* gamma, void* y,
+                               void* hidden, int m, int d, int h, float eps, int* status,
+                               cudaStream_t stream, bool* bad_map);
 
 }  // namespace credit

@@ -163,12 +163,54 @@ def launch_layernorm_backward_stats(inputs, outputs, cluster_size: int = 0, opts
             ws_bytes, _stream_ptr()))
 
 
+def pack_ffn_weight(w: torch.Tensor) -> torch.Tensor:
+    """[k, n] bf16 row-major weight -> the K-major [n, k] form the FFN GEMMs take (done once per
+    weight, on the device)."""
+    _check_matrix("w", w, torch.bfloat16)
+    k, n = w.shape
+    packed = torch.empty((n, k), dtype=torch.bfloat16, device=w.device)
+    with torch.cuda.device(w.device):
+        N.check(N.load().credit_ffn_pack_weight(w.data_ptr(), packed.data_ptr(), k, n, _stream_ptr()))
+    return packed
+
+
+def ffn_workspace_bytes(m: int, d: int, h: int) -> int:
+    return int(N.load().credit_ffn_workspace_bytes(m, d, h))
+
+
+def launch_ffn_forward(inputs, outputs, cluster_size: int = 0, opts=None, eps: float = 1.0e-6,
+                       workspace: torch.Tensor | None = None) -> None:
+    """Y = RMSNorm(GELU(X W1) W2 + X) * gamma. inputs = (x [m, d] bf16, w1_packed [h, d],
+    w2_packed [d, h], gamma [d] fp32) with the weights from `pack_ffn_weight`. The cluster size
+    is fixed by the width (d / 256 CTAs span a row); `cluster_size` and `opts` are accepted for
+    the common launcher signature and must be left at their defaults."""
+    x, w1p, w2p, gamma = inputs
+    (y,) = outputs
+    if cluster_size or opts:
+        raise ValueError("the FFN takes no launch options: its cluster size is d / 256")
+    _check_matrix("x", x, torch.bfloat16)
+    m, d = x.shape
+    h = w1p.shape[0]
+    _check_matrix("w1_packed", w1p, torch.bfloat16, (h, d))
+    _check_matrix("w2_packed", w2p, torch.bfloat16, (d, h))
+    _check_matrix("gamma", gamma, torch.float32, (d,))
+    _check_matrix("y", y, torch.bfloat16, (m, d))
+    if workspace is None:
+        workspace = torch.empty(max(ffn_workspace_bytes(m, d, h), 16), dtype=torch.uint8, device=x.device)
+    _check_matrix("workspace", workspace, torch.uint8)
+    with torch.cuda.device(x.device):
+        N.check(N.load().credit_ffn_forward(
+            x.data_ptr(), w1p.data_ptr(), w2p.data_ptr(), gamma.data_ptr(), y.data_ptr(), m, d, h, eps,
+            workspace.data_ptr(), workspace.numel(), _stream_ptr()))
+
+
 NATIVE_LAUNCHERS = {
     "rmsnorm_forward": launch_rmsnorm_forward,
     "row_reduce": launch_row_reduce,
     "layernorm_forward": launch_layernorm_forward,
     "layernorm_backward": launch_layernorm_backward,
     "layernorm_backward_stats": launch_layernorm_backward_stats,
+    "ffn_forward": launch_ffn_forward,
 }
 
 
@@ -195,6 +237,6 @@ def allocate_outputs(name: str, inputs: tuple[torch.Tensor, ...]) -> tuple[torch
             torch.empty(cols, device=dev, dtype=torch.float32),
             torch.empty(cols, device=dev, dtype=torch.float32),
         )
-    if name in ("rmsnorm_forward", "layernorm_backward"):
+    if name in ("rmsnorm_forward", "layernorm_backward", "ffn_forward"):
         return (torch.empty_like(x),)
     raise KeyError(f"unknown workload {name!r}")

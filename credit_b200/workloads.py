@@ -134,6 +134,23 @@ def make_layernorm_inputs(rows: int, cols: int, device, seed: int | None = None)
     )
 
 
+def make_ffn_inputs(rows: int, cols: int, device, seed: int = 0, hidden: int | None = None) -> TensorTuple:
+    """x ~ N(0,1) [rows, cols]; W1 ~ N(0, 0.02) [cols, hidden]; W2 ~ N(0, 0.02) [hidden, cols], all
+    rounded to bf16; gamma ~ U(0.5, 1.5) fp32 [cols]. hidden defaults to 4 * cols. The weights are
+    returned in their natural [k, n] layout; `launchers.pack_ffn_weight` makes the K-major copies."""
+    hidden = 4 * cols if hidden is None else hidden
+    gen = _generator(device, seed)
+    x = _normal((rows, cols), 0.0, 1.0, device, gen).to(torch.bfloat16)
+    w1 = _normal((cols, hidden), 0.0, 0.02, device, gen).to(torch.bfloat16)
+    w2 = _normal((hidden, cols), 0.0, 0.02, device, gen).to(torch.bfloat16)
+    gamma = _uniform((cols,), 0.5, 1.5, device, gen)
+    return x, w1, w2, gamma
+
+
+def ffn_flops(rows: int, cols: int, hidden: int) -> int:
+    return 2 * (2 * rows * cols * hidden)
+
+
 def _elem(dtype: torch.dtype) -> int:
     return torch.empty((), dtype=dtype).element_size()
 
@@ -176,6 +193,16 @@ WORKLOADS: dict[str, WorkloadSpec] = {
         modeled_bytes_per_element=10.0, reread_bytes_per_element=4.0, staged_bytes_per_element=4,
         reductions_per_stage=(2,), atol=2.0e-2, rtol=2.0e-2,
         algorithmic_bytes=lambda r, c: 3 * r * c * 2 + 2 * r * 4 + c * 4 + 2 * c * 4,
+    ),
+    "ffn_forward": WorkloadSpec(
+        name="ffn_forward", label="Fused FFN (GEMM + GELU, GEMM + residual + RMSNorm)",
+        category="gemm",
+        rows=2048, cols=4096, dtype=torch.bfloat16, input_factory=make_ffn_inputs, eps=1.0e-6,
+        modeled_bytes_per_element=0.0, reread_bytes_per_element=0.0, staged_bytes_per_element=0,
+        reductions_per_stage=(1,), atol=2.0e-2, rtol=2.0e-2,
+        # compulsory bytes with hidden = 4 * cols: X, W1, W2, Y (the hidden activations stay on chip
+        # only in a fully fused kernel; this implementation also writes and reads them once)
+        algorithmic_bytes=lambda r, c: 2 * r * c * 2 + 2 * c * 4 * c * 2 + c * 4,
     ),
 }
 

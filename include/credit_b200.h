@@ -196,6 +196,23 @@ int credit_layernorm_backward_stats(const void* x, const void* dy, const float* 
                                     const credit_launch_opts* opts, void* workspace,
                                     size_t workspace_bytes, void* stream);
 
+/* Fused FFN, bf16 with fp32 accumulation on the tensor cores:
+ *   H = GELU(X W1)  (exact erf GELU, b1 = 0),  Y = RMSNorm(H W2 + X) * gamma.
+ * X, Y: bf16 [m, d]; gamma fp32 [d]; W1 [d, h] and W2 [h, d] are given PACKED
+ * K-major, i.e. transposed once with credit_ffn_pack_weight(w [k, n] -> packed [n, k]):
+ * w1_packed is [h, d], w2_packed is [d, h]. `workspace` (credit_ffn_workspace_bytes)
+ * holds the hidden activations. Shapes: m % 128 == 0, d % 256 == 0, d <= 4096,
+ * h % 256 == 0; anything else returns CREDIT_ERR_UNSUPPORTED. The row statistics
+ * of the RMSNorm are reduced across the CTAs of a cluster through DSMEM in the
+ * epilogue of the second GEMM. No reference kernel or function exists for this
+ * workload; the exchange follows cluster_reduce_pair
+ * (src/workloads/layernorm_backward.cu:217-251). */
+int credit_ffn_pack_weight(const void* w, void* packed, int64_t k, int64_t n, void* stream);
+size_t credit_ffn_workspace_bytes(int64_t m, int64_t d, int64_t h);
+int credit_ffn_forward(const void* x, const void* w1_packed, const void* w2_packed, const float* gamma,
+                       void* y, int64_t m, int64_t d, int64_t h, float eps, void* workspace,
+                       size_t workspace_bytes, void* stream);
+
 /* The same computation as credit_layernorm_backward_stats for callers that cannot
  * obtain device memory for the workspace: code running where the CUDA allocator
  * must not be called (for example between launches of a latency-critical serving
