@@ -33,12 +33,19 @@ LIB_SOURCES = [
     "tables_layernorm_bwd_bf16.cu",
     "tables_row_reduce.cu",
     "ffn_kernels.cu",
+    "tables_block_read.cu",
 ]
 OBJ_DIR = LIB_DIR / "obj"
 # name of the executable -> (source, links against the shared library)
 CLI_SOURCES: dict[str, tuple[str, bool]] = {
     "primitive_benchmark": ("primitive_benchmark.cu", False),
+    "cluster_control": ("cluster_control.cu", False),
+    "workload_bench": ("workload_bench.cu", True),
 }
+# workload_bench takes its workload from the name it is started under: it is
+# installed once per workload, as the reference has one executable per workload.
+WORKLOAD_BINARIES = ["layernorm_backward", "rmsnorm_forward", "row_reduce", "layernorm_forward",
+                     "layernorm_backward_stats"]
 
 
 def nvcc_path() -> str:
@@ -106,6 +113,12 @@ def build_cli(force: bool = False, verbose: bool = False) -> list[Path]:
             cmd += [f"-L{LIB_DIR}", "-lcredit_b200", "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN/../lib"]
         _run(cmd, verbose)
         built.append(out)
+    generic = BIN_DIR / "workload_bench"
+    for name in WORKLOAD_BINARIES:
+        target = BIN_DIR / name
+        if force or not target.exists() or target.stat().st_mtime < generic.stat().st_mtime:
+            shutil.copy2(generic, target)
+        built.append(target)
     return built
 
 

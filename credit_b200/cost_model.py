@@ -1,0 +1,166 @@
+"""Cluster-size cost model.
+
+Two models live here.
+
+`estimate` is the reference's profitability model ("effective-bandwidth-overlap-v2",
+`dsmem_eval/cost_model.py:62-141`) with the same inputs, outputs and arithmetic, so
+result bundles stay comparable: predicted gain = re-read traffic saved - control
+overhead - local replay - store residual - DSMEM stores, with the device constants
+taken from `DeviceProfile`.
+
+`predict_cluster_ms` is the B200 recalibration that the headline target asks for
+(predict WHICH cluster size is fastest, not only whether clusters pay off). On
+B200 the register-resident kernels are bound neither by the re-read the reference
+model counts nor by DSMEM store bandwidth; what was measured is
+
+    time(P) = max( HBM time of the compulsory bytes,
+                   rows / resident_clusters(P) * row_period(P) )
+
+where a cluster finishes one row every `row_period` = fixed latency chain (ring
+wait, shared-memory reads, shuffle trees, mbarrier exchange, stores: about 1.4 us
+per reduction stage at 1.9 GHz) + a per-element term, and `resident_clusters(P)` is
+what the driver's occupancy query returns for the kernel (GPC packing makes it far
+from sm_count / P: 15 clusters of 8 CTAs at one CTA per SM on a 148-SM part).
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import Protocol
+
+
+class WorkloadModelSpec(Protocol):
+    rows: int
+    modeled_bytes_per_element: float
+    reread_bytes_per_element: float
+    staged_bytes_per_element: int
+    partial_count: int
+
+
+MODEL_VERSION = "effective-bandwidth-overlap-v2"
+B200_MODEL_VERSION = "b200-row-period-v1"
+
+
+@dataclass(frozen=True)
+class DeviceProfile:
+    name: str
+    sm_count: int
+    clock_ghz: float
+    hbm_bandwidth_gbps: float
+    l2_capacity_bytes: int
+    l2_bandwidth_gbps: float
+    local_smem_bytes_per_cycle_cta: float
+    local_smem_store_bytes_per_cycle_cta: float
+    dsmem_store_bytes_per_cycle_cta: float
+    max_shared_bytes_per_cta: int
+
+
+@dataclass(frozen=True)
+class ModelEstimate:
+    effective_bandwidth_gbps: float
+    saved_reread_ms: float
+    control_overhead_ms: float
+    local_replay_ms: float
+    local_store_residual_ms: float
+    dsmem_store_ms: float
+    predicted_delta_ms: float
+    predicted_profitable: bool
+
+    @property
+    def saved_hbm_ms(self) -> float:
+        return self.saved_reread_ms
+
+    @property
+    def local_staging_ms(self) -> float:
+        return self.local_replay_ms + self.local_store_residual_ms
+
+
+def shared_bytes_per_cta(spec: WorkloadModelSpec, cols: int, cluster_size: int) -> int:
+    return math.ceil(cols / cluster_size) * spec.staged_bytes_per_element
+
+
+def estimate(spec: WorkloadModelSpec, cols: int, cluster_size: int, control_overhead_ms: float,
+             profile: DeviceProfile, baseline_ms: float, rows: int | None = None) -> ModelEstimate:
+    """The reference model, term by term (cost_model.py:62-141)."""
+    n_rows = spec.rows if rows is None else rows
+    if not math.isfinite(baseline_ms) or baseline_ms <= 0.0:
+        raise ValueError("baseline_ms must be finite and positive")
+    if spec.modeled_bytes_per_element <= 0.0:
+        raise ValueError("modeled_bytes_per_element must be positive")
+    cycles_to_ms = 1.0 / (profile.clock_ghz * 1.0e6)
+
+    baseline_bytes = n_rows * cols * spec.modeled_bytes_per_element
+    effective_gbps = baseline_bytes / (baseline_ms * 1.0e6)
+    saved_ms = baseline_ms * spec.reread_bytes_per_element / spec.modeled_bytes_per_element
+
+    resident = max(profile.sm_count // cluster_size, 1)
+    waves = math.ceil(n_rows / resident)
+    slice_bytes = shared_bytes_per_cta(spec, cols, cluster_size)
+
+    dsmem_ms = waves * (4.0 * (cluster_size - 1) * spec.partial_count
+                        / profile.dsmem_store_bytes_per_cycle_cta) * cycles_to_ms
+    replay_ms = waves * slice_bytes / profile.local_smem_bytes_per_cycle_cta * cycles_to_ms
+    source_bytes_per_cycle_cta = effective_gbps / (profile.clock_ghz * profile.sm_count)
+    residual_cycles = slice_bytes * max(
+        1.0 / profile.local_smem_store_bytes_per_cycle_cta - 1.0 / source_bytes_per_cycle_cta, 0.0)
+    residual_ms = waves * residual_cycles * cycles_to_ms
+    control_ms = max(control_overhead_ms, 0.0)
+    delta = saved_ms - control_ms - replay_ms - residual_ms - dsmem_ms
+    return ModelEstimate(effective_gbps, saved_ms, control_ms, replay_ms, residual_ms, dsmem_ms, delta,
+                         delta > 0.0)
+
+
+# ---------------------------------------------------------------------------
+# B200 recalibration
+# ---------------------------------------------------------------------------
+@dataclass(frozen=True)
+class B200Calibration:
+    """Constants measured on B200 (profiles/primitive_benchmark_b200.txt and the cluster-size
+    sweeps); cycles are SM cycles at `clock_ghz`."""
+    clock_ghz: float = 1.93                    # SM clock under these memory-bound kernels
+    hbm_gbps: float = 6538.6                   # copy ceiling
+    chain_cycles_per_stage: float = 2500.0     # ring wait, LDS, shuffle trees, fold, push, wait, stores
+    exchange_cycles: dict | None = None        # st.async + mbarrier all-to-all, per cluster size
+    cycles_per_element_per_thread: float = 9.0 # issue cost of one row element in one thread
+    one_shot_cycles: float = 6000.0            # cluster launch + barrier set-up + first load, per row,
+                                               # when every cluster handles a single row
+
+    def exchange(self, cluster_size: int) -> float:
+        table = self.exchange_cycles or {1: 150.0, 2: 315.0, 4: 322.0, 8: 351.0, 16: 420.0}
+        return table.get(cluster_size, 420.0)
+
+
+@dataclass(frozen=True)
+class ClusterPrediction:
+    cluster_size: int
+    hbm_ms: float
+    rows_per_cluster: int
+    row_period_us: float
+    predicted_ms: float
+
+
+def predict_cluster_ms(rows: int, cols: int, cluster_size: int, resident_clusters: int, threads: int,
+                       algorithmic_bytes: float, reduction_stages: int, persistent: bool = True,
+                       cal: B200Calibration = B200Calibration()) -> ClusterPrediction:
+    """Predicted time of one call of a register-path cluster kernel.
+    resident_clusters: clusters of this shape that are co-resident (credit_plan's num_clusters for a
+    persistent launch); threads: threads per CTA."""
+    if min(rows, cols, cluster_size, resident_clusters, threads) <= 0:
+        raise ValueError("all sizes must be positive")
+    hbm_ms = algorithmic_bytes / (cal.hbm_gbps * 1.0e6)
+    elems_per_thread = math.ceil(cols / cluster_size / threads)
+    chain = reduction_stages * (cal.chain_cycles_per_stage + cal.exchange(cluster_size))
+    period_cycles = chain + elems_per_thread * cal.cycles_per_element_per_thread
+    if not persistent:
+        period_cycles += cal.one_shot_cycles
+    rows_per_cluster = math.ceil(rows / resident_clusters)
+    row_period_us = period_cycles / (cal.clock_ghz * 1.0e3)
+    latency_ms = rows_per_cluster * row_period_us * 1.0e-3
+    return ClusterPrediction(cluster_size, hbm_ms, rows_per_cluster, row_period_us, max(hbm_ms, latency_ms))
+
+
+def best_cluster_size(predictions: list[ClusterPrediction]) -> int:
+    """Cluster size with the lowest predicted time; ties go to the smaller cluster."""
+    if not predictions:
+        raise ValueError("no predictions")
+    return min(predictions, key=lambda p: (round(p.predicted_ms, 6), p.cluster_size)).cluster_size

@@ -17,6 +17,8 @@ const void* layernorm_fwd_kernel_for(int dtype, int threads, int vpt, bool full,
 const void* layernorm_bwd_kernel_for(int dtype, int threads, int vpt, bool full, bool aligned,
                                      bool has_stats, bool grads);
 const void* row_reduce_kernel_for(int load_path, int threads, bool aligned);
+// One CTA of 512 threads per row, nothing staged (CREDIT_VARIANT_BLOCK_READ).
+const void* block_read_kernel_for(int workload, int dtype, bool aligned);
 
 // Column sums of LayerNorm backward for shapes outside the register path, and
 // the finishing reduction over per-cluster (or per-row-block) partials.

@@ -261,6 +261,7 @@ int check_opts(const credit_launch_opts* o, credit_launch_opts* out) {
 // ---------------------------------------------------------------------------
 const void* workload_func(int workload, int dtype, const credit_plan_info& p, bool want_grads) {
     const bool al = p.aligned != 0;
+    if (p.variant == CREDIT_VARIANT_BLOCK_READ) return block_read_kernel_for(workload, dtype, al);
     const int vpt = p.vectors_per_thread;
     const bool full = p.full_tiles != 0;
     switch (workload) {
@@ -315,8 +316,9 @@ int plan_static(int workload, const Shape& s, int dtype, const credit_launch_opt
         return fail(CREDIT_ERR_INVALID_ARGUMENT, "unknown workload %d", workload);
     if (workload == CREDIT_WL_ROW_REDUCE && dtype != CREDIT_F32)
         return fail(CREDIT_ERR_INVALID_ARGUMENT, "row_reduce takes fp32 input");
-    if (o.variant == CREDIT_VARIANT_BLOCK_READ)
-        return fail(CREDIT_ERR_UNSUPPORTED, "the block_read variant is not built for this workload");
+    if (o.variant == CREDIT_VARIANT_BLOCK_READ && workload == CREDIT_WL_ROW_REDUCE)
+        return fail(CREDIT_ERR_UNSUPPORTED,
+                    "row_reduce reads its input once in every variant; use cluster_size 1 for the block form");
     if (!dev.cluster_launch && o.cluster_size > 1)
         return fail(CREDIT_ERR_UNSUPPORTED, "device cannot launch thread-block clusters");
 
@@ -360,6 +362,18 @@ int plan_static(int workload, const Shape& s, int dtype, const credit_launch_opt
             p->smem_bytes = 0;
             p->schedule = o.schedule ? o.schedule : CREDIT_SCHEDULE_ROW_PER_CLUSTER;
         }
+        return CREDIT_OK;
+    }
+
+    if (o.variant == CREDIT_VARIANT_BLOCK_READ) {
+        // one CTA of 512 threads per row, no shared-memory staging, no cluster
+        p->cluster_size = 1;
+        p->threads = 512;
+        p->schedule = CREDIT_SCHEDULE_ROW_PER_CLUSTER;
+        p->load_path = CREDIT_LOAD_LDG;
+        p->slice_elems = round_up(s.cols, 64);
+        p->stages = 0;
+        p->smem_bytes = 0;
         return CREDIT_OK;
     }
 
@@ -577,6 +591,10 @@ int credit_rmsnorm_forward(const void* x, const float* gamma, void* y, int64_t r
                      aligned16(x) && aligned16(gamma) && aligned16(y), false, &r);
     if (rc != CREDIT_OK) return rc;
     if (r.shape.rows == 0) return CREDIT_OK;
+    if (r.plan.variant == CREDIT_VARIANT_BLOCK_READ) {
+        void* args[] = {&x, &gamma, &y, &eps, &r.shape.rows, &r.shape.cols};
+        return launch_cluster_kernel(make_launch(r, stream), args);
+    }
     StagedArgs a = staged_args(r);
     void* args[] = {&x, &gamma, &y, &eps, &a};
     return launch_cluster_kernel(make_launch(r, stream), args);
@@ -614,6 +632,10 @@ int credit_layernorm_forward(const void* x, const float* gamma, const float* bet
                      aligned16(x) && aligned16(gamma) && aligned16(beta) && aligned16(y), false, &r);
     if (rc != CREDIT_OK) return rc;
     if (r.shape.rows == 0) return CREDIT_OK;
+    if (r.plan.variant == CREDIT_VARIANT_BLOCK_READ) {
+        void* args[] = {&x, &gamma, &beta, &y, &mean, &rstd, &eps, &r.shape.rows, &r.shape.cols};
+        return launch_cluster_kernel(make_launch(r, stream), args);
+    }
     StagedArgs a = staged_args(r);
     void* args[] = {&x, &gamma, &beta, &y, &mean, &rstd, &eps, &a};
     return launch_cluster_kernel(make_launch(r, stream), args);
@@ -629,9 +651,13 @@ int credit_layernorm_backward(const void* x, const void* dy, const float* gamma,
                      aligned16(x) && aligned16(dy) && aligned16(gamma) && aligned16(dx), false, &r);
     if (rc != CREDIT_OK) return rc;
     if (r.shape.rows == 0) return CREDIT_OK;
-    StagedArgs a = staged_args(r);
     const float* no_stats = nullptr;
     float* no_partials = nullptr;
+    if (r.plan.variant == CREDIT_VARIANT_BLOCK_READ) {
+        void* args[] = {&x, &dy, &gamma, &no_stats, &no_stats, &dx, &eps, &r.shape.rows, &r.shape.cols};
+        return launch_cluster_kernel(make_launch(r, stream), args);
+    }
+    StagedArgs a = staged_args(r);
     if (r.plan.vectors_per_thread > 0) {
         void* args[] = {&x, &dy, &gamma, &no_stats, &no_stats, &dx, &no_partials, &eps, &a};
         return launch_cluster_kernel(make_launch(r, stream), args);
@@ -686,7 +712,10 @@ int credit_layernorm_backward_stats(const void* x, const void* dy, const float* 
     StagedArgs a = staged_args(r);
     float* partials = static_cast<float*>(workspace);
     float eps = 0.0f;
-    if (r.plan.vectors_per_thread > 0) {
+    if (r.plan.variant == CREDIT_VARIANT_BLOCK_READ) {
+        void* args[] = {&x, &dy, &gamma, &mean, &rstd, &dx, &eps, &r.shape.rows, &r.shape.cols};
+        rc = launch_cluster_kernel(make_launch(r, stream), args);
+    } else if (r.plan.vectors_per_thread > 0) {
         void* args[] = {&x, &dy, &gamma, &mean, &rstd, &dx, &partials, &eps, &a};
         rc = launch_cluster_kernel(make_launch(r, stream), args);
     } else {

@@ -403,6 +403,26 @@ def test_generic_path_persistent_ring():
     close(y, O.rmsnorm_forward(x, gamma, dtype=torch.float64), FP32_RTOL, what="y")
 
 
+@pytest.mark.parametrize("shape", [(9, 4096), (5, 1000), (3, 1)])
+def test_block_read_variant(shape):
+    """One CTA per row, every pass from global memory: same results as the staged kernels."""
+    rows, cols = shape
+    opts = {"variant": N.VARIANT_BLOCK_READ}
+    x, gamma = W.make_rmsnorm_inputs(rows, cols, "cpu", seed=51)
+    (y,) = run("rmsnorm_forward", (x, gamma), 0, opts)
+    close(y, O.rmsnorm_forward(x, gamma, dtype=torch.float64), FP32_RTOL, what="y")
+    inputs = W.make_layernorm_forward_inputs(rows, cols, "cpu", seed=52)
+    check_layernorm_forward(inputs, run("layernorm_forward", inputs, 0, opts), BF16_RTOL)
+    inputs = W.make_layernorm_inputs(rows, cols, "cpu", seed=53)
+    (dx,) = run("layernorm_backward", inputs, 0, opts)
+    close(dx, O.layernorm_backward(*[t.double() for t in inputs]), FP32_RTOL, scale=2.0, what="dx")
+    inputs = W.make_layernorm_backward_stats_inputs(rows, cols, "cpu", seed=54)
+    check_backward_stats(inputs, run("layernorm_backward_stats", inputs, 0, opts), BF16_RTOL)
+    assert N.plan(N.WL_RMSNORM_FORWARD, rows, cols, N.F32, opts).cluster_size == 1
+    with pytest.raises(N.UnsupportedShape):
+        N.plan(N.WL_ROW_REDUCE, rows, cols, N.F32, opts)
+
+
 def test_plans_choose_the_expected_path():
     # aligned rows: register path; the flag or a ragged width: generic path
     assert N.plan(N.WL_RMSNORM_FORWARD, 1024, 32768, N.F32).vectors_per_thread > 0
