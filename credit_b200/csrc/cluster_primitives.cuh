@@ -124,6 +124,21 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t byt
                  : "memory");
 }
 
+// One arrival on a barrier of this CTA (release semantics).
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+// Remote store of one float into a peer CTA's shared memory; the peer's mbarrier
+// `remote_bar` is credited with the 4 bytes when they have landed, so data and
+// notification travel as one message (no cluster barrier, no fence).
+__device__ __forceinline__ void st_async_f32(uint32_t remote_addr, float v, uint32_t remote_bar) {
+    asm volatile("st.async.shared::cluster.mbarrier::complete_tx::bytes.f32 [%0], %1, [%2];" ::"r"(
+                     remote_addr),
+                 "f"(v), "r"(remote_bar)
+                 : "memory");
+}
+
 // One try: may suspend the thread (without issuing) for up to about a microsecond
 // while the phase is still pending.
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {

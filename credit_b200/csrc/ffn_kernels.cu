@@ -17,10 +17,18 @@
 // the shape the 128-byte swizzle of TMA and of the MMA shared-memory descriptors
 // is made for. Every CTA loads its own tiles (no TMA multicast anywhere).
 //
-// Kernel structure (one 128 x 256 output tile per CTA, 192 threads):
-//   warp 0   : TMA producer, 4-stage ring of (A 128x64, B 256x64) tiles
-//   warp 1   : allocates 256 TMEM columns, issues tcgen05.mma, commits to mbarriers
-//   warps 2-5: epilogue, tcgen05.ld 32 lanes x 32 columns at a time
+// Kernel structure (persistent, 192 threads, one CTA per SM; a CTA walks over
+// 128 x 256 output tiles):
+//   warp 0   : TMA producer, 4-stage ring of (A 128x64, B 256x64) tiles, runs ahead
+//              across tile boundaries
+//   warp 1   : allocates all 512 TMEM columns (two 128 x 256 fp32 accumulators),
+//              issues tcgen05.mma, commits to mbarriers
+//   warps 2-5: epilogue, tcgen05.ld 32 lanes x 32 columns at a time; the epilogue of
+//              tile i runs while the MMAs of tile i+1 fill the other accumulator
+// In the second GEMM the CTAs of a cluster walk over the same row blocks in step;
+// the per-row partial sums travel with st.async and are counted on the receiving
+// CTA's mbarrier (two slot buffers), so the producer and MMA warps never stop for
+// the exchange.
 // Every mbarrier wait is bounded; a timeout sets the device status word and the
 // kernel still releases its tensor memory.
 
@@ -43,23 +51,29 @@ constexpr int kBN = 256;
 constexpr int kBK = 64;                 // 64 bf16 = 128 bytes = one swizzle row
 constexpr int kStages = 4;
 constexpr int kUmmaK = 16;
-constexpr int kTmemCols = 256;
+constexpr int kAccCols = kBN;             // one accumulator: 128 lanes x 256 fp32 columns
+constexpr int kTmemCols = 2 * kAccCols;   // two accumulators = all of tensor memory
 constexpr int kATileBytes = kBM * kBK * 2;   // 16 KiB
 constexpr int kBTileBytes = kBN * kBK * 2;   // 32 KiB
 constexpr int kStageBytes = kATileBytes + kBTileBytes;
-constexpr int kFfnThreads = 192;
+constexpr int kEpilogueThreads = 128;
+constexpr int kFfnThreads = 64 + kEpilogueThreads;
 constexpr int kFfnControlBytes = 1024;
 constexpr int kMaxRowClusters = 16;
-// ring + control + alignment slack + row-partial slots of the second GEMM
+constexpr int kSlotBufferFloats = kBM * kMaxRowClusters;
+// ring + control + alignment slack + two buffers of row-partial slots (second GEMM)
 constexpr int kFfnSmemBytes = kStages * kStageBytes + kFfnControlBytes + 1024 +
-                              kBM * kMaxRowClusters * static_cast<int>(sizeof(float));
+                              2 * kSlotBufferFloats * static_cast<int>(sizeof(float));
 
 struct FfnControl {
-    uint64_t full[kStages];
-    uint64_t empty[kStages];
-    uint64_t tmem_full;
+    uint64_t full[kStages];     // TMA -> MMA: stage holds its tiles
+    uint64_t empty[kStages];    // MMA -> TMA: stage may be overwritten
+    uint64_t acc_full[2];       // MMA -> epilogue: accumulator complete
+    uint64_t acc_empty[2];      // epilogue -> MMA: accumulator read out (128 arrivals)
+    uint64_t slots_ready[2];    // peers -> epilogue: all row partials of a tile have landed
     uint32_t tmem_base;
 };
+static_assert(sizeof(FfnControl) <= kFfnControlBytes, "control block overflows its reservation");
 
 // ---- PTX wrappers --------------------------------------------------------------
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x,
@@ -166,36 +180,78 @@ __device__ __forceinline__ void unpack8(const uint4& r, float* o) {
     }
 }
 
+// Bounded wait that gives up for good after its first timeout, so a broken pipeline
+// costs one timeout per thread instead of one per k-block.
+__device__ __forceinline__ void wait_or_give_up(uint32_t bar, uint32_t parity, int* status, bool& gave_up) {
+    if (!gave_up && !mbar_wait_bounded(bar, parity, status)) gave_up = true;
+}
+
 // ---- the GEMM kernel -------------------------------------------------------------
-// C tile (m_tile = blockIdx.y, n_tile = blockIdx.x) of A [M, K] x B^T with B packed [N, K].
-// NORM_EPILOGUE == false: out = GELU(acc) as bf16 [M, N].
-// NORM_EPILOGUE == true : cluster of gridDim.x CTAs along N covers whole rows;
+// Output tiles of A [M, K] x B^T with B packed [N, K].
+// NORM_EPILOGUE == false: out = GELU(acc) as bf16 [M, N]; CTA b takes tiles b, b + grid, ...
+//                         numbered with the row block fastest, so that CTAs running at the
+//                         same time share B tiles through L2.
+// NORM_EPILOGUE == true : a cluster of n_tiles CTAs along N covers whole rows; cluster c takes
+//                         row blocks c, c + clusters, ...;
 //                         out = (acc + residual) * rsqrt(mean_row((acc+residual)^2) + eps) * gamma.
+struct TileWalk {
+    int begin, step, end, m_tiles;
+    int fixed_n;   // >= 0: every work item is a row block and the column tile is fixed
+    __device__ __forceinline__ void locate(int w, int& m_tile, int& n_tile) const {
+        if (fixed_n >= 0) {
+            m_tile = w;
+            n_tile = fixed_n;
+        } else {
+            m_tile = w % m_tiles;
+            n_tile = w / m_tiles;
+        }
+    }
+};
+
 template <bool NORM_EPILOGUE>
 __global__ void __launch_bounds__(kFfnThreads)
 ffn_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                 __nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ residual,
-                const float* __restrict__ gamma, int n_total, int k_total, float eps, int* status) {
+                const float* __restrict__ gamma, int m_tiles, int n_tiles, int n_total, int k_total, float eps,
+                int* status) {
     extern __shared__ unsigned char smem_raw[];
     // tiles need 1024-byte alignment for the 128-byte swizzle
     unsigned char* smem = reinterpret_cast<unsigned char*>(
         (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
     unsigned char* tiles = smem;
     FfnControl& ctl = *reinterpret_cast<FfnControl*>(smem + kStages * kStageBytes);
-    float* row_slots = reinterpret_cast<float*>(smem + kStages * kStageBytes + kFfnControlBytes);  // [kBM][16]
+    float* row_slots = reinterpret_cast<float*>(smem + kStages * kStageBytes + kFfnControlBytes);  // [2][kBM][16]
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    const int n_tile = blockIdx.x;
-    const int m_tile = blockIdx.y;
     const int k_blocks = k_total / kBK;
+    const uint32_t rank = NORM_EPILOGUE ? cluster_cta_rank() : 0u;
+    const uint32_t nranks = NORM_EPILOGUE ? cluster_cta_count() : 1u;
+
+    TileWalk walk;
+    walk.m_tiles = m_tiles;
+    if (NORM_EPILOGUE) {
+        walk.begin = static_cast<int>(blockIdx.x / nranks);
+        walk.step = static_cast<int>(gridDim.x / nranks);
+        walk.end = m_tiles;
+        walk.fixed_n = static_cast<int>(rank);
+    } else {
+        walk.begin = static_cast<int>(blockIdx.x);
+        walk.step = static_cast<int>(gridDim.x);
+        walk.end = m_tiles * n_tiles;
+        walk.fixed_n = -1;
+    }
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
             mbar_init(smem_u32(&ctl.full[s]), 1);
             mbar_init(smem_u32(&ctl.empty[s]), 1);
         }
-        mbar_init(smem_u32(&ctl.tmem_full), 1);
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(smem_u32(&ctl.acc_full[b]), 1);
+            mbar_init(smem_u32(&ctl.acc_empty[b]), kEpilogueThreads);
+            mbar_init(smem_u32(&ctl.slots_ready[b]), 1);
+        }
         fence_mbar_init();
     }
     if (warp == 1) tmem_alloc(smem_u32(&ctl.tmem_base), kTmemCols);
@@ -203,22 +259,27 @@ ffn_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_base = ctl.tmem_base;
-    if (NORM_EPILOGUE) cluster_sync_all();   // peers' shared memory may be written once they run
+    bool gave_up = false;
+    if (NORM_EPILOGUE) cluster_sync_all();   // peers' barriers exist before anything is sent to them
 
     if (warp == 0) {
         if (lane == 0) {
             int stage = 0;
             uint32_t parity = 1;   // a fresh barrier passes a wait on the "previous" phase
-            for (int kb = 0; kb < k_blocks; ++kb) {
-                mbar_wait_bounded(smem_u32(&ctl.empty[stage]), parity, status);
-                const uint32_t bar = smem_u32(&ctl.full[stage]);
-                mbar_arrive_expect_tx(bar, kStageBytes);
-                const uint32_t a_dst = smem_u32(tiles + stage * kStageBytes);
-                tma_load_2d(a_dst, &map_a, bar, kb * kBK, m_tile * kBM);
-                tma_load_2d(a_dst + kATileBytes, &map_b, bar, kb * kBK, n_tile * kBN);
-                if (++stage == kStages) {
-                    stage = 0;
-                    parity ^= 1u;
+            for (int w = walk.begin; w < walk.end; w += walk.step) {
+                int m_tile, n_tile;
+                walk.locate(w, m_tile, n_tile);
+                for (int kb = 0; kb < k_blocks; ++kb) {
+                    wait_or_give_up(smem_u32(&ctl.empty[stage]), parity, status, gave_up);
+                    const uint32_t bar = smem_u32(&ctl.full[stage]);
+                    mbar_arrive_expect_tx(bar, kStageBytes);
+                    const uint32_t a_dst = smem_u32(tiles + stage * kStageBytes);
+                    tma_load_2d(a_dst, &map_a, bar, kb * kBK, m_tile * kBM);
+                    tma_load_2d(a_dst + kATileBytes, &map_b, bar, kb * kBK, n_tile * kBN);
+                    if (++stage == kStages) {
+                        stage = 0;
+                        parity ^= 1u;
+                    }
                 }
             }
         }
@@ -228,109 +289,119 @@ ffn_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             constexpr uint32_t idesc = instr_desc(kBM, kBN);
             int stage = 0;
             uint32_t parity = 0;
-            for (int kb = 0; kb < k_blocks; ++kb) {
-                mbar_wait_bounded(smem_u32(&ctl.full[stage]), parity, status);
+            int it = 0;
+            for (int w = walk.begin; w < walk.end; w += walk.step, ++it) {
+                const int buf = it & 1;
+                // the epilogue has read this accumulator out (passes at once the first two times)
+                wait_or_give_up(smem_u32(&ctl.acc_empty[buf]), ((static_cast<uint32_t>(it) >> 1) & 1u) ^ 1u, status,
+                                gave_up);
                 tc_fence_after_sync();
-                const uint32_t a_addr = smem_u32(tiles + stage * kStageBytes);
-                const uint64_t desc_a = smem_desc_k_major_sw128(a_addr);
-                const uint64_t desc_b = smem_desc_k_major_sw128(a_addr + kATileBytes);
+                const uint32_t acc = tmem_base + static_cast<uint32_t>(buf * kAccCols);
+                for (int kb = 0; kb < k_blocks; ++kb) {
+                    wait_or_give_up(smem_u32(&ctl.full[stage]), parity, status, gave_up);
+                    tc_fence_after_sync();
+                    const uint32_t a_addr = smem_u32(tiles + stage * kStageBytes);
+                    const uint64_t desc_a = smem_desc_k_major_sw128(a_addr);
+                    const uint64_t desc_b = smem_desc_k_major_sw128(a_addr + kATileBytes);
 #pragma unroll
-                for (int k = 0; k < kBK / kUmmaK; ++k) {
-                    // advance 16 bf16 = 32 bytes inside the swizzle row: +2 in the address field
-                    umma_bf16(tmem_base, desc_a + 2u * k, desc_b + 2u * k, idesc, (kb | k) != 0 ? 1u : 0u);
+                    for (int k = 0; k < kBK / kUmmaK; ++k) {
+                        // advance 16 bf16 = 32 bytes inside the swizzle row: +2 in the address field
+                        umma_bf16(acc, desc_a + 2u * k, desc_b + 2u * k, idesc, (kb | k) != 0 ? 1u : 0u);
+                    }
+                    umma_commit(smem_u32(&ctl.empty[stage]));   // stage reusable when these MMAs are done
+                    if (++stage == kStages) {
+                        stage = 0;
+                        parity ^= 1u;
+                    }
                 }
-                umma_commit(smem_u32(&ctl.empty[stage]));   // stage reusable when these MMAs are done
-                if (++stage == kStages) {
-                    stage = 0;
-                    parity ^= 1u;
-                }
+                umma_commit(smem_u32(&ctl.acc_full[buf]));      // accumulator complete
             }
-            umma_commit(smem_u32(&ctl.tmem_full));          // accumulator complete
         }
         __syncwarp();
     } else {
         // epilogue warps 2..5: warp w may touch TMEM lanes 32 * (w % 4) .. +31
         const int quarter = warp & 3;
         const int row_in_tile = quarter * 32 + lane;
-        const size_t row = static_cast<size_t>(m_tile) * kBM + row_in_tile;
-        const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
-        mbar_wait_bounded(smem_u32(&ctl.tmem_full), 0, status);
-        tc_fence_after_sync();
-
-        if (!NORM_EPILOGUE) {
-            __nv_bfloat16* dst = out + row * n_total + static_cast<size_t>(n_tile) * kBN;
-#pragma unroll 1
-            for (int c = 0; c < kBN; c += 32) {
-                float v[32];
-                tmem_load_32x32(lane_base + c, v);
-#pragma unroll
-                for (int i = 0; i < 32; ++i) v[i] = gelu_erf(v[i]);
-#pragma unroll
-                for (int i = 0; i < 32; i += 8) *reinterpret_cast<uint4*>(dst + c + i) = pack8(v + i);
-            }
-        } else {
-            const uint32_t rank = cluster_cta_rank();
-            const uint32_t nranks = cluster_cta_count();
+        int it = 0;
+        for (int w = walk.begin; w < walk.end; w += walk.step, ++it) {
+            int m_tile, n_tile;
+            walk.locate(w, m_tile, n_tile);
+            const int buf = it & 1;
+            const uint32_t phase = (static_cast<uint32_t>(it) >> 1) & 1u;
+            const size_t row = static_cast<size_t>(m_tile) * kBM + row_in_tile;
             const size_t col0 = static_cast<size_t>(n_tile) * kBN;
-            const __nv_bfloat16* res = residual + row * n_total + col0;
-            // pass 1: sum of squares of z = acc + residual over this CTA's 256 columns of the row
-            float ss = 0.0f;
+            const uint32_t lane_base =
+                tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(buf * kAccCols);
+            __nv_bfloat16* dst = out + row * n_total + col0;
+            wait_or_give_up(smem_u32(&ctl.acc_full[buf]), phase, status, gave_up);
+            tc_fence_after_sync();
+
+            if (!NORM_EPILOGUE) {
 #pragma unroll 1
-            for (int c = 0; c < kBN; c += 32) {
-                float v[32];
-                tmem_load_32x32(lane_base + c, v);
+                for (int c = 0; c < kBN; c += 32) {
+                    float v[32];
+                    tmem_load_32x32(lane_base + c, v);
 #pragma unroll
-                for (int i = 0; i < 32; i += 8) {
-                    float r8[8];
-                    unpack8(__ldg(reinterpret_cast<const uint4*>(res + c + i)), r8);
+                    for (int i = 0; i < 32; ++i) v[i] = gelu_erf(v[i]);
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        const float z = v[i + j] + r8[j];
-                        ss = fmaf(z, z, ss);
+                    for (int i = 0; i < 32; i += 8) *reinterpret_cast<uint4*>(dst + c + i) = pack8(v + i);
+                }
+            } else {
+                const __nv_bfloat16* res = residual + row * n_total + col0;
+                float* slots = row_slots + buf * kSlotBufferFloats + row_in_tile * kMaxRowClusters;
+                const uint32_t ready = smem_u32(&ctl.slots_ready[buf]);
+                // this CTA will receive one float per row from every CTA of the cluster (itself included)
+                if (threadIdx.x == 64) mbar_arrive_expect_tx(ready, nranks * kBM * static_cast<uint32_t>(sizeof(float)));
+                // pass 1: sum of squares of z = acc + residual over this CTA's 256 columns of the row
+                float ss = 0.0f;
+#pragma unroll 1
+                for (int c = 0; c < kBN; c += 32) {
+                    float v[32];
+                    tmem_load_32x32(lane_base + c, v);
+#pragma unroll
+                    for (int i = 0; i < 32; i += 8) {
+                        float r8[8];
+                        unpack8(__ldg(reinterpret_cast<const uint4*>(res + c + i)), r8);
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            const float z = v[i + j] + r8[j];
+                            ss = fmaf(z, z, ss);
+                        }
+                    }
+                }
+                // every CTA of the cluster gets every CTA's partial of every row
+                for (uint32_t p = 0; p < nranks; ++p)
+                    st_async_f32(map_to_rank(smem_u32(&slots[rank]), p), ss, map_to_rank(ready, p));
+                wait_or_give_up(ready, phase, status, gave_up);
+                float total = 0.0f;
+                for (uint32_t p = 0; p < nranks; ++p) total += slots[p];
+                const float scale = rsqrtf(total / static_cast<float>(n_total) + eps);
+                // pass 2: normalise
+#pragma unroll 1
+                for (int c = 0; c < kBN; c += 32) {
+                    float v[32];
+                    tmem_load_32x32(lane_base + c, v);
+#pragma unroll
+                    for (int i = 0; i < 32; i += 8) {
+                        float r8[8], g8[8];
+                        unpack8(__ldg(reinterpret_cast<const uint4*>(res + c + i)), r8);
+                        ldg_f32x4(gamma + col0 + c + i, g8);
+                        ldg_f32x4(gamma + col0 + c + i + 4, g8 + 4);
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) v[i + j] = (v[i + j] + r8[j]) * scale * g8[j];
+                        *reinterpret_cast<uint4*>(dst + c + i) = pack8(v + i);
                     }
                 }
             }
-            // every CTA of the cluster gets every CTA's partial of every row
-            for (uint32_t p = 0; p < nranks; ++p)
-                st_cluster_f32(map_to_rank(smem_u32(&row_slots[row_in_tile * kMaxRowClusters + rank]), p), ss);
-        }
-    }
-
-    if (NORM_EPILOGUE) {
-        cluster_sync_all();   // all partials have landed everywhere (release / acquire)
-        if (warp >= 2) {
-            const int quarter = warp & 3;
-            const int row_in_tile = quarter * 32 + lane;
-            const size_t row = static_cast<size_t>(m_tile) * kBM + row_in_tile;
-            const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
-            const uint32_t nranks = cluster_cta_count();
-            const size_t col0 = static_cast<size_t>(n_tile) * kBN;
-            float total = 0.0f;
-            for (uint32_t p = 0; p < nranks; ++p) total += row_slots[row_in_tile * kMaxRowClusters + p];
-            const float scale = rsqrtf(total / static_cast<float>(n_total) + eps);
-            const __nv_bfloat16* res = residual + row * n_total + col0;
-            __nv_bfloat16* dst = out + row * n_total + col0;
-            tc_fence_after_sync();
-#pragma unroll 1
-            for (int c = 0; c < kBN; c += 32) {
-                float v[32];
-                tmem_load_32x32(lane_base + c, v);
-#pragma unroll
-                for (int i = 0; i < 32; i += 8) {
-                    float r8[8], g8[8];
-                    unpack8(__ldg(reinterpret_cast<const uint4*>(res + c + i)), r8);
-                    ldg_f32x4(gamma + col0 + c + i, g8);
-                    ldg_f32x4(gamma + col0 + c + i + 4, g8 + 4);
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) v[i + j] = (v[i + j] + r8[j]) * scale * g8[j];
-                    *reinterpret_cast<uint4*>(dst + c + i) = pack8(v + i);
-                }
-            }
+            // accumulator `buf` may be overwritten by the MMAs of tile it + 2
+            tc_fence_before_sync();
+            mbar_arrive(smem_u32(&ctl.acc_empty[buf]));
         }
     }
 
     tc_fence_before_sync();
     __syncthreads();
+    if (NORM_EPILOGUE) cluster_sync_all();   // no CTA leaves while a peer may still send to it
     if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
 }
 
@@ -422,31 +493,61 @@ cudaError_t launch_ffn_forward(const void* x, const void* w1p, const void* w2p, 
     });
     if (attr_err != cudaSuccess) return attr_err;
 
-    // GEMM 1: H = GELU(X W1), tiles over (h / 256, m / 128)
+    int device = 0, sms = 0;
+    cudaError_t err = cudaGetDevice(&device);
+    if (err == cudaSuccess) err = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+    if (err != cudaSuccess) return err;
+
+    const int m_tiles = m / kBM;
+    // GEMM 1: H = GELU(X W1); one persistent CTA per SM walks over the (m / 128) x (h / 256) tiles
     {
-        dim3 grid(static_cast<unsigned>(h / kBN), static_cast<unsigned>(m / kBM));
+        const int n_tiles = h / kBN;
+        const int tiles = m_tiles * n_tiles;
+        const unsigned grid = static_cast<unsigned>(tiles < sms ? tiles : sms);
         ffn_gemm_kernel<false><<<grid, kFfnThreads, kFfnSmemBytes, stream>>>(
-            map_x, map_w1, static_cast<__nv_bfloat16*>(hidden), nullptr, nullptr, h, d, 0.0f, status);
-        cudaError_t err = cudaGetLastError();
+            map_x, map_w1, static_cast<__nv_bfloat16*>(hidden), nullptr, nullptr, m_tiles, n_tiles, h, d, 0.0f,
+            status);
+        err = cudaGetLastError();
         if (err != cudaSuccess) return err;
     }
-    // GEMM 2: Y = RMSNorm(H W2 + X) gamma, one cluster of d / 256 CTAs per 128 rows
+    // GEMM 2: Y = RMSNorm(H W2 + X) gamma; clusters of d / 256 CTAs, as many as fit on the device
+    // at once, each walking over row blocks of 128 rows
     {
+        const int n_tiles = d / kBN;
         cudaLaunchConfig_t cfg{};
-        cfg.gridDim = dim3(static_cast<unsigned>(d / kBN), static_cast<unsigned>(m / kBM));
         cfg.blockDim = dim3(kFfnThreads);
         cfg.dynamicSmemBytes = kFfnSmemBytes;
         cfg.stream = stream;
         cudaLaunchAttribute attr{};
         attr.id = cudaLaunchAttributeClusterDimension;
-        attr.val.clusterDim.x = static_cast<unsigned>(d / kBN);
+        attr.val.clusterDim.x = static_cast<unsigned>(n_tiles);
         attr.val.clusterDim.y = 1;
         attr.val.clusterDim.z = 1;
         cfg.attrs = &attr;
         cfg.numAttrs = 1;
+
+        static std::mutex mu;
+        static int cached_clusters[kMaxRowClusters + 1] = {};   // per cluster size; one device kind per process
+        int resident = 0;
+        {
+            std::lock_guard<std::mutex> lock(mu);
+            if (cached_clusters[n_tiles] == 0) {
+                cfg.gridDim = dim3(static_cast<unsigned>(n_tiles * m_tiles));
+                int q = 0;
+                if (cudaOccupancyMaxActiveClusters(&q, ffn_gemm_kernel<true>, &cfg) != cudaSuccess || q < 1) {
+                    (void)cudaGetLastError();
+                    q = -1;   // unknown: one cluster per row block
+                }
+                cached_clusters[n_tiles] = q;
+            }
+            resident = cached_clusters[n_tiles];
+        }
+        const int clusters = (resident < 1 || resident > m_tiles) ? m_tiles : resident;
+        cfg.gridDim = dim3(static_cast<unsigned>(n_tiles * clusters));
         __nv_bfloat16* out = static_cast<__nv_bfloat16*>(y);
         const __nv_bfloat16* res = static_cast<const __nv_bfloat16*>(x);
-        return cudaLaunchKernelEx(&cfg, ffn_gemm_kernel<true>, map_h, map_w2, out, res, gamma, d, h, eps, status);
+        return cudaLaunchKernelEx(&cfg, ffn_gemm_kernel<true>, map_h, map_w2, out, res, gamma, m_tiles, n_tiles, d, h,
+                                  eps, status);
     }
 }
 

@@ -65,17 +65,6 @@ struct alignas(16) AsyncControl {
 };
 static_assert(sizeof(AsyncControl<2>) <= kControlBytes, "control block overflows its reservation");
 
-__device__ __forceinline__ void st_async_f32(uint32_t remote_addr, float v, uint32_t remote_bar) {
-    asm volatile("st.async.shared::cluster.mbarrier::complete_tx::bytes.f32 [%0], %1, [%2];" ::"r"(
-                     remote_addr),
-                 "f"(v), "r"(remote_bar)
-                 : "memory");
-}
-
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-
 // Delivers this warp's K warp-reduced partials of row `it`; warp 0 then collects
 // the W deliveries of the CTA, folds them and sends the CTA's totals to every CTA
 // of the cluster (arming its own mbarrier for the P * K floats it will receive).
