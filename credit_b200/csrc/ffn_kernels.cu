@@ -49,50 +49,85 @@ namespace {
 constexpr int kBM = 128;
 constexpr int kBN = 256;
 constexpr int kBK = 64;                 // 64 bf16 = 128 bytes = one swizzle row
-constexpr int kStages = 4;
+constexpr int kMaxFfnStages = 6;           // 4 stages of 48 KiB (one CTA per MMA) or 6 of 32 KiB (CTA pair)
 constexpr int kUmmaK = 16;
 constexpr int kAccCols = kBN;             // one accumulator: 128 lanes x 256 fp32 columns
 constexpr int kTmemCols = 2 * kAccCols;   // two accumulators = all of tensor memory
 constexpr int kATileBytes = kBM * kBK * 2;   // 16 KiB
-constexpr int kBTileBytes = kBN * kBK * 2;   // 32 KiB
-constexpr int kStageBytes = kATileBytes + kBTileBytes;
+constexpr int kRingBytes = 192 * 1024;
+
+// Ring geometry. One CTA per MMA: a stage holds A 128x64 and B 256x64. CTA pair
+// (tcgen05 cta_group::2, a 256 x 256 tile per pair): each CTA stages its own 128
+// rows of A and HALF of B (128 of the 256 columns of the tile); the tensor cores of
+// both SMs read both halves, so a CTA moves a third less through its shared memory
+// per MMA, which is what bounds the one-CTA form (TMA writes + MMA reads = 192 bytes
+// per clock against 128 available).
+template <bool PAIR>
+struct Ring {
+    static constexpr int kBRows = PAIR ? kBN / 2 : kBN;
+    static constexpr int kBTileBytes = kBRows * kBK * 2;
+    static constexpr int kStageBytes = kATileBytes + kBTileBytes;
+    static constexpr int kStages = kRingBytes / kStageBytes;
+    static_assert(kStages <= kMaxFfnStages, "control block has too few barriers");
+};
 constexpr int kEpilogueThreads = 128;
 constexpr int kFfnThreads = 64 + kEpilogueThreads;
 constexpr int kFfnControlBytes = 1024;
 constexpr int kMaxRowClusters = 16;
 constexpr int kSlotBufferFloats = kBM * kMaxRowClusters;
 // ring + control + alignment slack + two buffers of row-partial slots (second GEMM)
-constexpr int kFfnSmemBytes = kStages * kStageBytes + kFfnControlBytes + 1024 +
+constexpr int kFfnSmemBytes = kRingBytes + kFfnControlBytes + 1024 +
                               2 * kSlotBufferFloats * static_cast<int>(sizeof(float));
 
 struct FfnControl {
-    uint64_t full[kStages];     // TMA -> MMA: stage holds its tiles
-    uint64_t empty[kStages];    // MMA -> TMA: stage may be overwritten
+    uint64_t full[kMaxFfnStages];   // TMA -> MMA: stage holds its tiles (pair: both CTAs' halves)
+    uint64_t empty[kMaxFfnStages];  // MMA -> TMA: stage may be overwritten
     uint64_t acc_full[2];       // MMA -> epilogue: accumulator complete
-    uint64_t acc_empty[2];      // epilogue -> MMA: accumulator read out (128 arrivals)
+    uint64_t acc_empty[2];      // epilogue -> MMA: accumulator read out (one arrival per epilogue warp)
     uint64_t slots_ready[2];    // peers -> epilogue: all row partials of a tile have landed
     uint32_t tmem_base;
 };
 static_assert(sizeof(FfnControl) <= kFfnControlBytes, "control block overflows its reservation");
 
 // ---- PTX wrappers --------------------------------------------------------------
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x,
-                                            int y) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::
-            "r"(dst),
-        "l"(map), "r"(bar), "r"(x), "r"(y)
-        : "memory");
+// CG = 1: an MMA of one CTA. CG = 2: an MMA of a CTA pair (cluster ranks 2i, 2i + 1); the even
+// CTA (the leader) issues it, and copies, commits and tensor-memory management carry the same
+// qualifier.
+template <int CG>
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+    if (CG == 1)
+        asm volatile(
+            "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::
+                "r"(dst),
+            "l"(map), "r"(bar), "r"(x), "r"(y)
+            : "memory");
+    else   // `bar` may be the leader's barrier (a shared::cluster address)
+        asm volatile(
+            "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, "
+            "%4}], [%2];" ::"r"(dst),
+            "l"(map), "r"(bar), "r"(x), "r"(y)
+            : "memory");
 }
 
+template <int CG>
 __device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t cols) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(cols)
-                 : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    if (CG == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(cols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    } else {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(cols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
 }
 
+template <int CG>
 __device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+    if (CG == 1)
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+    else
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
 }
 
 __device__ __forceinline__ void tc_fence_before_sync() {
@@ -103,24 +138,54 @@ __device__ __forceinline__ void tc_fence_after_sync() {
 }
 
 // D[tmem] (+)= A[smem] * B[smem]; issued by one thread.
+template <int CG>
 __device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
                                           uint32_t accumulate) {
+    if (CG == 1)
+        asm volatile(
+            "{\n\t"
+            ".reg .pred p;\n\t"
+            "setp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
+            "}" ::"r"(tmem_d),
+            "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+            : "memory");
+    else
+        asm volatile(
+            "{\n\t"
+            ".reg .pred p;\n\t"
+            "setp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t"
+            "}" ::"r"(tmem_d),
+            "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+            : "memory");
+}
+
+// The mbarrier (any CTA of the cluster) gets one arrival when every MMA issued so far by this
+// thread is done.
+template <int CG>
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    if (CG == 1)
+        asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
+                     : "memory");
+    else
+        asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
+                     : "memory");
+}
+
+// Pair form for a barrier that exists at the same shared-memory offset in both CTAs of the pair:
+// one commit, one arrival on each CTA's copy (mask: cluster ranks of the receivers).
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar, uint16_t cta_mask) {
     asm volatile(
-        "{\n\t"
-        ".reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
-        "}" ::"r"(tmem_d),
-        "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar),
+        "h"(cta_mask)
         : "memory");
 }
 
-// The mbarrier gets one arrival when every MMA issued so far by this thread is done.
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
-                 : "memory");
+// Arrivals on a barrier that may live in another CTA of the cluster.
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
 }
-
 // 32 lanes x 32 consecutive fp32 columns: lane i of the warp gets row (lane base + i).
 __device__ __forceinline__ void tmem_load_32x32(uint32_t taddr, float (&v)[32]) {
     uint32_t r[32];
@@ -208,25 +273,38 @@ struct TileWalk {
     }
 };
 
-template <bool NORM_EPILOGUE>
+// PAIR: launched as clusters of two CTAs that share every MMA (NORM_EPILOGUE must be false).
+// A work item is then a 256 x 256 tile; CTA `half` of the pair owns rows half * 128 .. + 127 of it
+// (its A tile, its accumulators, its epilogue) and stages columns half * 128 .. + 127 of B.
+template <bool NORM_EPILOGUE, bool PAIR>
 __global__ void __launch_bounds__(kFfnThreads)
 ffn_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                 __nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ residual,
                 const float* __restrict__ gamma, int m_tiles, int n_tiles, int n_total, int k_total, float eps,
                 int* status) {
+    static_assert(!(NORM_EPILOGUE && PAIR), "the row-norm epilogue uses the cluster for whole rows");
+    constexpr int CG = PAIR ? 2 : 1;
+    using R = Ring<PAIR>;
+    constexpr int kStages = R::kStages;
+    constexpr int kStageBytes = R::kStageBytes;
+    constexpr int kTileRows = PAIR ? 2 * kBM : kBM;   // rows of a work item
+
     extern __shared__ unsigned char smem_raw[];
-    // tiles need 1024-byte alignment for the 128-byte swizzle
+    // tiles need 1024-byte alignment for the 128-byte swizzle; the dynamic window starts at the
+    // same shared-memory address in every CTA, so both CTAs of a pair get the same offsets
     unsigned char* smem = reinterpret_cast<unsigned char*>(
         (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
     unsigned char* tiles = smem;
-    FfnControl& ctl = *reinterpret_cast<FfnControl*>(smem + kStages * kStageBytes);
-    float* row_slots = reinterpret_cast<float*>(smem + kStages * kStageBytes + kFfnControlBytes);  // [2][kBM][16]
+    FfnControl& ctl = *reinterpret_cast<FfnControl*>(smem + kRingBytes);
+    float* row_slots = reinterpret_cast<float*>(smem + kRingBytes + kFfnControlBytes);  // [2][kBM][16]
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const int k_blocks = k_total / kBK;
-    const uint32_t rank = NORM_EPILOGUE ? cluster_cta_rank() : 0u;
+    const uint32_t rank = (NORM_EPILOGUE || PAIR) ? cluster_cta_rank() : 0u;
     const uint32_t nranks = NORM_EPILOGUE ? cluster_cta_count() : 1u;
+    const int half = PAIR ? static_cast<int>(rank & 1u) : 0;
+    const bool leader = half == 0;
 
     TileWalk walk;
     walk.m_tiles = m_tiles;
@@ -236,31 +314,32 @@ ffn_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         walk.end = m_tiles;
         walk.fixed_n = static_cast<int>(rank);
     } else {
-        walk.begin = static_cast<int>(blockIdx.x);
-        walk.step = static_cast<int>(gridDim.x);
+        walk.begin = static_cast<int>(blockIdx.x) / CG;
+        walk.step = static_cast<int>(gridDim.x) / CG;
         walk.end = m_tiles * n_tiles;
         walk.fixed_n = -1;
     }
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
-            mbar_init(smem_u32(&ctl.full[s]), 1);
+            mbar_init(smem_u32(&ctl.full[s]), 1);     // the (leader's) producer's arrive.expect_tx
             mbar_init(smem_u32(&ctl.empty[s]), 1);
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(smem_u32(&ctl.acc_full[b]), 1);
-            mbar_init(smem_u32(&ctl.acc_empty[b]), kEpilogueThreads);
+            mbar_init(smem_u32(&ctl.acc_empty[b]), CG * (kEpilogueThreads / 32));
             mbar_init(smem_u32(&ctl.slots_ready[b]), 1);
         }
         fence_mbar_init();
     }
-    if (warp == 1) tmem_alloc(smem_u32(&ctl.tmem_base), kTmemCols);
+    if (warp == 1) tmem_alloc<CG>(smem_u32(&ctl.tmem_base), kTmemCols);
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_base = ctl.tmem_base;
     bool gave_up = false;
-    if (NORM_EPILOGUE) cluster_sync_all();   // peers' barriers exist before anything is sent to them
+    // peers' barriers exist before anything is sent to them
+    if (NORM_EPILOGUE || PAIR) cluster_sync_all();
 
     if (warp == 0) {
         if (lane == 0) {
@@ -269,13 +348,19 @@ ffn_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             for (int w = walk.begin; w < walk.end; w += walk.step) {
                 int m_tile, n_tile;
                 walk.locate(w, m_tile, n_tile);
+                const int a_row = m_tile * kTileRows + half * kBM;
+                const int b_row = n_tile * kBN + half * R::kBRows;
                 for (int kb = 0; kb < k_blocks; ++kb) {
                     wait_or_give_up(smem_u32(&ctl.empty[stage]), parity, status, gave_up);
-                    const uint32_t bar = smem_u32(&ctl.full[stage]);
-                    mbar_arrive_expect_tx(bar, kStageBytes);
+                    // the stage's "full" barrier is the leader's: its MMA thread consumes both halves
+                    // and arms it for the bytes of both CTAs (the peer's copies may complete on it
+                    // first: the phase cannot end before this arrival)
+                    const uint32_t local_bar = smem_u32(&ctl.full[stage]);
+                    const uint32_t bar = PAIR ? map_to_rank(local_bar, rank & ~1u) : local_bar;
+                    if (leader) mbar_arrive_expect_tx(local_bar, CG * kStageBytes);
                     const uint32_t a_dst = smem_u32(tiles + stage * kStageBytes);
-                    tma_load_2d(a_dst, &map_a, bar, kb * kBK, m_tile * kBM);
-                    tma_load_2d(a_dst + kATileBytes, &map_b, bar, kb * kBK, n_tile * kBN);
+                    tma_load_2d<CG>(a_dst, &map_a, bar, kb * kBK, a_row);
+                    tma_load_2d<CG>(a_dst + kATileBytes, &map_b, bar, kb * kBK, b_row);
                     if (++stage == kStages) {
                         stage = 0;
                         parity ^= 1u;
@@ -285,14 +370,16 @@ ffn_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         }
         __syncwarp();
     } else if (warp == 1) {
-        if (lane == 0) {
-            constexpr uint32_t idesc = instr_desc(kBM, kBN);
+        if (lane == 0 && leader) {
+            constexpr uint32_t idesc = instr_desc(kTileRows, kBN);
+            const uint16_t pair_mask = static_cast<uint16_t>(3u << (rank & ~1u));
             int stage = 0;
             uint32_t parity = 0;
             int it = 0;
             for (int w = walk.begin; w < walk.end; w += walk.step, ++it) {
                 const int buf = it & 1;
-                // the epilogue has read this accumulator out (passes at once the first two times)
+                // the epilogue warps (of both CTAs) have read this accumulator out; passes at once
+                // the first two times
                 wait_or_give_up(smem_u32(&ctl.acc_empty[buf]), ((static_cast<uint32_t>(it) >> 1) & 1u) ^ 1u, status,
                                 gave_up);
                 tc_fence_after_sync();
@@ -306,15 +393,22 @@ ffn_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 #pragma unroll
                     for (int k = 0; k < kBK / kUmmaK; ++k) {
                         // advance 16 bf16 = 32 bytes inside the swizzle row: +2 in the address field
-                        umma_bf16(acc, desc_a + 2u * k, desc_b + 2u * k, idesc, (kb | k) != 0 ? 1u : 0u);
+                        umma_bf16<CG>(acc, desc_a + 2u * k, desc_b + 2u * k, idesc, (kb | k) != 0 ? 1u : 0u);
                     }
-                    umma_commit(smem_u32(&ctl.empty[stage]));   // stage reusable when these MMAs are done
+                    // stage reusable (in both CTAs) when these MMAs are done
+                    if (PAIR)
+                        umma_commit_pair(smem_u32(&ctl.empty[stage]), pair_mask);
+                    else
+                        umma_commit<CG>(smem_u32(&ctl.empty[stage]));
                     if (++stage == kStages) {
                         stage = 0;
                         parity ^= 1u;
                     }
                 }
-                umma_commit(smem_u32(&ctl.acc_full[buf]));      // accumulator complete
+                if (PAIR)   // accumulator complete (in both CTAs)
+                    umma_commit_pair(smem_u32(&ctl.acc_full[buf]), pair_mask);
+                else
+                    umma_commit<CG>(smem_u32(&ctl.acc_full[buf]));
             }
         }
         __syncwarp();
@@ -328,7 +422,7 @@ ffn_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             walk.locate(w, m_tile, n_tile);
             const int buf = it & 1;
             const uint32_t phase = (static_cast<uint32_t>(it) >> 1) & 1u;
-            const size_t row = static_cast<size_t>(m_tile) * kBM + row_in_tile;
+            const size_t row = static_cast<size_t>(m_tile) * kTileRows + half * kBM + row_in_tile;
             const size_t col0 = static_cast<size_t>(n_tile) * kBN;
             const uint32_t lane_base =
                 tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(buf * kAccCols);
@@ -393,16 +487,25 @@ ffn_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     }
                 }
             }
-            // accumulator `buf` may be overwritten by the MMAs of tile it + 2
+            // accumulator `buf` may be overwritten by the MMAs of tile it + 2: one arrival per warp
+            // on the barrier of the CTA that issues them
             tc_fence_before_sync();
-            mbar_arrive(smem_u32(&ctl.acc_empty[buf]));
+            __syncwarp();
+            if (lane == 0) {
+                const uint32_t bar = smem_u32(&ctl.acc_empty[buf]);
+                if (PAIR)
+                    mbar_arrive_cluster(map_to_rank(bar, rank & ~1u));
+                else
+                    mbar_arrive(bar);
+            }
         }
     }
 
     tc_fence_before_sync();
     __syncthreads();
-    if (NORM_EPILOGUE) cluster_sync_all();   // no CTA leaves while a peer may still send to it
-    if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
+    // no CTA leaves while a peer may still send to it, read its tiles or signal its barriers
+    if (NORM_EPILOGUE || PAIR) cluster_sync_all();
+    if (warp == 1) tmem_dealloc<CG>(tmem_base, kTmemCols);
 }
 
 // Transposes a row-major [k, n] bf16 weight into the K-major [n, k] form the GEMMs take.
@@ -469,13 +572,45 @@ cudaError_t launch_ffn_pack_weight(const void* w, void* packed, int k, int n, cu
     return cudaGetLastError();
 }
 
+namespace {
+// Clusters of `cluster_size` CTAs of `kernel` that can be resident at once (cached per cluster
+// size; one device kind per process), or -1 if the driver cannot tell. A persistent grid must not
+// be larger: the surplus clusters would only start when the first ones have finished everything.
+int resident_clusters(const void* kernel, int cluster_size, int grid_clusters, int* cache) {
+    static std::mutex mu;
+    std::lock_guard<std::mutex> lock(mu);
+    if (*cache == 0) {
+        cudaLaunchConfig_t cfg{};
+        cfg.gridDim = dim3(static_cast<unsigned>(cluster_size * grid_clusters));
+        cfg.blockDim = dim3(kFfnThreads);
+        cfg.dynamicSmemBytes = kFfnSmemBytes;
+        cudaLaunchAttribute attr{};
+        attr.id = cudaLaunchAttributeClusterDimension;
+        attr.val.clusterDim.x = static_cast<unsigned>(cluster_size);
+        attr.val.clusterDim.y = 1;
+        attr.val.clusterDim.z = 1;
+        cfg.attrs = &attr;
+        cfg.numAttrs = 1;
+        int q = 0;
+        if (cudaOccupancyMaxActiveClusters(&q, kernel, &cfg) != cudaSuccess || q < 1) {
+            (void)cudaGetLastError();
+            q = -1;
+        }
+        *cache = q;
+    }
+    return *cache;
+}
+}  // namespace
+
 // Returns cudaSuccess, or an error; *bad_map is set when a tensor map could not be encoded.
 cudaError_t launch_ffn_forward(const void* x, const void* w1p, const void* w2p, const float* gamma, void* y,
                                void* hidden, int m, int d, int h, float eps, int* status,
                                cudaStream_t stream, bool* bad_map) {
     *bad_map = false;
+    // CTA pairs need whole 256-row tiles; otherwise the first GEMM runs one CTA per MMA
+    const bool pair = m % (2 * kBM) == 0;
     CUtensorMap map_x, map_w1, map_h, map_w2;
-    if (!make_map(&map_x, x, m, d, kBM) || !make_map(&map_w1, w1p, h, d, kBN) ||
+    if (!make_map(&map_x, x, m, d, kBM) || !make_map(&map_w1, w1p, h, d, pair ? kBN / 2 : kBN) ||
         !make_map(&map_h, hidden, m, h, kBM) || !make_map(&map_w2, w2p, d, h, kBN)) {
         *bad_map = true;
         return cudaErrorInvalidValue;
@@ -483,13 +618,15 @@ cudaError_t launch_ffn_forward(const void* x, const void* w1p, const void* w2p, 
     static std::once_flag once;
     static cudaError_t attr_err = cudaSuccess;
     std::call_once(once, [] {
-        attr_err = cudaFuncSetAttribute(ffn_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                        kFfnSmemBytes);
+        const void* kernels[3] = {reinterpret_cast<const void*>(ffn_gemm_kernel<false, false>),
+                                  reinterpret_cast<const void*>(ffn_gemm_kernel<false, true>),
+                                  reinterpret_cast<const void*>(ffn_gemm_kernel<true, false>)};
+        for (const void* k : kernels)
+            if (attr_err == cudaSuccess)
+                attr_err = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, kFfnSmemBytes);
         if (attr_err == cudaSuccess)
-            attr_err = cudaFuncSetAttribute(ffn_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                            kFfnSmemBytes);
-        if (attr_err == cudaSuccess)
-            attr_err = cudaFuncSetAttribute(ffn_gemm_kernel<true>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+            attr_err = cudaFuncSetAttribute(ffn_gemm_kernel<true, false>,
+                                            cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
     });
     if (attr_err != cudaSuccess) return attr_err;
 
@@ -499,15 +636,41 @@ cudaError_t launch_ffn_forward(const void* x, const void* w1p, const void* w2p, 
     if (err != cudaSuccess) return err;
 
     const int m_tiles = m / kBM;
-    // GEMM 1: H = GELU(X W1); one persistent CTA per SM walks over the (m / 128) x (h / 256) tiles
+    // GEMM 1: H = GELU(X W1); persistent CTAs (pairs of CTAs sharing each MMA when m allows) walk
+    // over the tiles
     {
         const int n_tiles = h / kBN;
-        const int tiles = m_tiles * n_tiles;
-        const unsigned grid = static_cast<unsigned>(tiles < sms ? tiles : sms);
-        ffn_gemm_kernel<false><<<grid, kFfnThreads, kFfnSmemBytes, stream>>>(
-            map_x, map_w1, static_cast<__nv_bfloat16*>(hidden), nullptr, nullptr, m_tiles, n_tiles, h, d, 0.0f,
-            status);
-        err = cudaGetLastError();
+        __nv_bfloat16* hid = static_cast<__nv_bfloat16*>(hidden);
+        if (pair) {
+            const int tiles = (m_tiles / 2) * n_tiles;
+            static int cached_pairs = 0;
+            int pairs = resident_clusters(reinterpret_cast<const void*>(ffn_gemm_kernel<false, true>), 2, tiles,
+                                          &cached_pairs);
+            if (pairs < 1) pairs = sms / 2;
+            if (pairs > tiles) pairs = tiles;
+            cudaLaunchConfig_t cfg{};
+            cfg.gridDim = dim3(static_cast<unsigned>(2 * pairs));
+            cfg.blockDim = dim3(kFfnThreads);
+            cfg.dynamicSmemBytes = kFfnSmemBytes;
+            cfg.stream = stream;
+            cudaLaunchAttribute attr{};
+            attr.id = cudaLaunchAttributeClusterDimension;
+            attr.val.clusterDim.x = 2;
+            attr.val.clusterDim.y = 1;
+            attr.val.clusterDim.z = 1;
+            cfg.attrs = &attr;
+            cfg.numAttrs = 1;
+            const __nv_bfloat16* no_res = nullptr;
+            const float* no_gamma = nullptr;
+            err = cudaLaunchKernelEx(&cfg, ffn_gemm_kernel<false, true>, map_x, map_w1, hid, no_res, no_gamma,
+                                     m_tiles / 2, n_tiles, h, d, 0.0f, status);
+        } else {
+            const int tiles = m_tiles * n_tiles;
+            const unsigned grid = static_cast<unsigned>(tiles < sms ? tiles : sms);
+            ffn_gemm_kernel<false, false><<<grid, kFfnThreads, kFfnSmemBytes, stream>>>(
+                map_x, map_w1, hid, nullptr, nullptr, m_tiles, n_tiles, h, d, 0.0f, status);
+            err = cudaGetLastError();
+        }
         if (err != cudaSuccess) return err;
     }
     // GEMM 2: Y = RMSNorm(H W2 + X) gamma; clusters of d / 256 CTAs, as many as fit on the device
@@ -526,27 +689,14 @@ cudaError_t launch_ffn_forward(const void* x, const void* w1p, const void* w2p, 
         cfg.attrs = &attr;
         cfg.numAttrs = 1;
 
-        static std::mutex mu;
-        static int cached_clusters[kMaxRowClusters + 1] = {};   // per cluster size; one device kind per process
-        int resident = 0;
-        {
-            std::lock_guard<std::mutex> lock(mu);
-            if (cached_clusters[n_tiles] == 0) {
-                cfg.gridDim = dim3(static_cast<unsigned>(n_tiles * m_tiles));
-                int q = 0;
-                if (cudaOccupancyMaxActiveClusters(&q, ffn_gemm_kernel<true>, &cfg) != cudaSuccess || q < 1) {
-                    (void)cudaGetLastError();
-                    q = -1;   // unknown: one cluster per row block
-                }
-                cached_clusters[n_tiles] = q;
-            }
-            resident = cached_clusters[n_tiles];
-        }
+        static int cached_clusters[kMaxRowClusters + 1] = {};
+        const int resident = resident_clusters(reinterpret_cast<const void*>(ffn_gemm_kernel<true, false>), n_tiles,
+                                               m_tiles, &cached_clusters[n_tiles]);
         const int clusters = (resident < 1 || resident > m_tiles) ? m_tiles : resident;
         cfg.gridDim = dim3(static_cast<unsigned>(n_tiles * clusters));
         __nv_bfloat16* out = static_cast<__nv_bfloat16*>(y);
         const __nv_bfloat16* res = static_cast<const __nv_bfloat16*>(x);
-        return cudaLaunchKernelEx(&cfg, ffn_gemm_kernel<true>, map_h, map_w2, out, res, gamma, m_tiles, n_tiles, d, h,
+        return cudaLaunchKernelEx(&cfg, ffn_gemm_kernel<true, false>, map_h, map_w2, out, res, gamma, m_tiles, n_tiles, d, h,
                                   eps, status);
     }
 }

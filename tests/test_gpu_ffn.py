@@ -29,7 +29,7 @@ def check(y, want):
 
 
 @pytest.mark.parametrize("m,d,h", [(128, 256, 512), (256, 512, 1024), (128, 1024, 2048), (384, 2048, 512),
-                                    (128, 4096, 1024)])
+                                    (128, 4096, 1024), (1024, 512, 8192)])
 def test_ffn_forward_matches_oracle(native_lib, m, d, h):
     x, w1, w2, gamma = W.make_ffn_inputs(m, d, "cpu", seed=m + d, hidden=h)
     y, w1p = run_ffn(x, w1, w2, gamma)
