@@ -256,22 +256,77 @@ __device__ __forceinline__ void wait_or_give_up(uint32_t bar, uint32_t parity, i
 // NORM_EPILOGUE == false: out = GELU(acc) as bf16 [M, N]; CTA b takes tiles b, b + grid, ...
 //                         numbered with the row block fastest, so that CTAs running at the
 //                         same time share B tiles through L2.
-// NORM_EPILOGUE == true : a cluster of n_tiles CTAs along N covers whole rows; cluster c takes
-//                         row blocks c, c + clusters, ...;
+// NORM_EPILOGUE == true : a cluster of n_tiles CTAs along N covers whole rows;
 //                         out = (acc + residual) * rsqrt(mean_row((acc+residual)^2) + eps) * gamma.
+//   Plain walk : cluster c takes row blocks c, c + clusters, ... All clusters start a row block
+//                at the same time and move through k together, so a k block of B is fetched from
+//                HBM once and served to the other clusters by L2 (B is as large as L2).
+//   Split tail : when the row blocks do not divide evenly among the resident clusters, the L
+//                blocks left after the full rounds are each shared by a group of G = clusters / L
+//                clusters, which cut the k range into G equal parts (again in step across blocks).
+//                The cluster with the first part OWNS the block; the others are HELPERS: they write
+//                their raw fp32 partial tile to global memory and raise a flag; the owner adds the
+//                partials to its accumulator and runs the epilogue.
+struct WorkItem {
+    int tile;       // row block (NORM) or tile number
+    int kb0, kb1;   // k blocks [kb0, kb1)
+};
+
 struct TileWalk {
-    int begin, step, end, m_tiles;
-    int fixed_n;   // >= 0: every work item is a row block and the column tile is fixed
-    __device__ __forceinline__ void locate(int w, int& m_tile, int& n_tile) const {
+    int m_tiles, k_blocks;
+    int fixed_n;           // >= 0: every work item is a row block and the column tile is fixed
+    int next, step, end;   // plain walk
+    int tail_tile;         // >= 0: one more item, part of a shared row block
+    int tail_kb0, tail_kb1;
+
+    __device__ __forceinline__ bool pop(WorkItem& w) {
+        if (next < end) {
+            w.tile = next;
+            w.kb0 = 0;
+            w.kb1 = k_blocks;
+            next += step;
+            return true;
+        }
+        if (tail_tile < 0) return false;
+        w.tile = tail_tile;
+        w.kb0 = tail_kb0;
+        w.kb1 = tail_kb1;
+        tail_tile = -1;
+        return true;
+    }
+    __device__ __forceinline__ void locate(int tile, int& m_tile, int& n_tile) const {
         if (fixed_n >= 0) {
-            m_tile = w;
+            m_tile = tile;
             n_tile = fixed_n;
         } else {
-            m_tile = w % m_tiles;
-            n_tile = w / m_tiles;
+            m_tile = tile % m_tiles;
+            n_tile = tile / m_tiles;
         }
     }
 };
+
+constexpr int kPartialSlots = 16;   // split walk: at most this many clusters (one partial tile each)
+
+// Float offset, inside a partial slot, of the 4 columns [32 * chunk + 4 * g, +4) of row `row` in
+// the tile of cluster rank `rank`: rows are the fastest index, so a warp's stores are contiguous.
+__device__ __forceinline__ size_t partial_offset(uint32_t rank, int chunk, int g, int row) {
+    return ((static_cast<size_t>(rank) * (kBN / 32) + chunk) * 8 + g) * (kBM * 4) + static_cast<size_t>(row) * 4;
+}
+
+// Bounded wait for a flag another cluster sets in global memory.
+__device__ __forceinline__ void wait_flag(const int* flag, int* status, bool& gave_up) {
+    if (gave_up) return;
+    const volatile int* f = flag;
+    const long long t0 = clock64();
+    while (*f == 0) {
+        if (clock64() - t0 > (1ll << 31)) {
+            atomicOr(status, kStatusWaitTimeout);
+            gave_up = true;
+            break;
+        }
+    }
+    __threadfence();   // the partial tile written before the flag is visible to the loads after it
+}
 
 // PAIR: launched as clusters of two CTAs that share every MMA (NORM_EPILOGUE must be false).
 // A work item is then a 256 x 256 tile; CTA `half` of the pair owns rows half * 128 .. + 127 of it
@@ -281,7 +336,7 @@ __global__ void __launch_bounds__(kFfnThreads)
 ffn_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                 __nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ residual,
                 const float* __restrict__ gamma, int m_tiles, int n_tiles, int n_total, int k_total, float eps,
-                int* status) {
+                float* __restrict__ partials, int* __restrict__ flags, int* status) {
     static_assert(!(NORM_EPILOGUE && PAIR), "the row-norm epilogue uses the cluster for whole rows");
     constexpr int CG = PAIR ? 2 : 1;
     using R = Ring<PAIR>;
@@ -306,18 +361,41 @@ ffn_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     const int half = PAIR ? static_cast<int>(rank & 1u) : 0;
     const bool leader = half == 0;
 
-    TileWalk walk;
-    walk.m_tiles = m_tiles;
+    // every role walks over the same sequence of work items with its own copy of this
+    TileWalk walk0;
+    walk0.m_tiles = m_tiles;
+    walk0.k_blocks = k_blocks;
+    walk0.tail_tile = -1;
+    walk0.tail_kb0 = walk0.tail_kb1 = 0;
+    int group = 1;   // clusters sharing the tail row block of this cluster
+    const int cluster_id = static_cast<int>(blockIdx.x / (NORM_EPILOGUE ? nranks : CG));
+    const int num_clusters = static_cast<int>(gridDim.x / (NORM_EPILOGUE ? nranks : CG));
     if (NORM_EPILOGUE) {
-        walk.begin = static_cast<int>(blockIdx.x / nranks);
-        walk.step = static_cast<int>(gridDim.x / nranks);
-        walk.end = m_tiles;
-        walk.fixed_n = static_cast<int>(rank);
+        walk0.next = cluster_id;
+        walk0.step = num_clusters;
+        walk0.end = m_tiles;
+        walk0.fixed_n = static_cast<int>(rank);
+        const int left = m_tiles % num_clusters;
+        // at most 4 clusters per block (the owner reads every helper's tile twice), at least 4 k
+        // blocks per part
+        int share = left != 0 ? num_clusters / left : 1;
+        share = share < 4 ? share : 4;
+        share = share < k_blocks / 4 ? share : k_blocks / 4;
+        if (partials != nullptr && share >= 2) {
+            group = share;
+            walk0.end = m_tiles - left;   // full rounds only
+            if (cluster_id < left * group) {
+                const int part = cluster_id % group;
+                walk0.tail_tile = m_tiles - left + cluster_id / group;
+                walk0.tail_kb0 = static_cast<int>(static_cast<long long>(k_blocks) * part / group);
+                walk0.tail_kb1 = static_cast<int>(static_cast<long long>(k_blocks) * (part + 1) / group);
+            }
+        }
     } else {
-        walk.begin = static_cast<int>(blockIdx.x) / CG;
-        walk.step = static_cast<int>(gridDim.x) / CG;
-        walk.end = m_tiles * n_tiles;
-        walk.fixed_n = -1;
+        walk0.next = cluster_id;
+        walk0.step = num_clusters;
+        walk0.end = m_tiles * n_tiles;
+        walk0.fixed_n = -1;
     }
 
     if (threadIdx.x == 0) {
@@ -345,12 +423,14 @@ ffn_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         if (lane == 0) {
             int stage = 0;
             uint32_t parity = 1;   // a fresh barrier passes a wait on the "previous" phase
-            for (int w = walk.begin; w < walk.end; w += walk.step) {
+            TileWalk walk = walk0;
+            WorkItem w;
+            while (walk.pop(w)) {
                 int m_tile, n_tile;
-                walk.locate(w, m_tile, n_tile);
+                walk.locate(w.tile, m_tile, n_tile);
                 const int a_row = m_tile * kTileRows + half * kBM;
                 const int b_row = n_tile * kBN + half * R::kBRows;
-                for (int kb = 0; kb < k_blocks; ++kb) {
+                for (int kb = w.kb0; kb < w.kb1; ++kb) {
                     wait_or_give_up(smem_u32(&ctl.empty[stage]), parity, status, gave_up);
                     // the stage's "full" barrier is the leader's: its MMA thread consumes both halves
                     // and arms it for the bytes of both CTAs (the peer's copies may complete on it
@@ -375,8 +455,9 @@ ffn_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             const uint16_t pair_mask = static_cast<uint16_t>(3u << (rank & ~1u));
             int stage = 0;
             uint32_t parity = 0;
-            int it = 0;
-            for (int w = walk.begin; w < walk.end; w += walk.step, ++it) {
+            TileWalk walk = walk0;
+            WorkItem w;
+            for (int it = 0; walk.pop(w); ++it) {
                 const int buf = it & 1;
                 // the epilogue warps (of both CTAs) have read this accumulator out; passes at once
                 // the first two times
@@ -384,7 +465,7 @@ ffn_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                                 gave_up);
                 tc_fence_after_sync();
                 const uint32_t acc = tmem_base + static_cast<uint32_t>(buf * kAccCols);
-                for (int kb = 0; kb < k_blocks; ++kb) {
+                for (int kb = w.kb0; kb < w.kb1; ++kb) {
                     wait_or_give_up(smem_u32(&ctl.full[stage]), parity, status, gave_up);
                     tc_fence_after_sync();
                     const uint32_t a_addr = smem_u32(tiles + stage * kStageBytes);
@@ -393,7 +474,7 @@ ffn_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 #pragma unroll
                     for (int k = 0; k < kBK / kUmmaK; ++k) {
                         // advance 16 bf16 = 32 bytes inside the swizzle row: +2 in the address field
-                        umma_bf16<CG>(acc, desc_a + 2u * k, desc_b + 2u * k, idesc, (kb | k) != 0 ? 1u : 0u);
+                        umma_bf16<CG>(acc, desc_a + 2u * k, desc_b + 2u * k, idesc, (kb != w.kb0 || k != 0) ? 1u : 0u);
                     }
                     // stage reusable (in both CTAs) when these MMAs are done
                     if (PAIR)
@@ -416,18 +497,19 @@ ffn_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         // epilogue warps 2..5: warp w may touch TMEM lanes 32 * (w % 4) .. +31
         const int quarter = warp & 3;
         const int row_in_tile = quarter * 32 + lane;
-        int it = 0;
-        for (int w = walk.begin; w < walk.end; w += walk.step, ++it) {
+        TileWalk walk = walk0;
+        WorkItem w;
+        int exchanges = 0;   // row-norm exchanges done: selects the slot buffer and its barrier phase
+        for (int it = 0; walk.pop(w); ++it) {
             int m_tile, n_tile;
-            walk.locate(w, m_tile, n_tile);
+            walk.locate(w.tile, m_tile, n_tile);
             const int buf = it & 1;
-            const uint32_t phase = (static_cast<uint32_t>(it) >> 1) & 1u;
             const size_t row = static_cast<size_t>(m_tile) * kTileRows + half * kBM + row_in_tile;
             const size_t col0 = static_cast<size_t>(n_tile) * kBN;
             const uint32_t lane_base =
                 tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(buf * kAccCols);
             __nv_bfloat16* dst = out + row * n_total + col0;
-            wait_or_give_up(smem_u32(&ctl.acc_full[buf]), phase, status, gave_up);
+            wait_or_give_up(smem_u32(&ctl.acc_full[buf]), (static_cast<uint32_t>(it) >> 1) & 1u, status, gave_up);
             tc_fence_after_sync();
 
             if (!NORM_EPILOGUE) {
@@ -440,10 +522,35 @@ ffn_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 #pragma unroll
                     for (int i = 0; i < 32; i += 8) *reinterpret_cast<uint4*>(dst + c + i) = pack8(v + i);
                 }
+            } else if (w.kb0 != 0) {
+                // HELPER: the raw partial tile goes to this cluster's slot, then the flag of this
+                // column tile is raised for the owner's CTA of the same rank
+                float* slot = partials + static_cast<size_t>(cluster_id) * nranks * (kBM * kBN);
+#pragma unroll 1
+                for (int c = 0; c < kBN; c += 32) {
+                    float v[32];
+                    tmem_load_32x32(lane_base + c, v);
+#pragma unroll
+                    for (int g = 0; g < 8; ++g)
+                        *reinterpret_cast<float4*>(slot + partial_offset(rank, c / 32, g, row_in_tile)) =
+                            make_float4(v[4 * g], v[4 * g + 1], v[4 * g + 2], v[4 * g + 3]);
+                }
+                __threadfence();
+                asm volatile("bar.sync 1, %0;" ::"n"(kEpilogueThreads) : "memory");   // the epilogue warps only
+                if (threadIdx.x == 64) atomicExch(&flags[cluster_id * kMaxRowClusters + static_cast<int>(rank)], 1);
             } else {
+                // FULL tile, or OWNER of a shared one (then the helpers are the next group - 1 clusters)
+                const int helpers = w.kb1 != k_blocks ? group - 1 : 0;
+                const size_t slot_floats = static_cast<size_t>(nranks) * (kBM * kBN);
+                const float* part = partials + static_cast<size_t>(cluster_id + 1) * slot_floats;
+                for (int hlp = 1; hlp <= helpers; ++hlp)
+                    wait_flag(&flags[(cluster_id + hlp) * kMaxRowClusters + static_cast<int>(rank)], status, gave_up);
+                const int sbuf = exchanges & 1;
+                const uint32_t sphase = (static_cast<uint32_t>(exchanges) >> 1) & 1u;
+                ++exchanges;
                 const __nv_bfloat16* res = residual + row * n_total + col0;
-                float* slots = row_slots + buf * kSlotBufferFloats + row_in_tile * kMaxRowClusters;
-                const uint32_t ready = smem_u32(&ctl.slots_ready[buf]);
+                float* slots = row_slots + sbuf * kSlotBufferFloats + row_in_tile * kMaxRowClusters;
+                const uint32_t ready = smem_u32(&ctl.slots_ready[sbuf]);
                 // this CTA will receive one float per row from every CTA of the cluster (itself included)
                 if (threadIdx.x == 64) mbar_arrive_expect_tx(ready, nranks * kBM * static_cast<uint32_t>(sizeof(float)));
                 // pass 1: sum of squares of z = acc + residual over this CTA's 256 columns of the row
@@ -452,6 +559,17 @@ ffn_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 for (int c = 0; c < kBN; c += 32) {
                     float v[32];
                     tmem_load_32x32(lane_base + c, v);
+                    for (int hlp = 0; hlp < helpers; ++hlp) {
+#pragma unroll
+                        for (int g = 0; g < 8; ++g) {
+                            const float4 q = __ldcg(reinterpret_cast<const float4*>(
+                                part + hlp * slot_floats + partial_offset(rank, c / 32, g, row_in_tile)));
+                            v[4 * g] += q.x;
+                            v[4 * g + 1] += q.y;
+                            v[4 * g + 2] += q.z;
+                            v[4 * g + 3] += q.w;
+                        }
+                    }
 #pragma unroll
                     for (int i = 0; i < 32; i += 8) {
                         float r8[8];
@@ -466,7 +584,7 @@ ffn_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 // every CTA of the cluster gets every CTA's partial of every row
                 for (uint32_t p = 0; p < nranks; ++p)
                     st_async_f32(map_to_rank(smem_u32(&slots[rank]), p), ss, map_to_rank(ready, p));
-                wait_or_give_up(ready, phase, status, gave_up);
+                wait_or_give_up(ready, sphase, status, gave_up);
                 float total = 0.0f;
                 for (uint32_t p = 0; p < nranks; ++p) total += slots[p];
                 const float scale = rsqrtf(total / static_cast<float>(n_total) + eps);
@@ -475,6 +593,17 @@ ffn_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 for (int c = 0; c < kBN; c += 32) {
                     float v[32];
                     tmem_load_32x32(lane_base + c, v);
+                    for (int hlp = 0; hlp < helpers; ++hlp) {
+#pragma unroll
+                        for (int g = 0; g < 8; ++g) {
+                            const float4 q = __ldcg(reinterpret_cast<const float4*>(
+                                part + hlp * slot_floats + partial_offset(rank, c / 32, g, row_in_tile)));
+                            v[4 * g] += q.x;
+                            v[4 * g + 1] += q.y;
+                            v[4 * g + 2] += q.z;
+                            v[4 * g + 3] += q.w;
+                        }
+                    }
 #pragma unroll
                     for (int i = 0; i < 32; i += 8) {
                         float r8[8], g8[8];
@@ -487,7 +616,7 @@ ffn_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     }
                 }
             }
-            // accumulator `buf` may be overwritten by the MMAs of tile it + 2: one arrival per warp
+            // accumulator `buf` may be overwritten by the MMAs of item it + 2: one arrival per warp
             // on the barrier of the CTA that issues them
             tc_fence_before_sync();
             __syncwarp();
@@ -565,6 +694,16 @@ const char* ffn_check_shape(int64_t m, int64_t d, int64_t h) {
     return nullptr;
 }
 
+namespace {
+constexpr size_t kFlagBytes = static_cast<size_t>(kPartialSlots + 1) * kMaxRowClusters * sizeof(int);
+size_t ffn_partial_bytes(int64_t d) {
+    // one 128 x d fp32 partial tile per cluster (+ one never written: the last cluster owns nothing)
+    return static_cast<size_t>(kPartialSlots + 1) * kBM * static_cast<size_t>(d) * sizeof(float);
+}
+}  // namespace
+
+size_t ffn_scratch_bytes(int64_t d) { return ffn_partial_bytes(d) + kFlagBytes; }
+
 cudaError_t launch_ffn_pack_weight(const void* w, void* packed, int k, int n, cudaStream_t stream) {
     dim3 grid(static_cast<unsigned>((n + 31) / 32), static_cast<unsigned>((k + 31) / 32));
     pack_weight_kernel<<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(w),
@@ -604,7 +743,7 @@ int resident_clusters(const void* kernel, int cluster_size, int grid_clusters, i
 
 // Returns cudaSuccess, or an error; *bad_map is set when a tensor map could not be encoded.
 cudaError_t launch_ffn_forward(const void* x, const void* w1p, const void* w2p, const float* gamma, void* y,
-                               void* hidden, int m, int d, int h, float eps, int* status,
+                               void* hidden, void* scratch, int m, int d, int h, float eps, int* status,
                                cudaStream_t stream, bool* bad_map) {
     *bad_map = false;
     // CTA pairs need whole 256-row tiles; otherwise the first GEMM runs one CTA per MMA
@@ -662,13 +801,15 @@ cudaError_t launch_ffn_forward(const void* x, const void* w1p, const void* w2p, 
             cfg.numAttrs = 1;
             const __nv_bfloat16* no_res = nullptr;
             const float* no_gamma = nullptr;
+            float* no_partials = nullptr;
+            int* no_flags = nullptr;
             err = cudaLaunchKernelEx(&cfg, ffn_gemm_kernel<false, true>, map_x, map_w1, hid, no_res, no_gamma,
-                                     m_tiles / 2, n_tiles, h, d, 0.0f, status);
+                                     m_tiles / 2, n_tiles, h, d, 0.0f, no_partials, no_flags, status);
         } else {
             const int tiles = m_tiles * n_tiles;
             const unsigned grid = static_cast<unsigned>(tiles < sms ? tiles : sms);
             ffn_gemm_kernel<false, false><<<grid, kFfnThreads, kFfnSmemBytes, stream>>>(
-                map_x, map_w1, hid, nullptr, nullptr, m_tiles, n_tiles, h, d, 0.0f, status);
+                map_x, map_w1, hid, nullptr, nullptr, m_tiles, n_tiles, h, d, 0.0f, nullptr, nullptr, status);
             err = cudaGetLastError();
         }
         if (err != cudaSuccess) return err;
@@ -694,10 +835,21 @@ cudaError_t launch_ffn_forward(const void* x, const void* w1p, const void* w2p, 
                                                m_tiles, &cached_clusters[n_tiles]);
         const int clusters = (resident < 1 || resident > m_tiles) ? m_tiles : resident;
         cfg.gridDim = dim3(static_cast<unsigned>(n_tiles * clusters));
+        // Row blocks left over after the full rounds are shared by groups of clusters that split
+        // the k range (all clusters are resident, so an owner never waits for a helper that has
+        // not started).
+        float* partials = nullptr;
+        int* flags = nullptr;
+        if (resident >= 1 && clusters <= kPartialSlots && m_tiles % clusters != 0) {
+            partials = static_cast<float*>(scratch);
+            flags = reinterpret_cast<int*>(static_cast<unsigned char*>(scratch) + ffn_partial_bytes(d));
+            err = cudaMemsetAsync(flags, 0, kFlagBytes, stream);
+            if (err != cudaSuccess) return err;
+        }
         __nv_bfloat16* out = static_cast<__nv_bfloat16*>(y);
         const __nv_bfloat16* res = static_cast<const __nv_bfloat16*>(x);
         return cudaLaunchKernelEx(&cfg, ffn_gemm_kernel<true, false>, map_h, map_w2, out, res, gamma, m_tiles, n_tiles, d, h,
-                                  eps, status);
+                                  eps, partials, flags, status);
     }
 }
 

@@ -32,8 +32,10 @@ cudaError_t launch_layernorm_bwd_finish(const float* partials, float* dgamma, fl
 // shape is not supported.
 const char* ffn_check_shape(int64_t m, int64_t d, int64_t h);
 cudaError_t launch_ffn_pack_weight(const void* w, void* packed, int k, int n, cudaStream_t stream);
+// Scratch after the hidden activations: partial tiles and flags of the split row-block walk.
+size_t ffn_scratch_bytes(int64_t d);
 cudaError_t launch_ffn_forward(const void* x, const void* w1p, const void* w2p, const float* gamma, void* y,
-                               void* hidden, int m, int d, int h, float eps, int* status,
+                               void* hidden, void* scratch, int m, int d, int h, float eps, int* status,
                                cudaStream_t stream, bool* bad_map);
 
 }  // namespace credit

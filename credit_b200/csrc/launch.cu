@@ -751,7 +751,8 @@ int credit_ffn_pack_weight(const void* w, void* packed, int64_t k, int64_t n, vo
 
 size_t credit_ffn_workspace_bytes(int64_t m, int64_t d, int64_t h) {
     if (ffn_check_shape(m, d, h) != nullptr) return 0;
-    return static_cast<size_t>(m) * static_cast<size_t>(h) * 2;   // the hidden activations, bf16
+    // the hidden activations (bf16), then the scratch of the second GEMM
+    return static_cast<size_t>(m) * static_cast<size_t>(h) * 2 + ffn_scratch_bytes(d);
 }
 
 int credit_ffn_forward(const void* x, const void* w1_packed, const void* w2_packed, const float* gamma,
@@ -775,7 +776,8 @@ int credit_ffn_forward(const void* x, const void* w1_packed, const void* w2_pack
     if (st->info.sm_major != 10)
         return fail(CREDIT_ERR_UNSUPPORTED, "the FFN kernels need an sm_100 device (tcgen05)");
     bool bad_map = false;
-    cudaError_t err = launch_ffn_forward(x, w1_packed, w2_packed, gamma, y, workspace, static_cast<int>(m),
+    void* scratch = static_cast<unsigned char*>(workspace) + static_cast<size_t>(m) * static_cast<size_t>(h) * 2;
+    cudaError_t err = launch_ffn_forward(x, w1_packed, w2_packed, gamma, y, workspace, scratch, static_cast<int>(m),
                                          static_cast<int>(d), static_cast<int>(h), eps, st->status_ptr,
                                          static_cast<cudaStream_t>(stream), &bad_map);
     if (bad_map) return fail(CREDIT_ERR_CUDA, "could not encode a TMA tensor map for the FFN operands");
