@@ -40,9 +40,10 @@ ROWS, COLS = 512, 1048576
 WORKLOAD = "row_reduce fp32 [512, 1048576] -> sum, max, argmax(int64)"
 METRIC = "row_reduce_rows_per_s"
 FALLBACK_HBM_GBS = 6650.0
-# dram__bytes_read.sum + dram__bytes_write.sum of one full-size launch, from the ncu
-# capture summarised in profiles/ (None until one has been taken).
-NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+# dram__bytes_read.sum + dram__bytes_write.sum per full-size launch: the ncu capture summarised in
+# profiles/row_reduce_ncu_full.md was taken on 128 rows of the same width (536 888 064 B read +
+# 5 983 232 B written) and is scaled by 4 to the 512 rows of a launch (traffic is per row).
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 4 * (536_888_064 + 5_983_232)
 
 
 def measured_peaks() -> tuple[float, str]:
@@ -237,6 +238,28 @@ def time_other_workloads(torch, dev) -> dict:
             torch.cuda.empty_cache()
         except Exception as exc:  # report, do not hide
             out[name] = {"error": str(exc)[:200]}
+    # the fused FFN (tensor-bound): TFLOP/s against the measured dense bf16 peak
+    try:
+        m, d, h = 2048, 4096, 16384
+        x, w1, w2, gamma = W.make_ffn_inputs(m, d, dev, hidden=h)
+        w1p, w2p = L.pack_ffn_weight(w1), L.pack_ffn_weight(w2)
+        del w1, w2
+        y = torch.empty_like(x)
+        ws = torch.empty(L.ffn_workspace_bytes(m, d, h), dtype=torch.uint8, device=dev)
+        ms = timed(lambda: L.launch_ffn_forward((x, w1p, w2p, gamma), (y,), workspace=ws), 10)
+        tflops = W.ffn_flops(m, d, h) / ms / 1e9
+        entry = {"shape": [m, d, h], "dtype": "bfloat16", "ms": round(ms, 4), "tflops": round(tflops, 1),
+                 "rows_per_s": round(m / ms * 1e3, 1)}
+        peaks = ROOT / "MEASURED_PEAKS.json"
+        if peaks.exists():
+            burst = json.loads(peaks.read_text()).get("bf16_tflops")
+            if burst:
+                entry["frac_of_measured_bf16_burst"] = round(tflops / float(burst), 3)
+        out["ffn_forward"] = entry
+        del x, w1p, w2p, y, ws
+        torch.cuda.empty_cache()
+    except Exception as exc:
+        out["ffn_forward"] = {"error": str(exc)[:200]}
     return out
 
 
