@@ -34,6 +34,7 @@ LIB_SOURCES = [
     "tables_row_reduce.cu",
     "ffn_kernels.cu",
     "tables_block_read.cu",
+    "tables_row_ops.cu",
 ]
 OBJ_DIR = LIB_DIR / "obj"
 # name of the executable -> (source, links against the shared library)

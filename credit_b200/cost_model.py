@@ -119,11 +119,17 @@ class B200Calibration:
     sweeps); cycles are SM cycles at `clock_ghz`."""
     clock_ghz: float = 1.93                    # SM clock under these memory-bound kernels
     hbm_gbps: float = 6538.6                   # copy ceiling
-    chain_cycles_per_stage: float = 2500.0     # ring wait, LDS, shuffle trees, fold, push, wait, stores
+    chain_cycles_per_stage: float = 2200.0     # ring wait, LDS, shuffle trees, push, wait, stores
+    chain_cycles_per_warp: float = 25.0        # per stage: the CTA-local collection grows with its warps
     exchange_cycles: dict | None = None        # st.async + mbarrier all-to-all, per cluster size
-    cycles_per_element_per_thread: float = 9.0 # issue cost of one row element in one thread
+    cycles_per_element_per_thread: float = 14.0  # issue cost of one row element in one thread
     one_shot_cycles: float = 6000.0            # cluster launch + barrier set-up + first load, per row,
                                                # when every cluster handles a single row
+    generic_path_efficiency: float = 0.5       # slices too large for registers run on the shared-memory
+                                               # re-read kernels: about half of the copy ceiling
+    cta_launch_ns: float = 4.8                 # streaming kernels: CTA launch throughput of the device
+    launch_base_us: float = 3.0                # fixed cost of a launch
+    streaming_ctas_to_saturate: int = 320      # CTAs of the streaming reduction that fill HBM
 
     def exchange(self, cluster_size: int) -> float:
         table = self.exchange_cycles or {1: 150.0, 2: 315.0, 4: 322.0, 8: 351.0, 16: 420.0}
@@ -141,15 +147,20 @@ class ClusterPrediction:
 
 def predict_cluster_ms(rows: int, cols: int, cluster_size: int, resident_clusters: int, threads: int,
                        algorithmic_bytes: float, reduction_stages: int, persistent: bool = True,
-                       cal: B200Calibration = B200Calibration()) -> ClusterPrediction:
-    """Predicted time of one call of a register-path cluster kernel.
+                       cal: B200Calibration = B200Calibration(), register_path: bool = True) -> ClusterPrediction:
+    """Predicted time of one call of a cluster kernel.
     resident_clusters: clusters of this shape that are co-resident (credit_plan's num_clusters for a
-    persistent launch); threads: threads per CTA."""
+    persistent launch); threads: threads per CTA; register_path: the slice fits the register-resident
+    kernels (credit_plan's vectors_per_thread > 0), otherwise the shared-memory re-read kernels run."""
     if min(rows, cols, cluster_size, resident_clusters, threads) <= 0:
         raise ValueError("all sizes must be positive")
     hbm_ms = algorithmic_bytes / (cal.hbm_gbps * 1.0e6)
+    if not register_path:
+        rows_per_cluster = math.ceil(rows / resident_clusters)
+        return ClusterPrediction(cluster_size, hbm_ms, rows_per_cluster, 0.0, hbm_ms / cal.generic_path_efficiency)
     elems_per_thread = math.ceil(cols / cluster_size / threads)
-    chain = reduction_stages * (cal.chain_cycles_per_stage + cal.exchange(cluster_size))
+    chain = reduction_stages * (cal.chain_cycles_per_stage + cal.chain_cycles_per_warp * (threads // 32) +
+                                cal.exchange(cluster_size))
     period_cycles = chain + elems_per_thread * cal.cycles_per_element_per_thread
     if not persistent:
         period_cycles += cal.one_shot_cycles
@@ -157,6 +168,21 @@ def predict_cluster_ms(rows: int, cols: int, cluster_size: int, resident_cluster
     row_period_us = period_cycles / (cal.clock_ghz * 1.0e3)
     latency_ms = rows_per_cluster * row_period_us * 1.0e-3
     return ClusterPrediction(cluster_size, hbm_ms, rows_per_cluster, row_period_us, max(hbm_ms, latency_ms))
+
+
+def predict_streaming_ms(rows: int, cluster_size: int, algorithmic_bytes: float,
+                         cal: B200Calibration = B200Calibration()) -> ClusterPrediction:
+    """Predicted time of the streaming row reduction (nothing staged, one cluster per row):
+    HBM time, stretched when rows x P CTAs are too few to keep HBM busy, or the time the device
+    needs to launch that many CTAs, whichever is longer."""
+    if min(rows, cluster_size) <= 0:
+        raise ValueError("all sizes must be positive")
+    hbm_ms = algorithmic_bytes / (cal.hbm_gbps * 1.0e6)
+    ctas = rows * cluster_size
+    fill = min(1.0, ctas / cal.streaming_ctas_to_saturate)
+    launch_ms = ctas * cal.cta_launch_ns * 1.0e-6
+    predicted = max(hbm_ms / fill, launch_ms) + cal.launch_base_us * 1.0e-3
+    return ClusterPrediction(cluster_size, hbm_ms, 1, 0.0, predicted)
 
 
 def best_cluster_size(predictions: list[ClusterPrediction]) -> int:

@@ -19,6 +19,9 @@ const void* layernorm_bwd_kernel_for(int dtype, int threads, int vpt, bool full,
 const void* row_reduce_kernel_for(int load_path, int threads, bool aligned);
 // One CTA of 512 threads per row, nothing staged (CREDIT_VARIANT_BLOCK_READ).
 const void* block_read_kernel_for(int workload, int dtype, bool aligned);
+// Reference-sweep workloads (CREDIT_WL_WEIGHTED_VAR_BACKWARD ... CREDIT_WL_ROWWISE_QUANT), fp32;
+// staged = false: the no-staging, one-CTA-per-row form.
+const void* row_op_kernel_for(int workload, bool aligned, bool staged);
 
 // Column sums of LayerNorm backward for shapes outside the register path, and
 // the finishing reduction over per-cluster (or per-row-block) partials.

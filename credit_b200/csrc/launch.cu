@@ -259,8 +259,13 @@ int check_opts(const credit_launch_opts* o, credit_launch_opts* out) {
 // ---------------------------------------------------------------------------
 // kernel selection (the tables live in one translation unit per kernel family)
 // ---------------------------------------------------------------------------
+bool is_row_op(int workload) {
+    return workload >= CREDIT_WL_WEIGHTED_VAR_BACKWARD && workload <= CREDIT_WL_ROWWISE_QUANT;
+}
+
 const void* workload_func(int workload, int dtype, const credit_plan_info& p, bool want_grads) {
     const bool al = p.aligned != 0;
+    if (is_row_op(workload)) return row_op_kernel_for(workload, al, p.variant != CREDIT_VARIANT_BLOCK_READ);
     if (p.variant == CREDIT_VARIANT_BLOCK_READ) return block_read_kernel_for(workload, dtype, al);
     const int vpt = p.vectors_per_thread;
     const bool full = p.full_tiles != 0;
@@ -301,9 +306,18 @@ int max_elems_per_thread(int workload, bool grads) {
 }
 
 int inputs_staged(int workload) {
-    return (workload == CREDIT_WL_LAYERNORM_BACKWARD || workload == CREDIT_WL_LAYERNORM_BACKWARD_STATS)
-               ? 2
-               : 1;
+    switch (workload) {
+        case CREDIT_WL_LAYERNORM_BACKWARD:
+        case CREDIT_WL_LAYERNORM_BACKWARD_STATS:
+        case CREDIT_WL_PEARSON_BACKWARD:
+        case CREDIT_WL_SOFTMAX_LOGITS_BACKWARD:
+            return 2;
+        case CREDIT_WL_WEIGHTED_VAR_BACKWARD:
+        case CREDIT_WL_LARS_MOMENTUM:
+            return 3;
+        default:
+            return 1;
+    }
 }
 
 // Resolves everything that does not need the occupancy query. `want_grads`
@@ -312,8 +326,10 @@ int plan_static(int workload, const Shape& s, int dtype, const credit_launch_opt
                 bool pointers_aligned, bool want_grads, const credit_device_info& dev,
                 credit_plan_info* p) {
     std::memset(p, 0, sizeof(*p));
-    if (workload < CREDIT_WL_RMSNORM_FORWARD || workload > CREDIT_WL_LAYERNORM_BACKWARD_STATS)
+    if (workload < CREDIT_WL_RMSNORM_FORWARD || workload > CREDIT_WL_ROWWISE_QUANT)
         return fail(CREDIT_ERR_INVALID_ARGUMENT, "unknown workload %d", workload);
+    if (is_row_op(workload) && dtype != CREDIT_F32)
+        return fail(CREDIT_ERR_INVALID_ARGUMENT, "the reference-sweep workloads take fp32 data");
     if (workload == CREDIT_WL_ROW_REDUCE && dtype != CREDIT_F32)
         return fail(CREDIT_ERR_INVALID_ARGUMENT, "row_reduce takes fp32 input");
     if (o.variant == CREDIT_VARIANT_BLOCK_READ && workload == CREDIT_WL_ROW_REDUCE)
@@ -368,12 +384,12 @@ int plan_static(int workload, const Shape& s, int dtype, const credit_launch_opt
     if (o.variant == CREDIT_VARIANT_BLOCK_READ) {
         // one CTA of 512 threads per row, no shared-memory staging, no cluster
         p->cluster_size = 1;
-        p->threads = 512;
+        p->threads = is_row_op(workload) ? 256 : 512;
         p->schedule = CREDIT_SCHEDULE_ROW_PER_CLUSTER;
         p->load_path = CREDIT_LOAD_LDG;
         p->slice_elems = round_up(s.cols, 64);
         p->stages = 0;
-        p->smem_bytes = 0;
+        p->smem_bytes = is_row_op(workload) ? kControlBytes : 0;   // reduction scratch
         return CREDIT_OK;
     }
 
@@ -733,6 +749,45 @@ int credit_layernorm_backward_stats(const void* x, const void* dy, const float* 
     }
     CREDIT_CUDA_TRY(launch_layernorm_bwd_finish(partials, dgamma, dbeta, r.shape.cols, num_partials, s));
     return CREDIT_OK;
+}
+
+// ---------------------------------------------------------------------------
+// reference-sweep workloads
+// ---------------------------------------------------------------------------
+int credit_row_op(int workload, const float* in0, const float* in1, const float* in2, const float* row_in,
+                  void* out0, void* out1, float* row_out, int64_t rows, int64_t cols,
+                  const credit_launch_opts* opts, void* stream) {
+    if (!is_row_op(workload))
+        return fail(CREDIT_ERR_INVALID_ARGUMENT, "credit_row_op: workload %d is not one of the reference-sweep workloads",
+                    workload);
+    const int nin = inputs_staged(workload);
+    const bool two_out = workload == CREDIT_WL_PEARSON_BACKWARD || workload == CREDIT_WL_LARS_MOMENTUM;
+    const bool needs_row_in = workload == CREDIT_WL_PEARSON_BACKWARD;
+    const bool needs_row_out = workload == CREDIT_WL_ROWWISE_QUANT;
+    const float* ins[3] = {in0, in1, in2};
+    for (int n = 0; n < 3; ++n) {
+        if (rows != 0 && (n < nin) != (ins[n] != nullptr))
+            return fail(CREDIT_ERR_INVALID_ARGUMENT, "credit_row_op: workload %d takes %d input arrays (in%d is %s)",
+                        workload, nin, n, ins[n] ? "given" : "NULL");
+    }
+    if (rows != 0 && (out0 == nullptr || two_out != (out1 != nullptr) || needs_row_in != (row_in != nullptr) ||
+                      needs_row_out != (row_out != nullptr)))
+        return fail(CREDIT_ERR_INVALID_ARGUMENT, "credit_row_op: wrong set of output / per-row pointers for workload %d",
+                    workload);
+    const bool al = aligned16(in0) && aligned16(in1) && aligned16(in2) && aligned16(out0) && aligned16(out1);
+    Resolved r;
+    int rc = resolve(workload, rows, cols, CREDIT_F32, opts, al, false, &r);
+    if (rc != CREDIT_OK) return rc;
+    if (r.shape.rows == 0) return CREDIT_OK;
+    RowOpArgs io;
+    for (int n = 0; n < 3; ++n) io.in[n] = ins[n];
+    io.row_in = row_in;
+    io.out[0] = out0;
+    io.out[1] = out1;
+    io.row_out = row_out;
+    StagedArgs a = staged_args(r);
+    void* args[] = {&io, &a};
+    return launch_cluster_kernel(make_launch(r, stream), args);
 }
 
 // ---------------------------------------------------------------------------

@@ -25,6 +25,15 @@ struct StagedArgs {
     int* status;        // device status word
 };
 
+// Pointers of a reference-sweep workload (weighted variance, Pearson, softmax
+// backward, LARS, int8 quantisation).
+struct RowOpArgs {
+    const float* in[3];     // row-major [rows, cols] inputs
+    const float* row_in;    // per-row input (Pearson: upstream gradient [rows]) or NULL
+    void* out[2];           // row-major outputs: fp32, or int8 for the quantiser
+    float* row_out;         // per-row output (quantiser: scale [rows]) or NULL
+};
+
 // Geometry of the streaming row reduction.
 struct ReduceArgs {
     int rows;

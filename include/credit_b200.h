@@ -108,7 +108,13 @@ typedef enum credit_workload {
     CREDIT_WL_ROW_REDUCE = 1,
     CREDIT_WL_LAYERNORM_FORWARD = 2,
     CREDIT_WL_LAYERNORM_BACKWARD = 3,      /* statistics recomputed, dx only */
-    CREDIT_WL_LAYERNORM_BACKWARD_STATS = 4 /* statistics given, dx + dgamma + dbeta */
+    CREDIT_WL_LAYERNORM_BACKWARD_STATS = 4, /* statistics given, dx + dgamma + dbeta */
+    /* the other workloads of the reference sweep (fp32), through credit_row_op */
+    CREDIT_WL_WEIGHTED_VAR_BACKWARD = 5,
+    CREDIT_WL_PEARSON_BACKWARD = 6,
+    CREDIT_WL_SOFTMAX_LOGITS_BACKWARD = 7,
+    CREDIT_WL_LARS_MOMENTUM = 8,
+    CREDIT_WL_ROWWISE_QUANT = 9
 } credit_workload;
 
 /* What a call would launch: the resolved form of credit_launch_opts. */
@@ -195,6 +201,24 @@ int credit_layernorm_backward_stats(const void* x, const void* dy, const float* 
                                     float* dbeta, int64_t rows, int64_t cols, int dtype,
                                     const credit_launch_opts* opts, void* workspace,
                                     size_t workspace_bytes, void* stream);
+
+/* The other five workloads of the reference sweep, fp32, on the same cluster core
+ * (slices staged once in shared memory, partial sums / maxima exchanged through
+ * DSMEM, 2 to 3 dependent reductions). `workload` selects the formula:
+ *   CREDIT_WL_WEIGHTED_VAR_BACKWARD   in0 x, in1 weight, in2 dy        -> out0 dx
+ *       (weighted_var_backward.cu:426, dsmem_eval/workloads.py:72-87)
+ *   CREDIT_WL_PEARSON_BACKWARD        in0 x, in1 y, row_in grad [rows] -> out0 dx, out1 dy
+ *       (pearson_backward.cu:417, workloads.py:98-115)
+ *   CREDIT_WL_SOFTMAX_LOGITS_BACKWARD in0 logits, in1 dy               -> out0 dlogits
+ *       (softmax_logits_backward.cu:410, workloads.py:125-128)
+ *   CREDIT_WL_LARS_MOMENTUM           in0 weight, in1 grad, in2 momentum -> out0 weight', out1 update
+ *       (lars_momentum.cu:364, workloads.py:139-147)
+ *   CREDIT_WL_ROWWISE_QUANT           in0 x -> out0 int8 q [rows, cols], row_out scale [rows]
+ *       (rowwise_quant.cu:321, workloads.py:153-157)
+ * Unused pointers must be NULL. Inputs and outputs are [rows, cols] row-major. */
+int credit_row_op(int workload, const float* in0, const float* in1, const float* in2, const float* row_in,
+                  void* out0, void* out1, float* row_out, int64_t rows, int64_t cols,
+                  const credit_launch_opts* opts, void* stream);
 
 /* Fused FFN, bf16 with fp32 accumulation on the tensor cores:
  *   H = GELU(X W1)  (exact erf GELU, b1 = 0),  Y = RMSNorm(H W2 + X) * gamma.
