@@ -34,6 +34,11 @@ WL_ROW_REDUCE = 1
 WL_LAYERNORM_FORWARD = 2
 WL_LAYERNORM_BACKWARD = 3
 WL_LAYERNORM_BACKWARD_STATS = 4
+WL_WEIGHTED_VAR_BACKWARD = 5
+WL_PEARSON_BACKWARD = 6
+WL_SOFTMAX_LOGITS_BACKWARD = 7
+WL_LARS_MOMENTUM = 8
+WL_ROWWISE_QUANT = 9
 
 
 class CreditError(RuntimeError):
@@ -127,6 +132,9 @@ PROTOTYPES: dict[str, tuple] = {
     "credit_layernorm_backward_stats": (
         c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                 c_int64, c_int64, c_int, _OPTS_P, c_void_p, c_size_t, c_void_p]),
+    "credit_row_op": (
+        c_int, [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
+                _OPTS_P, c_void_p]),
     "credit_ffn_pack_weight": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_void_p]),
     "credit_ffn_workspace_bytes": (c_size_t, [c_int64, c_int64, c_int64]),
     "credit_ffn_forward": (

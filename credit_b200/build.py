@@ -46,7 +46,8 @@ CLI_SOURCES: dict[str, tuple[str, bool]] = {
 # workload_bench takes its workload from the name it is started under: it is
 # installed once per workload, as the reference has one executable per workload.
 WORKLOAD_BINARIES = ["layernorm_backward", "rmsnorm_forward", "row_reduce", "layernorm_forward",
-                     "layernorm_backward_stats"]
+                     "layernorm_backward_stats", "weighted_var_backward", "pearson_backward",
+                     "softmax_logits_backward", "lars_momentum", "rowwise_quant"]
 
 
 def nvcc_path() -> str:

@@ -61,7 +61,15 @@ const Workload kWorkloads[] = {
     {"row_reduce", CREDIT_WL_ROW_REDUCE, 512, CREDIT_F32},
     {"layernorm_forward", CREDIT_WL_LAYERNORM_FORWARD, 4096, CREDIT_BF16},
     {"layernorm_backward_stats", CREDIT_WL_LAYERNORM_BACKWARD_STATS, 8192, CREDIT_BF16},
+    // the rest of the reference sweep (rows as in dsmem_eval/workloads.py:164-210), fp32 only
+    {"weighted_var_backward", CREDIT_WL_WEIGHTED_VAR_BACKWARD, 4096, CREDIT_F32},
+    {"pearson_backward", CREDIT_WL_PEARSON_BACKWARD, 4096, CREDIT_F32},
+    {"softmax_logits_backward", CREDIT_WL_SOFTMAX_LOGITS_BACKWARD, 4096, CREDIT_F32},
+    {"lars_momentum", CREDIT_WL_LARS_MOMENTUM, 4096, CREDIT_F32},
+    {"rowwise_quant", CREDIT_WL_ROWWISE_QUANT, 4096, CREDIT_F32},
 };
+
+bool is_row_op(int id) { return id >= CREDIT_WL_WEIGHTED_VAR_BACKWARD && id <= CREDIT_WL_ROWWISE_QUANT; }
 
 std::vector<int> parse_int_list(const std::string& text) {
     std::vector<int> values;
@@ -360,6 +368,212 @@ void print_result(int cols, int rows, const VariantResult& block, const VariantR
     else std::printf("%g\n", ratio);
 }
 
+// ---- the reference sweep's other workloads (credit_row_op) ---------------------------------
+// Values in [low, high) with 1/2048 granularity from an index hash; `salt` separates the arrays.
+__global__ void init_uniform_kernel(float* a, size_t elements, float low, float high, unsigned salt) {
+    const size_t idx = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (idx >= elements) return;
+    const unsigned h = static_cast<unsigned>(((idx + salt) * 1103515245ull + 12345ull + 7919ull * salt) >> 16);
+    a[idx] = low + static_cast<float>(h & 2047u) * ((high - low) / 2048.0f);
+}
+
+struct RowOpShape {
+    int nin, nout;
+    bool row_in, row_out;
+    float low[3], high[3];     // input ranges of the reference factories (workloads.py:64-150)
+    double bytes_per_elem;     // compulsory traffic: every input read once, every output written once
+    double tol;
+};
+
+RowOpShape row_op_shape(int id) {
+    switch (id) {
+        case CREDIT_WL_WEIGHTED_VAR_BACKWARD: return {3, 1, false, false, {-2.0f, 0.5f, -1.0f}, {2.0f, 1.5f, 1.0f}, 16.0, 3.0e-2};
+        case CREDIT_WL_PEARSON_BACKWARD: return {2, 2, true, false, {-1.0f, -1.0f, 0.0f}, {1.0f, 1.0f, 0.0f}, 16.0, 3.0e-3};
+        case CREDIT_WL_SOFTMAX_LOGITS_BACKWARD: return {2, 1, false, false, {-4.0f, -1.0f, 0.0f}, {4.0f, 1.0f, 0.0f}, 12.0, 3.0e-3};
+        case CREDIT_WL_LARS_MOMENTUM: return {3, 2, false, false, {-1.0f, -1.0f, -1.0f}, {1.0f, 1.0f, 1.0f}, 20.0, 3.0e-3};
+        default: return {1, 1, false, true, {-1.0f, 0.0f, 0.0f}, {1.0f, 0.0f, 0.0f}, 5.0, 1.0e-6};
+    }
+}
+
+struct RowOpBuffers {
+    float* in[3] = {nullptr, nullptr, nullptr};
+    void* out[2] = {nullptr, nullptr};
+    float *row_in = nullptr, *row_out = nullptr;
+};
+
+int call_row_op(int id, const RowOpBuffers& b, int rows, int cols, const credit_launch_opts& o) {
+    return credit_row_op(id, b.in[0], b.in[1], b.in[2], b.row_in, b.out[0], b.out[1], b.row_out, rows, cols, &o, nullptr);
+}
+
+VariantResult time_row_op(const char* name, int id, const RowOpBuffers& b, int rows, int cols,
+                          const credit_launch_opts& o, const Options& opts, double bytes) {
+    VariantResult r;
+    r.name = name;
+    int rc = call_row_op(id, b, rows, cols, o);
+    if (rc == CREDIT_ERR_UNSUPPORTED) return r;
+    if (rc != CREDIT_OK) throw std::runtime_error(std::string(name) + ": " + credit_last_error());
+    for (int i = 1; i < opts.warmup; ++i) call_row_op(id, b, rows, cols, o);
+    CUDA_OK(cudaDeviceSynchronize());
+    cudaEvent_t start, stop;
+    CUDA_OK(cudaEventCreate(&start));
+    CUDA_OK(cudaEventCreate(&stop));
+    CUDA_OK(cudaEventRecord(start));
+    for (int i = 0; i < opts.iters; ++i) call_row_op(id, b, rows, cols, o);
+    CUDA_OK(cudaEventRecord(stop));
+    CUDA_OK(cudaEventSynchronize(stop));
+    float ms = 0.0f;
+    CUDA_OK(cudaEventElapsedTime(&ms, start, stop));
+    CUDA_OK(cudaEventDestroy(start));
+    CUDA_OK(cudaEventDestroy(stop));
+    int status = 0;
+    if (credit_device_status(&status, 1) != CREDIT_OK)
+        throw std::runtime_error(std::string(name) + ": " + credit_last_error());
+    r.valid = true;
+    r.avg_ms = static_cast<double>(ms) / opts.iters;
+    r.gbps = bytes / (r.avg_ms / 1000.0) / 1.0e9;
+    return r;
+}
+
+// fp64 recomputation of sampled rows on the host (verify_output_samples of the reference binaries).
+void verify_row_op(int id, const RowOpBuffers& b, const RowOpShape& sh, int rows, int cols, const char* label) {
+    const auto sample_rows = unique_samples({0, rows / 2, rows - 1}, rows);
+    const auto sample_cols = unique_samples({0, cols / 7, cols / 2, cols - 1}, cols);
+    for (int row : sample_rows) {
+        std::vector<double> in[3], out[2];
+        for (int n = 0; n < sh.nin; ++n) in[n] = fetch_row(b.in[n], CREDIT_F32, row, cols);
+        const auto& x = in[0];
+        auto check = [&](int k, int c, double ref) {
+            float got = 0.0f;
+            CUDA_OK(cudaMemcpy(&got, static_cast<const float*>(b.out[k]) + static_cast<size_t>(row) * cols + c,
+                               sizeof(float), cudaMemcpyDeviceToHost));
+            expect_close(got, ref, sh.tol, label, k == 0 ? "out0" : "out1", row, c);
+        };
+        if (id == CREDIT_WL_WEIGHTED_VAR_BACKWARD) {
+            const auto &w = in[1], &dy = in[2];
+            double sw = 0, swx = 0;
+            for (int c = 0; c < cols; ++c) { sw += w[c]; swx += w[c] * x[c]; }
+            const double inv_w = 1.0 / (sw + 1.0e-5), mean = swx * inv_w;
+            double var = 0, s_dy = 0, s_dyd = 0;
+            for (int c = 0; c < cols; ++c) {
+                const double d = x[c] - mean;
+                var += w[c] * d * d; s_dy += dy[c]; s_dyd += dy[c] * d;
+            }
+            const double rstd = 1.0 / std::sqrt(var * inv_w + 1.0e-5);
+            for (int c : sample_cols) {
+                const double d = x[c] - mean;
+                check(0, c, rstd * (dy[c] - w[c] * inv_w * s_dy - w[c] * d * rstd * rstd * inv_w * s_dyd));
+            }
+        } else if (id == CREDIT_WL_PEARSON_BACKWARD) {
+            const auto& y = in[1];
+            const double grad = fetch_floats(b.row_in + row, 1)[0];
+            double mx = 0, my = 0;
+            for (int c = 0; c < cols; ++c) { mx += x[c]; my += y[c]; }
+            mx /= cols; my /= cols;
+            double vx = 0, vy = 0, cov = 0;
+            for (int c = 0; c < cols; ++c) {
+                const double xc = x[c] - mx, yc = y[c] - my;
+                vx += xc * xc; vy += yc * yc; cov += xc * yc;
+            }
+            const double ix = 1.0 / std::sqrt(vx + 1.0e-6), iy = 1.0 / std::sqrt(vy + 1.0e-6);
+            for (int c : sample_cols) {
+                const double xc = x[c] - mx, yc = y[c] - my;
+                check(0, c, grad * (yc * ix * iy - xc * cov * ix * ix * ix * iy));
+                check(1, c, grad * (xc * ix * iy - yc * cov * ix * iy * iy * iy));
+            }
+        } else if (id == CREDIT_WL_SOFTMAX_LOGITS_BACKWARD) {
+            const auto& dy = in[1];
+            double mx = -std::numeric_limits<double>::infinity();
+            for (double v : x) mx = std::max(mx, v);
+            double sum = 0, dot = 0;
+            for (int c = 0; c < cols; ++c) sum += std::exp(x[c] - mx);
+            for (int c = 0; c < cols; ++c) dot += std::exp(x[c] - mx) / sum * dy[c];
+            for (int c : sample_cols) check(0, c, std::exp(x[c] - mx) / sum * (dy[c] - dot));
+        } else if (id == CREDIT_WL_LARS_MOMENTUM) {
+            const auto &g = in[1], &m = in[2];
+            double wn = 0, un = 0;
+            for (int c = 0; c < cols; ++c) {
+                const double u = 0.9 * m[c] + g[c] + 0.01 * x[c];
+                wn += x[c] * x[c]; un += u * u;
+            }
+            const double trust = 0.02 * std::sqrt(wn) / (std::sqrt(un) + 1.0e-6);
+            for (int c : sample_cols) {
+                const double u = 0.9 * m[c] + g[c] + 0.01 * x[c];
+                check(0, c, x[c] - 1.0e-3 * trust * u);
+                check(1, c, u);
+            }
+        } else {
+            double mx = 0;
+            for (double v : x) mx = std::max(mx, std::abs(v));
+            const double scale = fetch_floats(b.row_out + row, 1)[0];
+            expect_close(scale, mx / 127.0, 1.0e-6, label, "scale", row, 0);
+            const float inv = mx > 0 ? 127.0f / static_cast<float>(mx) : 0.0f;
+            for (int c : sample_cols) {
+                signed char q = 0;
+                CUDA_OK(cudaMemcpy(&q, static_cast<const signed char*>(b.out[0]) + static_cast<size_t>(row) * cols + c, 1,
+                                   cudaMemcpyDeviceToHost));
+                const float want = std::min(std::max(std::nearbyint(static_cast<float>(x[c]) * inv), -127.0f), 127.0f);
+                if (std::abs(static_cast<int>(q) - static_cast<int>(want)) > 1)
+                    throw std::runtime_error(std::string(label) + " verification failed for q row=" + std::to_string(row));
+            }
+        }
+    }
+}
+
+void run_row_op_shape(const Workload& w, int rows, int cols, int chosen, const Options& opts) {
+    const RowOpShape sh = row_op_shape(w.id);
+    const size_t elements = static_cast<size_t>(rows) * cols;
+    RowOpBuffers b;
+    const unsigned init_blocks = static_cast<unsigned>((elements + 255) / 256);
+    for (int n = 0; n < sh.nin; ++n) {
+        CUDA_OK(cudaMalloc(&b.in[n], elements * sizeof(float)));
+        init_uniform_kernel<<<init_blocks, 256>>>(b.in[n], elements, sh.low[n], sh.high[n], 17u * n + 1u);
+    }
+    const size_t out_elem = w.id == CREDIT_WL_ROWWISE_QUANT ? 1 : sizeof(float);
+    for (int k = 0; k < sh.nout; ++k) CUDA_OK(cudaMalloc(&b.out[k], elements * out_elem));
+    if (sh.row_in) {
+        CUDA_OK(cudaMalloc(&b.row_in, sizeof(float) * rows));
+        init_uniform_kernel<<<(rows + 255) / 256, 256>>>(b.row_in, rows, 0.75f, 1.25f, 101u);
+    }
+    if (sh.row_out) CUDA_OK(cudaMalloc(&b.row_out, sizeof(float) * rows));
+    CUDA_OK(cudaGetLastError());
+    CUDA_OK(cudaDeviceSynchronize());
+    const double bytes = sh.bytes_per_elem * static_cast<double>(elements);
+
+    VariantResult block, cluster;
+    credit_launch_opts o{};
+    if (opts.profile_variant != "cluster") {
+        o.variant = CREDIT_VARIANT_BLOCK_READ;
+        block = time_row_op("block_read", w.id, b, rows, cols, o, opts, bytes);
+        o = credit_launch_opts{};
+        o.variant = CREDIT_VARIANT_BLOCK_SMEM;
+        const VariantResult staged = time_row_op("block_smem", w.id, b, rows, cols, o, opts, bytes);
+        if (staged.valid && (!block.valid || staged.avg_ms < block.avg_ms)) block = staged;
+        if (block.valid && opts.verify) {
+            o = credit_launch_opts{};
+            o.variant = block.name == "block_smem" ? CREDIT_VARIANT_BLOCK_SMEM : CREDIT_VARIANT_BLOCK_READ;
+            call_row_op(w.id, b, rows, cols, o);
+            CUDA_OK(cudaDeviceSynchronize());
+            verify_row_op(w.id, b, sh, rows, cols, "block");
+        }
+    }
+    if (opts.profile_variant != "block" && chosen >= 2) {
+        o = credit_launch_opts{};
+        o.variant = CREDIT_VARIANT_CLUSTER_SMEM;
+        o.cluster_size = chosen;
+        cluster = time_row_op("cluster_smem", w.id, b, rows, cols, o, opts, bytes);
+        if (cluster.valid && opts.verify) {
+            call_row_op(w.id, b, rows, cols, o);
+            CUDA_OK(cudaDeviceSynchronize());
+            verify_row_op(w.id, b, sh, rows, cols, "cluster");
+        }
+    }
+    cluster.name = "cluster_smem";
+    print_result(cols, rows, block, cluster, chosen, opts.csv);
+    for (void* p : {static_cast<void*>(b.in[0]), static_cast<void*>(b.in[1]), static_cast<void*>(b.in[2]), b.out[0],
+                    b.out[1], static_cast<void*>(b.row_in), static_cast<void*>(b.row_out)})
+        if (p != nullptr) cudaFree(p);
+}
+
 void run_shape(const Workload& w, int dtype, int rows, int cols, int chosen, const Options& opts) {
     const int elem = dtype == CREDIT_F32 ? 4 : 2;
     const size_t elements = static_cast<size_t>(rows) * cols;
@@ -459,7 +673,8 @@ int main(int argc, char** argv) {
         if (w == nullptr) throw std::runtime_error("unknown workload: " + opts.workload);
         int dtype = w->default_dtype;
         if (!opts.dtype.empty()) dtype = opts.dtype == "f32" ? CREDIT_F32 : CREDIT_BF16;
-        if (w->id == CREDIT_WL_ROW_REDUCE && dtype != CREDIT_F32) throw std::runtime_error("row_reduce takes f32");
+        if ((w->id == CREDIT_WL_ROW_REDUCE || is_row_op(w->id)) && dtype != CREDIT_F32)
+            throw std::runtime_error(std::string(w->name) + " takes f32");
         const int rows = opts.rows > 0 ? opts.rows : w->default_rows;
 
         credit_device_info info{};
@@ -486,7 +701,10 @@ int main(int argc, char** argv) {
                         dtype == CREDIT_F32 ? "f32" : "bf16", rows, opts.warmup, opts.iters, chosen);
             std::printf("%8s%14s%12s%14s%12s%12s\n", "N", "block", "ms", "cluster", "ms", "c/b");
         }
-        for (int cols : opts.n_values) run_shape(*w, dtype, rows, cols, chosen, opts);
+        for (int cols : opts.n_values) {
+            if (is_row_op(w->id)) run_row_op_shape(*w, rows, cols, chosen, opts);
+            else run_shape(*w, dtype, rows, cols, chosen, opts);
+        }
         CUDA_OK(cudaDeviceSynchronize());
     } catch (const std::exception& exc) {
         std::fprintf(stderr, "error: %s\n", exc.what());

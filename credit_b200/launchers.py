@@ -204,6 +204,53 @@ def launch_ffn_forward(inputs, outputs, cluster_size: int = 0, opts=None, eps: f
             workspace.data_ptr(), workspace.numel(), _stream_ptr()))
 
 
+# name -> (workload id, staged inputs, per-row input?, row-major outputs, per-row output?)
+_ROW_OPS = {
+    "weighted_var_backward": (N.WL_WEIGHTED_VAR_BACKWARD, 3, False, 1, False),
+    "pearson_backward": (N.WL_PEARSON_BACKWARD, 2, True, 2, False),
+    "softmax_logits_backward": (N.WL_SOFTMAX_LOGITS_BACKWARD, 2, False, 1, False),
+    "lars_momentum": (N.WL_LARS_MOMENTUM, 3, False, 2, False),
+    "rowwise_quant": (N.WL_ROWWISE_QUANT, 1, False, 1, True),
+}
+
+
+def _make_row_op_launcher(name: str):
+    workload, nin, has_row_in, nout, has_row_out = _ROW_OPS[name]
+
+    def launch(inputs, outputs, cluster_size: int = 0, opts=None) -> None:
+        if len(inputs) != nin + int(has_row_in) or len(outputs) != nout + int(has_row_out):
+            raise ValueError(f"{name}: expected {nin + int(has_row_in)} inputs and {nout + int(has_row_out)} outputs")
+        x = inputs[0]
+        _check_matrix("input 0", x, torch.float32)
+        rows, cols = x.shape
+        for i in range(1, nin):
+            _check_matrix(f"input {i}", inputs[i], torch.float32, (rows, cols))
+        row_in = None
+        if has_row_in:      # the reference passes it as [rows, 1]
+            row_in = inputs[nin]
+            if row_in.numel() != rows:
+                raise ValueError(f"{name}: the per-row input must have {rows} elements")
+            _check_matrix("per-row input", row_in, torch.float32)
+        out_dtype = torch.int8 if name == "rowwise_quant" else torch.float32
+        for i in range(nout):
+            _check_matrix(f"output {i}", outputs[i], out_dtype, (rows, cols))
+        row_out = None
+        if has_row_out:
+            row_out = outputs[nout]
+            _check_matrix("per-row output", row_out, torch.float32, (rows,))
+        ptr = [t.data_ptr() if rows else None for t in inputs[:nin]] + [None] * (3 - nin)
+        N.check(N.load().credit_row_op(
+            workload, ptr[0], ptr[1], ptr[2], row_in.data_ptr() if has_row_in and rows else None,
+            outputs[0].data_ptr() if rows else None, outputs[1].data_ptr() if nout > 1 and rows else None,
+            row_out.data_ptr() if has_row_out and rows else None, rows, cols, _ref(_opts(cluster_size, opts)),
+            _stream_ptr()))
+
+    launch.__name__ = f"launch_{name}"
+    launch.__doc__ = (f"{name} of the reference sweep (dsmem_eval/workloads.py), fp32, through credit_row_op; "
+                      "same launcher convention as the others.")
+    return launch
+
+
 NATIVE_LAUNCHERS = {
     "rmsnorm_forward": launch_rmsnorm_forward,
     "row_reduce": launch_row_reduce,
@@ -211,6 +258,7 @@ NATIVE_LAUNCHERS = {
     "layernorm_backward": launch_layernorm_backward,
     "layernorm_backward_stats": launch_layernorm_backward_stats,
     "ffn_forward": launch_ffn_forward,
+    **{name: _make_row_op_launcher(name) for name in _ROW_OPS},
 }
 
 
@@ -237,6 +285,12 @@ def allocate_outputs(name: str, inputs: tuple[torch.Tensor, ...]) -> tuple[torch
             torch.empty(cols, device=dev, dtype=torch.float32),
             torch.empty(cols, device=dev, dtype=torch.float32),
         )
-    if name in ("rmsnorm_forward", "layernorm_backward", "ffn_forward"):
+    if name in ("rmsnorm_forward", "layernorm_backward", "ffn_forward", "weighted_var_backward",
+                "softmax_logits_backward"):
         return (torch.empty_like(x),)
+    if name in ("pearson_backward", "lars_momentum"):
+        return (torch.empty_like(x), torch.empty_like(x))
+    if name == "rowwise_quant":
+        return (torch.empty(rows, cols, device=dev, dtype=torch.int8),
+                torch.empty(rows, device=dev, dtype=torch.float32))
     raise KeyError(f"unknown workload {name!r}")

@@ -33,9 +33,11 @@ BIN_DIR = PACKAGE_DIR / "bin"
 DEFAULT_N_VALUES = (4096, 8192, 16384, 32768, 65536)
 DEFAULT_CLUSTER_SIZES = (2, 4, 8, 16)
 CLI_WORKLOADS = ("layernorm_backward", "rmsnorm_forward", "row_reduce", "layernorm_forward",
-                 "layernorm_backward_stats")
+                 "layernorm_backward_stats", "weighted_var_backward", "pearson_backward",
+                 "softmax_logits_backward", "lars_momentum", "rowwise_quant")
 _WORKLOAD_IDS = {"rmsnorm_forward": 0, "row_reduce": 1, "layernorm_forward": 2, "layernorm_backward": 3,
-                 "layernorm_backward_stats": 4}
+                 "layernorm_backward_stats": 4, "weighted_var_backward": 5, "pearson_backward": 6,
+                 "softmax_logits_backward": 7, "lars_momentum": 8, "rowwise_quant": 9}
 
 
 @dataclass(frozen=True)

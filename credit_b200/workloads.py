@@ -147,6 +147,34 @@ def make_ffn_inputs(rows: int, cols: int, device, seed: int = 0, hidden: int | N
     return x, w1, w2, gamma
 
 
+# Input factories of the reference sweep's other workloads (dsmem_eval/workloads.py:64-150):
+# same uniform ranges, seeded like the rest of this registry.
+def make_weighted_var_inputs(rows: int, cols: int, device, seed: int = 0) -> TensorTuple:
+    gen = _generator(device, seed)
+    return (_uniform((rows, cols), -2.0, 2.0, device, gen), _uniform((rows, cols), 0.5, 1.5, device, gen),
+            _uniform((rows, cols), -1.0, 1.0, device, gen))
+
+
+def make_pearson_inputs(rows: int, cols: int, device, seed: int = 0) -> TensorTuple:
+    gen = _generator(device, seed)
+    return (_uniform((rows, cols), -1.0, 1.0, device, gen), _uniform((rows, cols), -1.0, 1.0, device, gen),
+            _uniform((rows, 1), 0.75, 1.25, device, gen))
+
+
+def make_softmax_inputs(rows: int, cols: int, device, seed: int = 0) -> TensorTuple:
+    gen = _generator(device, seed)
+    return (_uniform((rows, cols), -4.0, 4.0, device, gen), _uniform((rows, cols), -1.0, 1.0, device, gen))
+
+
+def make_lars_inputs(rows: int, cols: int, device, seed: int = 0) -> TensorTuple:
+    gen = _generator(device, seed)
+    return tuple(_uniform((rows, cols), -1.0, 1.0, device, gen) for _ in range(3))
+
+
+def make_quant_inputs(rows: int, cols: int, device, seed: int = 0) -> TensorTuple:
+    return (_uniform((rows, cols), -1.0, 1.0, device, _generator(device, seed)),)
+
+
 def ffn_flops(rows: int, cols: int, hidden: int) -> int:
     return 2 * (2 * rows * cols * hidden)
 
@@ -203,6 +231,43 @@ WORKLOADS: dict[str, WorkloadSpec] = {
         # compulsory bytes with hidden = 4 * cols: X, W1, W2, Y (the hidden activations stay on chip
         # only in a fully fused kernel; this implementation also writes and reads them once)
         algorithmic_bytes=lambda r, c: 2 * r * c * 2 + 2 * c * 4 * c * 2 + c * 4,
+    ),
+    # the rest of the reference sweep: metadata of workload_metadata.py:17-34, tolerances of
+    # workloads.py:164-210
+    "weighted_var_backward": WorkloadSpec(
+        name="weighted_var_backward", label="Weighted variance backward", category="normalization",
+        rows=4096, cols=65536, dtype=torch.float32, input_factory=make_weighted_var_inputs, eps=1.0e-5,
+        modeled_bytes_per_element=40.0, reread_bytes_per_element=24.0, staged_bytes_per_element=12,
+        reductions_per_stage=(2, 3), atol=3.0e-2, rtol=3.0e-2,
+        algorithmic_bytes=lambda r, c: 4 * r * c * 4,
+    ),
+    "pearson_backward": WorkloadSpec(
+        name="pearson_backward", label="Pearson backward", category="pairwise statistics",
+        rows=4096, cols=65536, dtype=torch.float32, input_factory=make_pearson_inputs, eps=1.0e-6,
+        modeled_bytes_per_element=24.0, reread_bytes_per_element=8.0, staged_bytes_per_element=8,
+        reductions_per_stage=(2, 3), atol=3.0e-3, rtol=3.0e-3,
+        algorithmic_bytes=lambda r, c: 4 * r * c * 4 + r * 4,
+    ),
+    "softmax_logits_backward": WorkloadSpec(
+        name="softmax_logits_backward", label="Softmax-logits backward", category="softmax",
+        rows=4096, cols=65536, dtype=torch.float32, input_factory=make_softmax_inputs, eps=0.0,
+        modeled_bytes_per_element=28.0, reread_bytes_per_element=16.0, staged_bytes_per_element=8,
+        reductions_per_stage=(1, 1, 1), atol=3.0e-3, rtol=3.0e-3,
+        algorithmic_bytes=lambda r, c: 3 * r * c * 4,
+    ),
+    "lars_momentum": WorkloadSpec(
+        name="lars_momentum", label="LARS momentum", category="optimizer",
+        rows=4096, cols=65536, dtype=torch.float32, input_factory=make_lars_inputs, eps=1.0e-6,
+        modeled_bytes_per_element=32.0, reread_bytes_per_element=12.0, staged_bytes_per_element=12,
+        reductions_per_stage=(2,), atol=3.0e-3, rtol=3.0e-3,
+        algorithmic_bytes=lambda r, c: 5 * r * c * 4,
+    ),
+    "rowwise_quant": WorkloadSpec(
+        name="rowwise_quant", label="Row-wise int8 quantization", category="quantization",
+        rows=4096, cols=65536, dtype=torch.float32, input_factory=make_quant_inputs, eps=0.0,
+        modeled_bytes_per_element=9.0, reread_bytes_per_element=4.0, staged_bytes_per_element=4,
+        reductions_per_stage=(1,), atol=1.0e-6, rtol=1.0e-6,
+        algorithmic_bytes=lambda r, c: r * c * 5 + r * 4,
     ),
 }
 
