@@ -168,3 +168,53 @@ def test_build_summary(parsed):
 def test_require_binaries_names_what_is_missing(tmp_path):
     with pytest.raises(FileNotFoundError, match="cluster_control"):
         runner.require_binaries(tmp_path, ("row_reduce",))
+
+
+def test_generic_path_and_streaming_predictions(parsed):
+    cal = make_b200_calibration(parsed)
+    alg = 8192 * 65536 * 6.0
+    reg = cost_model.predict_cluster_ms(8192, 65536, 8, 15, 512, alg, 1, True, cal, register_path=True)
+    gen = cost_model.predict_cluster_ms(8192, 65536, 2, 74, 256, alg, 1, True, cal, register_path=False)
+    assert gen.predicted_ms == pytest.approx(gen.hbm_ms / cal.generic_path_efficiency)
+    assert cost_model.best_cluster_size([gen, reg]) == 8      # the re-read kernels lose to the register path
+    # streaming reduction: few CTAs cannot fill HBM, many CTAs cost launch time
+    few = cost_model.predict_streaming_ms(16, 2, 16 * 1048576 * 4.0, cal)
+    many = cost_model.predict_streaming_ms(16, 16, 16 * 1048576 * 4.0, cal)
+    assert many.predicted_ms < few.predicted_ms
+    tiny2 = cost_model.predict_streaming_ms(512, 2, 512 * 4096 * 4.0, cal)
+    tiny16 = cost_model.predict_streaming_ms(512, 16, 512 * 4096 * 4.0, cal)
+    assert tiny2.predicted_ms < tiny16.predicted_ms
+    with pytest.raises(ValueError):
+        cost_model.predict_streaming_ms(0, 2, 1.0, cal)
+
+
+def test_rescore_bundle_round_trip(tmp_path, parsed):
+    """A saved bundle is re-scored offline: same files in, summary and sweep rewritten."""
+    import csv
+    import json
+    from dataclasses import asdict
+
+    cfg = runner.RunConfig(workloads=("layernorm_backward_stats",), n_values=(65536,), cluster_sizes=(2, 8), trials=1)
+    (tmp_path / "metadata.json").write_text(json.dumps({"config": asdict(cfg)}))
+    (tmp_path / "primitive_stdout.txt").write_text((GOLDEN / "primitive_benchmark_b200.txt").read_text())
+    profile = make_device_profile(parsed, PROPS)
+    (tmp_path / "primitive_profile.json").write_text(json.dumps({"profile": asdict(profile)}))
+    raw = [{"workload": "layernorm_backward_stats", "cols": 65536, "rows": 8192, "trial": 0, "dtype": "bf16",
+            "block_variant": "block_read", "block_ms": 1.93, "cluster_variant": "cluster_smem", "cluster_ms": ms,
+            "cluster_size": p} for p, ms in ((2, 1.84), (8, 0.83))]
+    runner.write_csv(tmp_path / "cuda_raw.csv", raw)
+    runner.write_csv(tmp_path / "control_raw.csv", [
+        {"workload": "layernorm_backward_stats", "cols": 65536, "cluster_size": p, "delta_ms": 0.03} for p in (2, 8)])
+    runner.write_csv(tmp_path / "plans.csv", [
+        {"workload": "layernorm_backward_stats", "cols": 65536, "cluster_size": 2, "resident_clusters": 74,
+         "threads": 256, "register_path": 0},
+        {"workload": "layernorm_backward_stats", "cols": 65536, "cluster_size": 8, "resident_clusters": 15,
+         "threads": 512, "register_path": 1}])
+    result = runner.rescore_bundle(tmp_path)
+    assert result == {"points": 1, "b200_model_hits": 1, "b200_model_within_5pct": 1}
+    with (tmp_path / "summary.csv").open() as f:
+        (row,) = list(csv.DictReader(f))
+    assert row["measured_cluster_size"] == "8" and row["b200_predicted_cluster_size"] == "8"
+    with (tmp_path / "cluster_sweep.csv").open() as f:
+        sweep = list(csv.DictReader(f))
+    assert [r["register_path"] for r in sweep] == ["False", "True"]
