@@ -393,8 +393,10 @@ __device__ __forceinline__ float row_first_element(const T* x, int row, int cols
 // ---------------------------------------------------------------------------
 // LayerNorm forward
 // ---------------------------------------------------------------------------
+// 256-thread CTAs are held to 128 registers so that two of them (of different clusters, whose
+// phases drift apart) share an SM.
 template <typename T, int THREADS, int VPT, bool FULL>
-__global__ void __launch_bounds__(THREADS)
+__global__ void __launch_bounds__(THREADS, THREADS == 256 ? 2 : 1)
 layernorm_fwd_reg_kernel(const T* __restrict__ x, const float* __restrict__ gamma,
                          const float* __restrict__ beta, T* __restrict__ y,
                          float* __restrict__ mean_out, float* __restrict__ rstd_out, float eps,
@@ -502,7 +504,7 @@ layernorm_fwd_reg_kernel(const T* __restrict__ x, const float* __restrict__ gamm
 // fixed order (deterministic, no atomics).
 // ---------------------------------------------------------------------------
 template <typename T, int THREADS, int VPT, bool FULL, bool HAS_STATS, bool PARAM_GRADS>
-__global__ void __launch_bounds__(THREADS)
+__global__ void __launch_bounds__(THREADS, THREADS == 256 ? 2 : 1)
 layernorm_bwd_reg_kernel(const T* __restrict__ x, const T* __restrict__ dy,
                          const float* __restrict__ gamma, const float* __restrict__ mean_in,
                          const float* __restrict__ rstd_in, T* __restrict__ dx,
