@@ -135,6 +135,7 @@ PROTOTYPES: dict[str, tuple] = {
     "credit_row_op": (
         c_int, [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
                 _OPTS_P, c_void_p]),
+    "credit_bench": (c_int, [c_char_p, c_int64, c_int64, c_int, c_int, c_int, c_int, c_int, POINTER(ctypes.c_double)]),
     "credit_ffn_pack_weight": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_void_p]),
     "credit_ffn_workspace_bytes": (c_size_t, [c_int64, c_int64, c_int64]),
     "credit_ffn_forward": (

@@ -35,6 +35,7 @@ LIB_SOURCES = [
     "ffn_kernels.cu",
     "tables_block_read.cu",
     "tables_row_ops.cu",
+    "bench_entry.cu",
 ]
 OBJ_DIR = LIB_DIR / "obj"
 # name of the executable -> (source, links against the shared library)

@@ -13,8 +13,8 @@ taken from `DeviceProfile`.
 B200 the register-resident kernels are bound neither by the re-read the reference
 model counts nor by DSMEM store bandwidth; what was measured is
 
-    time(P) = max( HBM time of the compulsory bytes,
-                   rows / resident_clusters(P) * row_period(P) )
+    time(P) = smooth_max( HBM time of the compulsory bytes,
+                          rows / resident_clusters(P) * row_period(P) )
 
 where a cluster finishes one row every `row_period` = fixed latency chain (ring
 wait, shared-memory reads, shuffle trees, mbarrier exchange, stores: about 1.4 us
@@ -125,6 +125,7 @@ class B200Calibration:
     cycles_per_element_per_thread: float = 14.0  # issue cost of one row element in one thread
     one_shot_cycles: float = 6000.0            # cluster launch + barrier set-up + first load, per row,
                                                # when every cluster handles a single row
+    overlap_exponent: float = 3.0              # time = (hbm^k + latency^k)^(1/k)
     generic_path_efficiency: float = 0.5       # slices too large for registers run on the shared-memory
                                                # re-read kernels: about half of the copy ceiling
     cta_launch_ns: float = 4.8                 # streaming kernels: CTA launch throughput of the device
@@ -167,7 +168,11 @@ def predict_cluster_ms(rows: int, cols: int, cluster_size: int, resident_cluster
     rows_per_cluster = math.ceil(rows / resident_clusters)
     row_period_us = period_cycles / (cal.clock_ghz * 1.0e3)
     latency_ms = rows_per_cluster * row_period_us * 1.0e-3
-    return ClusterPrediction(cluster_size, hbm_ms, rows_per_cluster, row_period_us, max(hbm_ms, latency_ms))
+    # neither bound is reached exactly: the two overlap imperfectly (a cubic mean stays within a
+    # few per cent of max() when one term dominates)
+    k = cal.overlap_exponent
+    predicted = (hbm_ms ** k + latency_ms ** k) ** (1.0 / k)
+    return ClusterPrediction(cluster_size, hbm_ms, rows_per_cluster, row_period_us, predicted)
 
 
 def predict_streaming_ms(rows: int, cluster_size: int, algorithmic_bytes: float,

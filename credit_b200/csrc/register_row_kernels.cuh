@@ -581,6 +581,7 @@ layernorm_bwd_reg_kernel(const T* __restrict__ x, const T* __restrict__ dy,
     };
     auto front = [&](Regs& r, int it) {
         const int row = cluster + it * a.num_clusters;
+        CREDIT_TRACE_POINT(1, it);
         if (fills_ring && it > 0) filler.recycle(it);
         if (HAS_STATS) {
             r.mean = __ldg(mean_in + row);
@@ -590,6 +591,7 @@ layernorm_bwd_reg_kernel(const T* __restrict__ x, const T* __restrict__ dy,
             if (it + 1 < my_rows) next_shift = row_first_element(x, row + a.num_clusters, a.cols);
         }
         if (g.local > 0) mbar_wait_bounded(smem_u32(&ctl.full[ring.stage]), ring.parity, a.status);
+        CREDIT_TRACE_POINT(2, it);
         load_raw<THREADS, VPT, FULL>(
             reinterpret_cast<const uint4*>(stage_tile<T, 2>(data, ring.stage, 0, a.slice_elems)), nvec, r.x);
         load_raw<THREADS, VPT, FULL>(
@@ -602,9 +604,11 @@ layernorm_bwd_reg_kernel(const T* __restrict__ x, const T* __restrict__ dy,
             part[0] = warp_sum(part[0]);
             part[1] = warp_sum(part[1]);
         }
+        CREDIT_TRACE_POINT(4, it);
         if (g.local > 0 && (threadIdx.x & 31) == 0) mbar_arrive(smem_u32(&ctl.empty[ring.stage]));
         exchange_send<2, W>(part, ctl.ex, it, rank, nranks, a.status);
         ring.advance(a.stages);
+        CREDIT_TRACE_POINT(6, it);
     };
     // stats recomputed only: finish the statistics, start the exchange of S1, S2
     auto middle = [&](Regs& r, int it) {
@@ -621,7 +625,9 @@ layernorm_bwd_reg_kernel(const T* __restrict__ x, const T* __restrict__ dy,
     auto back = [&](const Regs& r, int it) {
         const int row = cluster + it * a.num_clusters;
         float sums[2];
+        CREDIT_TRACE_POINT(7, it);
         exchange_receive<2>(HAS_STATS ? ctl.ex : ctl.ex2, it, nranks, a.status, sums);
+        CREDIT_TRACE_POINT(8, it);
         const float2 neg_mean = splat(-r.mean), rstd2 = splat(r.rstd);
         const float2 ca = splat(-r.rstd * r.rstd * r.rstd * (sums[1] * inv_cols));
         const float2 cb = splat(-r.rstd * (sums[0] * inv_cols));
@@ -644,6 +650,7 @@ layernorm_bwd_reg_kernel(const T* __restrict__ x, const T* __restrict__ dy,
             }
             if (FULL || v < nvec) __stcs(out + v, PairVec<T>::pack(o));
         }
+        CREDIT_TRACE_POINT(9, it);
     };
 
     Regs r0, r1;

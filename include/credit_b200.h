@@ -220,6 +220,20 @@ int credit_row_op(int workload, const float* in0, const float* in1, const float*
                   void* out0, void* out1, float* row_out, int64_t rows, int64_t cols,
                   const credit_launch_opts* opts, void* stream);
 
+/* Times `iters` back-to-back calls of a workload (after `warmup` calls) with CUDA
+ * events, on device buffers this call allocates, fills with deterministic values and
+ * frees again; *avg_ms receives the time per call. `workload` is one of the ten
+ * names ("rmsnorm_forward", "row_reduce", "layernorm_forward", "layernorm_backward",
+ * "layernorm_backward_stats", "weighted_var_backward", "pearson_backward",
+ * "softmax_logits_backward", "lars_momentum", "rowwise_quant"); cluster_size 0 and
+ * variant CREDIT_VARIANT_AUTO let the planner choose. A variant that does not fit
+ * the shape returns CREDIT_ERR_UNSUPPORTED (the reference prints n/a). Replaces
+ * time_kernel + benchmark_block_read / benchmark_block_staged / benchmark_cluster of
+ * the reference binaries (layernorm_backward.cu:150-175, 480-593). Synchronous; not
+ * for use on a hot path. */
+int credit_bench(const char* workload, int64_t rows, int64_t cols, int dtype, int cluster_size, int variant,
+                 int warmup, int iters, double* avg_ms);
+
 /* Fused FFN, bf16 with fp32 accumulation on the tensor cores:
  *   H = GELU(X W1)  (exact erf GELU, b1 = 0),  Y = RMSNorm(H W2 + X) * gamma.
  * X, Y: bf16 [m, d]; gamma fp32 [d]; W1 [d, h] and W2 [h, d] are given PACKED
