@@ -508,3 +508,24 @@ def test_plan_and_device_query():
     assert p.grid_ctas == p.num_clusters * p.cluster_size
     p = N.plan(N.WL_ROW_REDUCE, 512, 1 << 20, N.F32)
     assert p.smem_bytes <= info.max_dynamic_smem_per_block
+
+
+def test_credit_bench_times_every_workload():
+    """The self-contained timing entry point: positive times, n/a reported as UNSUPPORTED."""
+    import ctypes
+    lib = N.load()
+    ms = ctypes.c_double(0.0)
+    names = ["rmsnorm_forward", "row_reduce", "layernorm_forward", "layernorm_backward", "layernorm_backward_stats",
+             "weighted_var_backward", "pearson_backward", "softmax_logits_backward", "lars_momentum", "rowwise_quant"]
+    for name in names:
+        for cluster, variant in ((0, N.VARIANT_AUTO), (4, N.VARIANT_CLUSTER_SMEM)):
+            rc = lib.credit_bench(name.encode(), 64, 8192, N.F32, cluster, variant, 2, 3, ctypes.byref(ms))
+            assert rc == N.CREDIT_OK, (name, cluster, lib.credit_last_error())
+            assert 0.0 < ms.value < 50.0
+    assert lib.credit_bench(b"layernorm_forward", 64, 8192, N.BF16, 8, N.VARIANT_CLUSTER_SMEM, 1, 2,
+                            ctypes.byref(ms)) == N.CREDIT_OK
+    # a staged single-CTA variant cannot hold a 1M-column row
+    assert lib.credit_bench(b"rmsnorm_forward", 4, 1048576, N.F32, 0, N.VARIANT_BLOCK_SMEM, 1, 1,
+                            ctypes.byref(ms)) == N.ERR_UNSUPPORTED
+    assert lib.credit_bench(b"no_such_workload", 4, 64, N.F32, 0, 0, 1, 1, ctypes.byref(ms)) == N.ERR_INVALID_ARGUMENT
+    assert lib.credit_bench(b"row_reduce", 4, 64, N.BF16, 0, 0, 1, 1, ctypes.byref(ms)) == N.ERR_INVALID_ARGUMENT
