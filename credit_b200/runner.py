@@ -134,6 +134,74 @@ def safe_ratio(numerator: float, denominator: float) -> float:
     return numerator / denominator
 
 
+def benchmark_callable(function, warmup: int, iterations: int, trials: int) -> list[float]:
+    """ms per call over `trials` event-timed batches of `iterations` calls (reference:
+    benchmark_callable, runner.py:166-182)."""
+    import torch
+
+    for _ in range(warmup):
+        function()
+    torch.cuda.synchronize()
+    samples: list[float] = []
+    for _ in range(trials):
+        start = torch.cuda.Event(enable_timing=True)
+        stop = torch.cuda.Event(enable_timing=True)
+        start.record()
+        for _ in range(iterations):
+            function()
+        stop.record()
+        stop.synchronize()
+        samples.append(start.elapsed_time(stop) / iterations)
+    return samples
+
+
+def assert_outputs_close(name: str, outputs, references, atol: float, rtol: float) -> list[dict[str, float | int]]:
+    """The reference's acceptance rule (runner.py:185-223): int8 outputs may differ by one at a rate
+    of at most 1e-5, everything else must pass allclose(atol, rtol). Returns its diagnostics."""
+    import torch
+
+    if len(outputs) != len(references):
+        raise RuntimeError(f"{name}: output count {len(outputs)} != reference count {len(references)}")
+    diagnostics: list[dict[str, float | int]] = []
+    for index, (output, reference) in enumerate(zip(outputs, references)):
+        if output.dtype == torch.int8:
+            difference = (output.to(torch.int16) - reference.to(torch.int16)).abs()
+            mismatch = int(torch.count_nonzero(difference).item())
+            maximum = int(difference.max().item()) if difference.numel() else 0
+            rate = mismatch / max(output.numel(), 1)
+            if maximum > 1 or rate > 1.0e-5:
+                raise RuntimeError(f"{name} output {index}: {mismatch} int8 mismatches ({rate:.3e}), "
+                                   f"maximum difference {maximum}")
+            diagnostics.append({"mismatch_count": mismatch, "mismatch_rate": rate, "max_integer_difference": maximum})
+            continue
+        reference = reference.to(output.dtype).reshape(output.shape)
+        max_error = float((output.float() - reference.float()).abs().max().item()) if output.numel() else 0.0
+        diagnostics.append({"max_abs_error": max_error})
+        if not torch.allclose(output, reference, atol=atol, rtol=rtol):
+            raise RuntimeError(f"{name} output {index}: max error {max_error} exceeds atol={atol}, rtol={rtol}")
+    return diagnostics
+
+
+def benchmark_native(name: str, rows: int, cols: int, warmup: int, iterations: int, trials: int,
+                     cluster_size: int = 0, opts: dict | None = None) -> dict[str, Any]:
+    """In-process arm (the native counterpart of benchmark_frameworks, runner.py:350-441): seeded
+    inputs of the registry on cuda:0, one launcher from NATIVE_LAUNCHERS, event timing."""
+    import torch
+
+    from .launchers import NATIVE_LAUNCHERS, allocate_outputs
+
+    spec = WORKLOADS[name]
+    inputs = spec.input_factory(rows, cols, torch.device("cuda:0"), seed=1234 + cols)
+    outputs = allocate_outputs(name, inputs)
+    launcher = NATIVE_LAUNCHERS[name]
+    samples = benchmark_callable(lambda: launcher(inputs, outputs, cluster_size, dict(opts or {})), warmup, iterations,
+                                 trials)
+    stats = summarize(samples)
+    return {"workload": name, "framework": "native", "rows": rows, "cols": cols, "cluster_size": cluster_size,
+            "ms": stats["median"], "p20_ms": stats["p20"], "p80_ms": stats["p80"],
+            "gbps": spec.algorithmic_bytes(rows, cols) / stats["median"] / 1.0e6, "samples": samples}
+
+
 def require_binaries(bin_dir: Path, selected: tuple[str, ...]) -> None:
     required = ["primitive_benchmark", "cluster_control", *selected]
     missing = [name for name in required if not (bin_dir / name).is_file()]

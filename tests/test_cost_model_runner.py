@@ -218,3 +218,21 @@ def test_rescore_bundle_round_trip(tmp_path, parsed):
     with (tmp_path / "cluster_sweep.csv").open() as f:
         sweep = list(csv.DictReader(f))
     assert [r["register_path"] for r in sweep] == ["False", "True"]
+
+
+def test_assert_outputs_close_rules():
+    import torch
+
+    a = torch.tensor([1.0, 2.0, 3.0])
+    assert runner.assert_outputs_close("w", (a,), (a + 1e-7,), 1e-6, 1e-6)[0]["max_abs_error"] < 1e-6
+    with pytest.raises(RuntimeError, match="exceeds"):
+        runner.assert_outputs_close("w", (a,), (a + 1e-2,), 1e-6, 1e-6)
+    with pytest.raises(RuntimeError, match="output count"):
+        runner.assert_outputs_close("w", (a,), (a, a), 1e-6, 1e-6)
+    q = torch.zeros(200000, dtype=torch.int8)
+    r = q.clone()
+    r[0] = 1                                      # one off-by-one in 200k: rate 5e-6 is accepted
+    assert runner.assert_outputs_close("q", (q,), (r,), 0, 0)[0]["mismatch_count"] == 1
+    r[1] = 2                                      # a difference of two is not
+    with pytest.raises(RuntimeError, match="int8 mismatches"):
+        runner.assert_outputs_close("q", (q,), (r,), 0, 0)

@@ -529,3 +529,12 @@ def test_credit_bench_times_every_workload():
                             ctypes.byref(ms)) == N.ERR_UNSUPPORTED
     assert lib.credit_bench(b"no_such_workload", 4, 64, N.F32, 0, 0, 1, 1, ctypes.byref(ms)) == N.ERR_INVALID_ARGUMENT
     assert lib.credit_bench(b"row_reduce", 4, 64, N.BF16, 0, 0, 1, 1, ctypes.byref(ms)) == N.ERR_INVALID_ARGUMENT
+
+
+def test_runner_in_process_arm():
+    from credit_b200 import runner
+
+    res = runner.benchmark_native("layernorm_backward", 128, 8192, warmup=2, iterations=5, trials=2, cluster_size=4)
+    assert res["framework"] == "native" and 0.0 < res["ms"] < 10.0 and len(res["samples"]) == 2
+    res = runner.benchmark_native("rowwise_quant", 64, 4096, warmup=1, iterations=3, trials=1)
+    assert res["gbps"] > 0.0
