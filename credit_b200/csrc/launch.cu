@@ -299,8 +299,11 @@ int max_elems_per_thread(int workload, bool grads) {
     switch (workload) {
         case CREDIT_WL_RMSNORM_FORWARD: return 32;
         case CREDIT_WL_LAYERNORM_FORWARD: return 32;
-        case CREDIT_WL_LAYERNORM_BACKWARD: return 16;
-        case CREDIT_WL_LAYERNORM_BACKWARD_STATS: return grads ? 16 : 16;
+        // up to 16 elements are held in registers across the exchange; 17..32 are read from the
+        // shared-memory stage a second time instead (the stage then lives one row longer)
+        // (with the column sums in registers as well, 32 elements spill: measured slower)
+        case CREDIT_WL_LAYERNORM_BACKWARD: return 32;
+        case CREDIT_WL_LAYERNORM_BACKWARD_STATS: return grads ? 16 : 32;
         default: return 0;
     }
 }
@@ -409,11 +412,14 @@ int plan_static(int workload, const Shape& s, int dtype, const credit_launch_opt
         // Smallest cluster whose slice fits the stage budget and, for aligned rows,
         // the register path at 512 threads.
         cluster = o.variant == CREDIT_VARIANT_CLUSTER_SMEM ? 2 : 1;
+        // LayerNorm backward without column sums: measured best (fp32 and bf16, N = 16K ... 128K) is
+        // the smallest cluster whose slice fits 256 threads x 32 elements, read twice from its stage
+        const bool two_reads = nin == 2 && !grads && p->aligned && !(o.flags & CREDIT_FLAG_NO_REGISTER_PATH);
         auto fits = [&](int c) {
-            if (stage_bytes_for(c) > kAutoStageBytes) return false;
+            if (stage_bytes_for(c) > (two_reads ? 2 : 1) * kAutoStageBytes) return false;
             if (!p->aligned || (o.flags & CREDIT_FLAG_NO_REGISTER_PATH)) return true;
             const int nvec = round_up((s.cols + c - 1) / c, 64) / s.vec_elems;
-            const int threads = o.threads ? o.threads : 512;
+            const int threads = o.threads ? o.threads : (two_reads ? 256 : 512);
             return nvec <= threads * (max_elems_per_thread(workload, grads) / s.vec_elems);
         };
         while (cluster < max_cluster && !fits(cluster)) cluster *= 2;
@@ -439,7 +445,11 @@ int plan_static(int workload, const Shape& s, int dtype, const credit_launch_opt
         if (threads == 0) threads = nvec > 256 * max_vpt ? 512 : 256;
         int vpt = 1;
         while (vpt * threads < nvec) vpt *= 2;
-        if (vpt <= max_vpt) {
+        // slices read twice from their stage need three stages; a caller who asks for fewer gets
+        // the shared-memory kernels instead
+        const bool two_reads = inputs_staged(workload) == 2 && vpt * s.vec_elems > 16;
+        const bool three_fit = kControlBytes + 3 * stage_bytes <= max_smem;
+        if (vpt <= max_vpt && !(two_reads && (o.stages == 1 || o.stages == 2 || !three_fit))) {
             p->threads = threads;
             p->vectors_per_thread = vpt;
             p->full_tiles = (vpt * threads == nvec && 1ll * p->slice_elems * cluster == s.cols) ? 1 : 0;
@@ -463,6 +473,8 @@ int plan_static(int workload, const Shape& s, int dtype, const credit_launch_opt
                                            : std::max(1, std::min(4, kAutoRingBytes / stage_bytes));
         while (stages > 1 && control_bytes + stages * stage_bytes > max_smem) --stages;
     }
+    const bool backward = workload == CREDIT_WL_LAYERNORM_BACKWARD || workload == CREDIT_WL_LAYERNORM_BACKWARD_STATS;
+    if (backward && p->vectors_per_thread * s.vec_elems > 16 && stages < 3) stages = 3;
     p->stages = stages;
     p->smem_bytes = control_bytes + stages * stage_bytes;
     if (p->smem_bytes > max_smem)

@@ -218,11 +218,15 @@ struct RingFiller {
         for (int n = 0; n < a.stages && n < my_rows; ++n)
             issue_slice_fill<T, NIN>(src, data, ctl.full, n, cluster + n * a.num_clusters, a, g);
     }
-    __device__ __forceinline__ void recycle(int it) const {
-        const int n = it - 1 + a.stages;
-        if (g.local == 0 || n >= my_rows) return;
-        const int stage = (it - 1) % a.stages;
-        const uint32_t parity = static_cast<uint32_t>((it - 1) / a.stages) & 1u;
+    // `lag`: how many rows back the stage to refill was used. 1: stages are released as soon as
+    // a row is in registers; 2: a row's stage stays in use until its outputs are written (kernels
+    // that read the row from shared memory twice), so the one to refill is that of row it - 2.
+    __device__ __forceinline__ void recycle(int it, int lag = 1) const {
+        const int freed = it - lag;
+        const int n = freed + a.stages;
+        if (g.local == 0 || freed < 0 || n >= my_rows) return;
+        const int stage = freed % a.stages;
+        const uint32_t parity = static_cast<uint32_t>(freed / a.stages) & 1u;
         mbar_wait_bounded(smem_u32(&ctl.empty[stage]), parity, a.status);
         issue_slice_fill<T, NIN>(src, data, ctl.full, stage, cluster + n * a.num_clusters, a, g);
     }
@@ -515,6 +519,13 @@ layernorm_bwd_reg_kernel(const T* __restrict__ x, const T* __restrict__ dy,
     constexpr int E = PairVec<T>::kElems;
     constexpr int PAIRS = PairVec<T>::kPairs;
     constexpr int W = THREADS / 32;
+    // More than 16 row elements per thread do not fit next to gamma and the column sums: such
+    // slices are not kept in registers across the exchange but read from the shared-memory stage
+    // a second time (the stage is then held until the row's outputs are written). Twice the
+    // elements per thread means half the cluster size for the same row: more co-resident
+    // clusters, and the per-row overhead is spread over twice the work.
+    constexpr bool REREAD = VPT * E > 16;
+    constexpr int HELD = REREAD ? 1 : VPT;
 
     const uint32_t rank = cluster_cta_rank();
     const uint32_t nranks = cluster_cta_count();
@@ -553,10 +564,24 @@ layernorm_bwd_reg_kernel(const T* __restrict__ x, const T* __restrict__ dy,
     const float inv_cols = 1.0f / static_cast<float>(a.cols);
 
     struct Regs {
-        uint4 x[VPT];
-        uint4 dy[VPT];
+        uint4 x[HELD];
+        uint4 dy[HELD];
         float mean;    // HAS_STATS: given; else the shift first, the mean after `middle`
         float rstd;
+        int stage;     // REREAD: the ring stage that holds the row
+    };
+    // vector i of this thread's part of the row: from registers, or again from the stage
+    auto fetch = [&](const Regs& r, int i, uint4& xr, uint4& dr) {
+        if (REREAD) {
+            const int v = threadIdx.x + i * THREADS;
+            const bool live = FULL || v < nvec;
+            const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+            xr = live ? reinterpret_cast<const uint4*>(stage_tile<T, 2>(data, r.stage, 0, a.slice_elems))[v] : zero;
+            dr = live ? reinterpret_cast<const uint4*>(stage_tile<T, 2>(data, r.stage, 1, a.slice_elems))[v] : zero;
+        } else {
+            xr = r.x[REREAD ? 0 : i];
+            dr = r.dy[REREAD ? 0 : i];
+        }
     };
     float next_shift = (!HAS_STATS && my_rows > 0) ? row_first_element(x, cluster, a.cols) : 0.0f;
 
@@ -567,8 +592,10 @@ layernorm_bwd_reg_kernel(const T* __restrict__ x, const T* __restrict__ dy,
 #pragma unroll
         for (int i = 0; i < VPT; ++i) {
             float2 xv[PAIRS], dv[PAIRS];
-            PairVec<T>::unpack(r.x[i], xv);
-            PairVec<T>::unpack(r.dy[i], dv);
+            uint4 xr, dr;
+            fetch(r, i, xr, dr);
+            PairVec<T>::unpack(xr, xv);
+            PairVec<T>::unpack(dr, dv);
 #pragma unroll
             for (int j = 0; j < PAIRS; ++j) {
                 const float2 gg = __fmul2_rn(dv[j], gam[i][j]);   // 0 past the slice: dy = gamma = 0
@@ -582,7 +609,7 @@ layernorm_bwd_reg_kernel(const T* __restrict__ x, const T* __restrict__ dy,
     auto front = [&](Regs& r, int it) {
         const int row = cluster + it * a.num_clusters;
         CREDIT_TRACE_POINT(1, it);
-        if (fills_ring && it > 0) filler.recycle(it);
+        if (fills_ring && it > 0) filler.recycle(it, REREAD ? 2 : 1);
         if (HAS_STATS) {
             r.mean = __ldg(mean_in + row);
             r.rstd = __ldg(rstd_in + row);
@@ -592,20 +619,31 @@ layernorm_bwd_reg_kernel(const T* __restrict__ x, const T* __restrict__ dy,
         }
         if (g.local > 0) mbar_wait_bounded(smem_u32(&ctl.full[ring.stage]), ring.parity, a.status);
         CREDIT_TRACE_POINT(2, it);
-        load_raw<THREADS, VPT, FULL>(
-            reinterpret_cast<const uint4*>(stage_tile<T, 2>(data, ring.stage, 0, a.slice_elems)), nvec, r.x);
-        load_raw<THREADS, VPT, FULL>(
-            reinterpret_cast<const uint4*>(stage_tile<T, 2>(data, ring.stage, 1, a.slice_elems)), nvec, r.dy);
+        r.stage = ring.stage;
+        if (!REREAD) {
+            load_raw<THREADS, HELD, FULL>(
+                reinterpret_cast<const uint4*>(stage_tile<T, 2>(data, ring.stage, 0, a.slice_elems)), nvec, r.x);
+            load_raw<THREADS, HELD, FULL>(
+                reinterpret_cast<const uint4*>(stage_tile<T, 2>(data, ring.stage, 1, a.slice_elems)), nvec, r.dy);
+        }
         float part[2];
         if (HAS_STATS) {
             sums_of_g(r, part);
+        } else if (REREAD) {
+            uint4 raw[VPT];
+            load_raw<THREADS, VPT, FULL>(
+                reinterpret_cast<const uint4*>(stage_tile<T, 2>(data, ring.stage, 0, a.slice_elems)), nvec, raw);
+            shifted_partials<T, THREADS, VPT, FULL>(raw, nvec, r.mean, part[0], part[1]);
+            part[0] = warp_sum(part[0]);
+            part[1] = warp_sum(part[1]);
         } else {
-            shifted_partials<T, THREADS, VPT, FULL>(r.x, nvec, r.mean, part[0], part[1]);
+            shifted_partials<T, THREADS, HELD, FULL>(r.x, nvec, r.mean, part[0], part[1]);
             part[0] = warp_sum(part[0]);
             part[1] = warp_sum(part[1]);
         }
         CREDIT_TRACE_POINT(4, it);
-        if (g.local > 0 && (threadIdx.x & 31) == 0) mbar_arrive(smem_u32(&ctl.empty[ring.stage]));
+        // the stage is free once the row is in registers, or (REREAD) once its outputs are written
+        if (!REREAD && g.local > 0 && (threadIdx.x & 31) == 0) mbar_arrive(smem_u32(&ctl.empty[ring.stage]));
         exchange_send<2, W>(part, ctl.ex, it, rank, nranks, a.status);
         ring.advance(a.stages);
         CREDIT_TRACE_POINT(6, it);
@@ -636,8 +674,10 @@ layernorm_bwd_reg_kernel(const T* __restrict__ x, const T* __restrict__ dy,
         for (int i = 0; i < VPT; ++i) {
             const int v = threadIdx.x + i * THREADS;
             float2 xv[PAIRS], dv[PAIRS], o[PAIRS];
-            PairVec<T>::unpack(r.x[i], xv);
-            PairVec<T>::unpack(r.dy[i], dv);
+            uint4 xr, dr;
+            fetch(r, i, xr, dr);
+            PairVec<T>::unpack(xr, xv);
+            PairVec<T>::unpack(dr, dv);
 #pragma unroll
             for (int j = 0; j < PAIRS; ++j) {
                 const float2 c = __fadd2_rn(xv[j], neg_mean);
@@ -649,6 +689,10 @@ layernorm_bwd_reg_kernel(const T* __restrict__ x, const T* __restrict__ dy,
                 }
             }
             if (FULL || v < nvec) __stcs(out + v, PairVec<T>::pack(o));
+        }
+        if (REREAD && g.local > 0) {
+            __syncwarp();   // every lane has read its vectors of the stage
+            if ((threadIdx.x & 31) == 0) mbar_arrive(smem_u32(&ctl.empty[r.stage]));
         }
         CREDIT_TRACE_POINT(9, it);
     };

@@ -14,6 +14,7 @@ namespace {
         case 1: return (const void*)KERNEL<T, THREADS, 1, FULL __VA_ARGS__>; \
         case 2: return (const void*)KERNEL<T, THREADS, 2, FULL __VA_ARGS__>; \
         case 4: return (const void*)KERNEL<T, THREADS, 4, FULL __VA_ARGS__>; \
+        case 8: return (const void*)KERNEL<T, THREADS, 8, FULL __VA_ARGS__>; \
         default: return nullptr;                                       \
     }
 #define CREDIT_COMMA ,
