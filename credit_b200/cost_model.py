@@ -18,7 +18,7 @@ model counts nor by DSMEM store bandwidth; what was measured is
 
 where a cluster finishes one row every `row_period` = fixed latency chain (ring
 wait, shared-memory reads, shuffle trees, mbarrier exchange, stores: about 1.4 us
-per reduction stage at 1.9 GHz) + a per-element term, and `resident_clusters(P)` is
+for the first reduction of a row at 1.9 GHz) + a per-element term, and `resident_clusters(P)` is
 what the driver's occupancy query returns for the kernel (GPC packing makes it far
 from sm_count / P: 15 clusters of 8 CTAs at one CTA per SM on a 148-SM part).
 """
@@ -119,13 +119,15 @@ class B200Calibration:
     sweeps); cycles are SM cycles at `clock_ghz`."""
     clock_ghz: float = 1.93                    # SM clock under these memory-bound kernels
     hbm_gbps: float = 6538.6                   # copy ceiling
-    chain_cycles_per_stage: float = 2200.0     # ring wait, LDS, shuffle trees, push, wait, stores
-    chain_cycles_per_warp: float = 25.0        # per stage: the CTA-local collection grows with its warps
+    chain_cycles_per_stage: float = 1600.0     # first reduction of a row: ring wait, LDS, shuffle
+                                               # trees, push, wait, stores
+    chain_cycles_next_stage: float = 200.0     # every further dependent reduction of the row
+    chain_cycles_per_warp: float = 20.0        # per stage: the CTA-local collection grows with its warps
     exchange_cycles: dict | None = None        # st.async + mbarrier all-to-all, per cluster size
-    cycles_per_element_per_thread: float = 14.0  # issue cost of one row element in one thread
+    cycles_per_element_per_thread: float = 4.0   # issue cost of one row element in one thread
     one_shot_cycles: float = 6000.0            # cluster launch + barrier set-up + first load, per row,
                                                # when every cluster handles a single row
-    overlap_exponent: float = 3.0              # time = (hbm^k + latency^k)^(1/k)
+    overlap_exponent: float = 2.0              # time = (hbm^k + latency^k)^(1/k)
     generic_path_efficiency: float = 0.5       # slices too large for registers run on the shared-memory
                                                # re-read kernels: about half of the copy ceiling
     cta_launch_ns: float = 4.8                 # streaming kernels: CTA launch throughput of the device
@@ -160,8 +162,8 @@ def predict_cluster_ms(rows: int, cols: int, cluster_size: int, resident_cluster
         rows_per_cluster = math.ceil(rows / resident_clusters)
         return ClusterPrediction(cluster_size, hbm_ms, rows_per_cluster, 0.0, hbm_ms / cal.generic_path_efficiency)
     elems_per_thread = math.ceil(cols / cluster_size / threads)
-    chain = reduction_stages * (cal.chain_cycles_per_stage + cal.chain_cycles_per_warp * (threads // 32) +
-                                cal.exchange(cluster_size))
+    chain = (cal.chain_cycles_per_stage + (reduction_stages - 1) * cal.chain_cycles_next_stage +
+             reduction_stages * (cal.chain_cycles_per_warp * (threads // 32) + cal.exchange(cluster_size)))
     period_cycles = chain + elems_per_thread * cal.cycles_per_element_per_thread
     if not persistent:
         period_cycles += cal.one_shot_cycles
@@ -190,8 +192,10 @@ def predict_streaming_ms(rows: int, cluster_size: int, algorithmic_bytes: float,
     return ClusterPrediction(cluster_size, hbm_ms, 1, 0.0, predicted)
 
 
-def best_cluster_size(predictions: list[ClusterPrediction]) -> int:
-    """Cluster size with the lowest predicted time; ties go to the smaller cluster."""
+def best_cluster_size(predictions: list[ClusterPrediction], tie: float = 0.01) -> int:
+    """Cluster size with the lowest predicted time; predictions within `tie` (1 %) of the lowest
+    count as equal and the smallest cluster among them wins (it is the easiest to place)."""
     if not predictions:
         raise ValueError("no predictions")
-    return min(predictions, key=lambda p: (round(p.predicted_ms, 6), p.cluster_size)).cluster_size
+    lowest = min(p.predicted_ms for p in predictions)
+    return min(p.cluster_size for p in predictions if p.predicted_ms <= lowest * (1.0 + tie))

@@ -21,7 +21,7 @@ const void* row_reduce_kernel_for(int load_path, int threads, bool aligned);
 const void* block_read_kernel_for(int workload, int dtype, bool aligned);
 // Reference-sweep workloads (CREDIT_WL_WEIGHTED_VAR_BACKWARD ... CREDIT_WL_ROWWISE_QUANT), fp32;
 // staged = false: the no-staging, one-CTA-per-row form.
-const void* row_op_kernel_for(int workload, bool aligned, bool staged);
+const void* row_op_kernel_for(int workload, int threads, bool aligned, bool staged);
 
 // Column sums of LayerNorm backward for shapes outside the register path, and
 // the finishing reduction over per-cluster (or per-row-block) partials.

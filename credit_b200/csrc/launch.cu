@@ -265,7 +265,7 @@ bool is_row_op(int workload) {
 
 const void* workload_func(int workload, int dtype, const credit_plan_info& p, bool want_grads) {
     const bool al = p.aligned != 0;
-    if (is_row_op(workload)) return row_op_kernel_for(workload, al, p.variant != CREDIT_VARIANT_BLOCK_READ);
+    if (is_row_op(workload)) return row_op_kernel_for(workload, p.threads, al, p.variant != CREDIT_VARIANT_BLOCK_READ);
     if (p.variant == CREDIT_VARIANT_BLOCK_READ) return block_read_kernel_for(workload, dtype, al);
     const int vpt = p.vectors_per_thread;
     const bool full = p.full_tiles != 0;
@@ -387,7 +387,7 @@ int plan_static(int workload, const Shape& s, int dtype, const credit_launch_opt
     if (o.variant == CREDIT_VARIANT_BLOCK_READ) {
         // one CTA of 512 threads per row, no shared-memory staging, no cluster
         p->cluster_size = 1;
-        p->threads = is_row_op(workload) ? 256 : 512;
+        p->threads = is_row_op(workload) ? (o.threads ? o.threads : 256) : 512;
         p->schedule = CREDIT_SCHEDULE_ROW_PER_CLUSTER;
         p->load_path = CREDIT_LOAD_LDG;
         p->slice_elems = round_up(s.cols, 64);
