@@ -9,6 +9,7 @@
 #include <cuda_runtime.h>
 
 #include <algorithm>
+#include <cmath>
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
@@ -519,6 +520,91 @@ struct Resolved {
     const void* func = nullptr;
 };
 
+// ---------------------------------------------------------------------------
+// automatic cluster size: the B200 row-period model (same constants and formula as
+// credit_b200/cost_model.py: predict_cluster_ms), evaluated over the admissible sizes
+//   time(P) = sqrt(hbm^2 + latency^2),  latency = ceil(rows / resident(P)) * row_period(P)
+// with resident(P) from the driver's occupancy query. Calibrated on B200 (copy ceiling
+// 6538.6 GB/s, 1.93 GHz under these kernels, exchange cycles from primitive_benchmark).
+// ---------------------------------------------------------------------------
+double compulsory_bytes(int workload, const Shape& s, bool grads) {
+    const double rc = static_cast<double>(s.rows) * s.cols, e = s.elem_bytes;
+    switch (workload) {
+        case CREDIT_WL_RMSNORM_FORWARD: return 2 * rc * e + s.cols * 4.0;
+        case CREDIT_WL_LAYERNORM_FORWARD: return 2 * rc * e + 2 * s.cols * 4.0 + 2 * s.rows * 4.0;
+        case CREDIT_WL_LAYERNORM_BACKWARD: return 3 * rc * e + s.cols * 4.0;
+        default: return 3 * rc * e + 2 * s.rows * 4.0 + (grads ? 3 : 1) * s.cols * 4.0;
+    }
+}
+
+double predicted_ms(int workload, const Shape& s, const credit_plan_info& p, bool grads) {
+    const double hbm_ms = compulsory_bytes(workload, s, grads) / (6538.6 * 1.0e6);
+    if (p.vectors_per_thread == 0) return hbm_ms / 0.5;   // shared-memory re-read kernels
+    static const double kExchange[5] = {157.0, 315.0, 322.0, 351.0, 420.0};   // P = 1, 2, 4, 8, 16
+    int log2p = 0;
+    while ((1 << log2p) < p.cluster_size) ++log2p;
+    const int stages = workload == CREDIT_WL_LAYERNORM_BACKWARD ? 2 : 1;
+    const double elems = std::ceil(static_cast<double>(s.cols) / p.cluster_size / p.threads);
+    const double chain = 1600.0 + (stages - 1) * 200.0 + stages * (20.0 * (p.threads / 32) + kExchange[log2p]) +
+                         4.0 * elems;
+    const double rows_per_cluster = std::ceil(static_cast<double>(s.rows) / std::max(p.num_clusters, 1));
+    const double latency_ms = rows_per_cluster * chain / (1.93 * 1.0e6);
+    return std::sqrt(hbm_ms * hbm_ms + latency_ms * latency_ms);
+}
+
+// (device, workload, rows, cols, dtype, aligned, grads, variant, threads, stages, flags) -> chosen size
+std::map<std::tuple<int, int, int, int, int, bool, bool, int, int, int, int>, int> g_auto_cluster;
+
+// Fills o->cluster_size for the staged workloads when the caller left it at 0. On any failure the
+// planner's own rule (smallest cluster that fits) stays in charge.
+void choose_cluster_by_model(int device, const DeviceState& dev, int workload, const Shape& s, int dtype,
+                             bool pointers_aligned, bool grads, credit_launch_opts* o) {
+    if (o->cluster_size != 0 || s.rows == 0 || !dev.info.cluster_launch) return;
+    if (workload == CREDIT_WL_ROW_REDUCE || is_row_op(workload)) return;
+    if (o->variant == CREDIT_VARIANT_BLOCK_READ || o->variant == CREDIT_VARIANT_BLOCK_SMEM) return;
+    if (o->schedule == CREDIT_SCHEDULE_ROW_PER_CLUSTER) return;
+    const auto key = std::make_tuple(device, workload, s.rows, s.cols, dtype, pointers_aligned, grads, o->variant,
+                                     o->threads, o->stages, o->flags);
+    {
+        std::lock_guard<std::mutex> lock(g_mutex);
+        auto it = g_auto_cluster.find(key);
+        if (it != g_auto_cluster.end()) {
+            o->cluster_size = it->second;
+            return;
+        }
+    }
+    int best = 0;
+    double best_ms = 0.0;
+    for (int c = o->variant == CREDIT_VARIANT_CLUSTER_SMEM ? 2 : 1; c <= kMaxClusterSize; c *= 2) {
+        credit_launch_opts trial = *o;
+        trial.cluster_size = c;
+        credit_plan_info plan;
+        if (plan_static(workload, s, dtype, trial, pointers_aligned, grads, dev.info, &plan) != CREDIT_OK) continue;
+        if (plan.schedule != CREDIT_SCHEDULE_PERSISTENT) continue;
+        // never below the smallest cluster whose stage fits the budget (larger stages measured
+        // slower with inputs that are not in L2); the model decides whether to go above it
+        const bool two_reads = inputs_staged(workload) == 2 && !grads;
+        if (c < kMaxClusterSize &&
+            inputs_staged(workload) * plan.slice_elems * s.elem_bytes > (two_reads ? 2 : 1) * kAutoStageBytes)
+            continue;
+        const void* func = workload_func(workload, dtype, plan, grads);
+        if (func == nullptr || prepare_function(device, func, dev.info.max_dynamic_smem_per_block) != CREDIT_OK) continue;
+        if (plan_grid(device, func, s, &plan) != CREDIT_OK) continue;
+        const double ms = predicted_ms(workload, s, plan, grads);
+        if (best == 0 || ms < best_ms * 0.99) {   // within 1 %: the smaller cluster stays
+            best = c;
+            best_ms = ms;
+        }
+    }
+    t_last_error[0] = '\0';   // failed trials are not errors of this call
+    if (best == 0) return;
+    {
+        std::lock_guard<std::mutex> lock(g_mutex);
+        g_auto_cluster[key] = best;
+    }
+    o->cluster_size = best;
+}
+
 int resolve(int workload, int64_t rows, int64_t cols, int dtype, const credit_launch_opts* opts,
             bool pointers_aligned, bool want_grads, Resolved* r) {
     int rc = check_shape(rows, cols, dtype, &r->shape);
@@ -529,6 +615,8 @@ int resolve(int workload, int64_t rows, int64_t cols, int dtype, const credit_la
     CREDIT_CUDA_TRY(cudaGetDevice(&r->device));
     rc = load_device(r->device, &r->dev);
     if (rc != CREDIT_OK) return rc;
+    if (workload >= CREDIT_WL_RMSNORM_FORWARD && workload <= CREDIT_WL_ROWWISE_QUANT)
+        choose_cluster_by_model(r->device, *r->dev, workload, r->shape, dtype, pointers_aligned, want_grads, &o);
     rc = plan_static(workload, r->shape, dtype, o, pointers_aligned, want_grads, r->dev->info, &r->plan);
     if (rc != CREDIT_OK) return rc;
     r->func = workload_func(workload, dtype, r->plan, want_grads);
