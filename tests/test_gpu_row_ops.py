@@ -146,3 +146,10 @@ def test_row_op_argument_errors(native_lib):
     # empty batch is a no-op
     e = torch.zeros(0, 256, device=DEV)
     L.NATIVE_LAUNCHERS["rowwise_quant"]((e,), L.allocate_outputs("rowwise_quant", (e,)))
+
+
+@pytest.mark.parametrize("name", ROW_OPS)
+def test_512_thread_kernels(native_lib, name):
+    inputs = W.WORKLOADS[name].input_factory(10, 16384, "cpu", seed=21)
+    compare(name, run(name, inputs, 4, {"threads": 512}), oracle64(name, inputs))
+    compare(name, run(name, inputs, 0, {"threads": 512, "variant": N.VARIANT_BLOCK_READ}), oracle64(name, inputs))
