@@ -538,3 +538,18 @@ def test_runner_in_process_arm():
     assert res["framework"] == "native" and 0.0 < res["ms"] < 10.0 and len(res["samples"]) == 2
     res = runner.benchmark_native("rowwise_quant", 64, 4096, warmup=1, iterations=3, trials=1)
     assert res["gbps"] > 0.0
+
+
+@pytest.mark.parametrize("cluster_size", [0, 1, 2, 4, 8, 16])
+def test_layernorm_backward_reproduces_reference_outputs(cluster_size):
+    """dx on the stored golden inputs against what the reference's own function returned."""
+    import numpy as np
+    from pathlib import Path
+
+    golden = np.load(Path(__file__).resolve().parent / "golden" / "reference_workloads.npz")
+    for shape in ("3x96", "2x1000"):
+        ins = tuple(torch.from_numpy(golden[f"layernorm_backward/{shape}/in{i}"]) for i in range(3))
+        want = torch.from_numpy(golden[f"layernorm_backward/{shape}/out0"])
+        (got,) = try_run("layernorm_backward", ins, cluster_size)
+        # same formula in fp32 on both sides: rounding noise only (the reference's own gate is 2e-2)
+        assert torch.allclose(got, want, rtol=1e-4, atol=2e-5), float((got - want).abs().max())
