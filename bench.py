@@ -183,7 +183,7 @@ def run_reference_arm(args) -> None:
         "e2e": {"value": value, "unit": "rows/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
-    print(json.dumps(line), flush=True)
+    emit_result(line)
 
 
 def time_other_workloads(torch, dev) -> dict:
@@ -263,6 +263,29 @@ def time_other_workloads(torch, dev) -> dict:
     return out
 
 
+_RESULT_FD = None
+
+
+def keep_stdout_for_the_result() -> None:
+    """Libraries print to stdout too (NCCL announces its version there on the first collective).
+    Everything written to fd 1 from here on goes to stderr; the JSON line is written to the saved
+    descriptor, so stdout carries exactly that one line."""
+    global _RESULT_FD
+    if _RESULT_FD is None:
+        sys.stdout.flush()
+        _RESULT_FD = os.dup(1)
+        os.dup2(2, 1)
+
+
+def emit_result(line: dict) -> None:
+    text = (json.dumps(line) + "\n").encode()
+    if _RESULT_FD is None:
+        sys.stdout.write(text.decode())
+        sys.stdout.flush()
+    else:
+        os.write(_RESULT_FD, text)
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -272,6 +295,7 @@ def main() -> None:
     ap.add_argument("--no-others", action="store_true", help="skip the context workloads")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "native" else args.warmup
+    keep_stdout_for_the_result()
 
     if args.impl == "reference":
         run_reference_arm(args)
@@ -460,7 +484,7 @@ def main() -> None:
             line["cpu_baseline"] = baseline
         if others:
             line["others"] = others
-        print(json.dumps(line), flush=True)
+        emit_result(line)
 
     if world > 1:
         dist.barrier()
