@@ -25,6 +25,7 @@ from pathlib import Path
 from typing import Any, Iterable
 
 from . import cost_model
+from .report import write_report
 from .profile import make_b200_calibration, make_device_profile, parse_primitive_output, profile_as_dict
 from .workloads import WORKLOADS
 
@@ -438,6 +439,8 @@ def run_suite(raw_config: dict[str, Any], output_dir: Path, requested_gpu: str =
     summary_rows, cluster_rows = build_summary(config, profile, calibration, raw_cuda, control_samples, residency)
     write_csv(output_dir / "summary.csv", summary_rows)
     write_csv(output_dir / "cluster_sweep.csv", cluster_rows)
+    (output_dir / "metadata.json").write_text(json.dumps(metadata, indent=2))
+    write_report(output_dir)
     hits = sum(1 for r in summary_rows if r["b200_model_picks_measured_best"])
     near = sum(1 for r in summary_rows if r["b200_model_within_5pct"])
     metadata.update({"status": "complete", "finished": time.time(), "points": len(summary_rows),
@@ -480,6 +483,7 @@ def rescore_bundle(bundle_dir: Path) -> dict[str, Any]:
     summary_rows, cluster_rows = build_summary(config, profile, calibration, raw_cuda, control, residency)
     write_csv(bundle_dir / "summary.csv", summary_rows)
     write_csv(bundle_dir / "cluster_sweep.csv", cluster_rows)
+    write_report(bundle_dir)
     return {"points": len(summary_rows),
             "b200_model_hits": sum(1 for r in summary_rows if r["b200_model_picks_measured_best"]),
             "b200_model_within_5pct": sum(1 for r in summary_rows if r["b200_model_within_5pct"])}

@@ -218,6 +218,10 @@ def test_rescore_bundle_round_trip(tmp_path, parsed):
     with (tmp_path / "cluster_sweep.csv").open() as f:
         sweep = list(csv.DictReader(f))
     assert [r["register_path"] for r in sweep] == ["False", "True"]
+    report = (tmp_path / "REPORT.md").read_text()
+    assert "picks the measured-best cluster size at 1/1 points" in report
+    assert "| layernorm_backward_stats | 65536 | 1930.0 | 1840.0 | 830.0 | 8 | 8 | 830.0 | yes |" in report
+    assert json.loads((tmp_path / "aggregate.json").read_text())["b200_model_within_5pct"] == 1
 
 
 def test_assert_outputs_close_rules():
