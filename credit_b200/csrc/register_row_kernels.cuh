@@ -605,11 +605,14 @@ layernorm_bwd_reg_kernel(const T* __restrict__ x, const T* __restrict__ dy,
             for (int j = 0; j < PAIRS; ++j) {
                 const float2 gg = __fmul2_rn(dv[j], gam[i][j]);   // 0 past the slice: dy = gamma = 0
                 s1 = __fadd2_rn(s1, gg);
-                s2 = __ffma2_rn(gg, __fadd2_rn(xv[j], neg_mean), s2);
+                // 16-bit rows: sum g * x here and take mean * sum g off once per row below (a mean
+                // that dwarfs the spread cannot be stored in 16 bits in the first place)
+                s2 = sizeof(T) == 2 ? __ffma2_rn(gg, xv[j], s2) : __ffma2_rn(gg, __fadd2_rn(xv[j], neg_mean), s2);
             }
         }
-        part[0] = warp_sum(s1.x + s1.y);
-        part[1] = warp_sum(s2.x + s2.y);
+        const float t1 = s1.x + s1.y, t2 = s2.x + s2.y;
+        part[0] = warp_sum(t1);
+        part[1] = warp_sum(sizeof(T) == 2 ? fmaf(-r.mean, t1, t2) : t2);
     };
     auto front = [&](Regs& r, int it) {
         const int row = cluster + it * a.num_clusters;
