@@ -107,6 +107,7 @@ __device__ __forceinline__ void exchange_receive(ExchangeStream<K>& s, int it, u
     const int buf = it & (kExchangeBuffers - 1);
     const uint32_t phase = (static_cast<uint32_t>(it) / kExchangeBuffers) & 1u;
     mbar_wait_bounded(smem_u32(&s.bar[buf]), phase, status);
+    CREDIT_TRACE_POINT(10, it);
     const uint32_t lane = threadIdx.x & 31;
 #pragma unroll
     for (int k = 0; k < K; ++k) {
