@@ -37,6 +37,7 @@
 #include <cuda_runtime.h>
 
 #include <cstdint>
+#include <map>
 #include <mutex>
 
 #include "../../include/credit_b200.h"
@@ -712,9 +713,10 @@ cudaError_t launch_ffn_pack_weight(const void* w, void* packed, int k, int n, cu
 }
 
 namespace {
-// Clusters of `cluster_size` CTAs of `kernel` that can be resident at once (cached per cluster
-// size; one device kind per process), or -1 if the driver cannot tell. A persistent grid must not
-// be larger: the surplus clusters would only start when the first ones have finished everything.
+// Clusters of `cluster_size` CTAs of `kernel` that can be resident at once on the current device
+// (cached by the caller in `*cache`, 0 = not asked yet), or -1 if the driver cannot tell. A
+// persistent grid must not be larger: the surplus clusters would only start when the first ones
+// have finished everything.
 int resident_clusters(const void* kernel, int cluster_size, int grid_clusters, int* cache) {
     static std::mutex mu;
     std::lock_guard<std::mutex> lock(mu);
@@ -739,6 +741,33 @@ int resident_clusters(const void* kernel, int cluster_size, int grid_clusters, i
     }
     return *cache;
 }
+// What is set up or asked once per device: kernel attributes live in the device's context, and
+// the resident-cluster counts depend on the device.
+struct FfnDeviceState {
+    cudaError_t attr_err = cudaSuccess;
+    int resident_pairs = 0;
+    int resident_row_clusters[kMaxRowClusters + 1] = {};
+};
+
+// The state of `device`, which must be the current device; kernel attributes are set on first use.
+FfnDeviceState& ffn_device_state(int device) {
+    static std::mutex mu;
+    static std::map<int, FfnDeviceState> states;
+    std::lock_guard<std::mutex> lock(mu);
+    auto found = states.find(device);
+    if (found != states.end()) return found->second;
+    FfnDeviceState& st = states[device];
+    const void* kernels[3] = {reinterpret_cast<const void*>(ffn_gemm_kernel<false, false>),
+                              reinterpret_cast<const void*>(ffn_gemm_kernel<false, true>),
+                              reinterpret_cast<const void*>(ffn_gemm_kernel<true, false>)};
+    for (const void* k : kernels)
+        if (st.attr_err == cudaSuccess)
+            st.attr_err = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, kFfnSmemBytes);
+    if (st.attr_err == cudaSuccess)
+        st.attr_err = cudaFuncSetAttribute(ffn_gemm_kernel<true, false>,
+                                           cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+    return st;
+}
 }  // namespace
 
 // Returns cudaSuccess, or an error; *bad_map is set when a tensor map could not be encoded.
@@ -754,25 +783,12 @@ cudaError_t launch_ffn_forward(const void* x, const void* w1p, const void* w2p, 
         *bad_map = true;
         return cudaErrorInvalidValue;
     }
-    static std::once_flag once;
-    static cudaError_t attr_err = cudaSuccess;
-    std::call_once(once, [] {
-        const void* kernels[3] = {reinterpret_cast<const void*>(ffn_gemm_kernel<false, false>),
-                                  reinterpret_cast<const void*>(ffn_gemm_kernel<false, true>),
-                                  reinterpret_cast<const void*>(ffn_gemm_kernel<true, false>)};
-        for (const void* k : kernels)
-            if (attr_err == cudaSuccess)
-                attr_err = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, kFfnSmemBytes);
-        if (attr_err == cudaSuccess)
-            attr_err = cudaFuncSetAttribute(ffn_gemm_kernel<true, false>,
-                                            cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
-    });
-    if (attr_err != cudaSuccess) return attr_err;
-
     int device = 0, sms = 0;
     cudaError_t err = cudaGetDevice(&device);
     if (err == cudaSuccess) err = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
     if (err != cudaSuccess) return err;
+    FfnDeviceState& dev = ffn_device_state(device);
+    if (dev.attr_err != cudaSuccess) return dev.attr_err;
 
     const int m_tiles = m / kBM;
     // GEMM 1: H = GELU(X W1); persistent CTAs (pairs of CTAs sharing each MMA when m allows) walk
@@ -782,9 +798,8 @@ cudaError_t launch_ffn_forward(const void* x, const void* w1p, const void* w2p, 
         __nv_bfloat16* hid = static_cast<__nv_bfloat16*>(hidden);
         if (pair) {
             const int tiles = (m_tiles / 2) * n_tiles;
-            static int cached_pairs = 0;
             int pairs = resident_clusters(reinterpret_cast<const void*>(ffn_gemm_kernel<false, true>), 2, tiles,
-                                          &cached_pairs);
+                                          &dev.resident_pairs);
             if (pairs < 1) pairs = sms / 2;
             if (pairs > tiles) pairs = tiles;
             cudaLaunchConfig_t cfg{};
@@ -830,9 +845,8 @@ cudaError_t launch_ffn_forward(const void* x, const void* w1p, const void* w2p, 
         cfg.attrs = &attr;
         cfg.numAttrs = 1;
 
-        static int cached_clusters[kMaxRowClusters + 1] = {};
         const int resident = resident_clusters(reinterpret_cast<const void*>(ffn_gemm_kernel<true, false>), n_tiles,
-                                               m_tiles, &cached_clusters[n_tiles]);
+                                               m_tiles, &dev.resident_row_clusters[n_tiles]);
         const int clusters = (resident < 1 || resident > m_tiles) ? m_tiles : resident;
         cfg.gridDim = dim3(static_cast<unsigned>(n_tiles * clusters));
         // Row blocks left over after the full rounds are shared by groups of clusters that split
