@@ -118,6 +118,68 @@ __device__ __forceinline__ void exchange_receive(ExchangeStream<K>& s, int it, u
     }
 }
 
+// Two sums over the warp in five exchange rounds instead of ten: after the first round lanes
+// 0..15 carry `a` and lanes 16..31 carry `b`. Returns the total of a in lanes 0..15 and the total
+// of b in lanes 16..31.
+__device__ __forceinline__ float warp_sum_split(float a, float b) {
+    const bool upper = (threadIdx.x & 16u) != 0;
+    float keep = upper ? b : a;
+    const float give = upper ? a : b;
+    keep += __shfl_xor_sync(0xffffffffu, give, 16);
+#pragma unroll
+    for (int offset = 8; offset > 0; offset >>= 1) keep += __shfl_xor_sync(0xffffffffu, keep, offset);
+    return keep;
+}
+
+// exchange_send for two partials in the split form of warp_sum_split (`keep`: partial 0 in lanes
+// 0..15, partial 1 in lanes 16..31). The collector folds both partials in one shuffle tree, the
+// halves of the warp working on one partial each. W <= 16.
+template <int W>
+__device__ __forceinline__ void exchange_send_split(float keep, ExchangeStream<2>& s, int it, uint32_t rank,
+                                                    uint32_t nranks, int* status) {
+    static_assert(W <= 16, "one half of the collecting warp folds one partial of every warp");
+    const uint32_t lane = threadIdx.x & 31;
+    const uint32_t warp = threadIdx.x >> 5;
+    const uint32_t half = lane >> 4, idx = lane & 15;
+    const int par = it & 1;
+    const uint32_t local_bar = smem_u32(&s.local_bar[par]);
+    if (idx == 0) s.warp_part[par][half][warp] = keep;
+    __syncwarp();                           // lane 16's store is ordered before lane 0's release
+    if (lane == 0) mbar_arrive(local_bar);
+    if (warp != 0) return;
+    mbar_wait_bounded(local_bar, (static_cast<uint32_t>(it) >> 1) & 1u, status);
+    const int buf = it & (kExchangeBuffers - 1);
+    const uint32_t bar = smem_u32(&s.bar[buf]);
+    if (lane == 0) mbar_arrive_expect_tx(bar, nranks * 2u * static_cast<uint32_t>(sizeof(float)));
+    float t = idx < W ? s.warp_part[par][half][idx] : 0.0f;
+#pragma unroll
+    for (int offset = W / 2; offset > 0; offset >>= 1) t += __shfl_xor_sync(0xffffffffu, t, offset);
+    const float t0 = __shfl_sync(0xffffffffu, t, 0);
+    const float t1 = __shfl_sync(0xffffffffu, t, 16);
+    if (lane < nranks) {
+        const uint32_t remote_bar = map_to_rank(bar, lane);
+        st_async_f32(map_to_rank(smem_u32(&s.slot[buf][0][rank]), lane), t0, remote_bar);
+        st_async_f32(map_to_rank(smem_u32(&s.slot[buf][1][rank]), lane), t1, remote_bar);
+    }
+}
+
+// exchange_receive for two partials, both folded in one shuffle tree.
+__device__ __forceinline__ void exchange_receive_split(ExchangeStream<2>& s, int it, uint32_t nranks, int* status,
+                                                       float (&total)[2]) {
+    static_assert(kMaxClusterSize == 16, "one half of the warp reads the slots of one partial");
+    const int buf = it & (kExchangeBuffers - 1);
+    const uint32_t phase = (static_cast<uint32_t>(it) / kExchangeBuffers) & 1u;
+    mbar_wait_bounded(smem_u32(&s.bar[buf]), phase, status);
+    CREDIT_TRACE_POINT(10, it);
+    const uint32_t lane = threadIdx.x & 31;
+    const uint32_t half = lane >> 4, idx = lane & 15;
+    float t = idx < nranks ? s.slot[buf][half][idx] : 0.0f;
+#pragma unroll
+    for (int offset = 8; offset > 0; offset >>= 1) t += __shfl_xor_sync(0xffffffffu, t, offset);
+    total[0] = __shfl_sync(0xffffffffu, t, 0);
+    total[1] = __shfl_sync(0xffffffffu, t, 16);
+}
+
 // A 16-byte vector of row elements as packed fp32 pairs, so that the elementwise
 // arithmetic can use the two-wide fp32 instructions of sm_100
 // (fma/add/mul.rn.f32x2 through __ffma2_rn, __fadd2_rn, __fmul2_rn): half the
@@ -457,16 +519,15 @@ layernorm_fwd_reg_kernel(const T* __restrict__ x, const float* __restrict__ gamm
             reinterpret_cast<const uint4*>(stage_tile<T, 1>(data, ring.stage, 0, a.slice_elems)), nvec, r.raw);
         float part[2];
         shifted_partials<T, THREADS, VPT, FULL>(r.raw, nvec, r.shift, part[0], part[1]);
-        part[0] = warp_sum(part[0]);
-        part[1] = warp_sum(part[1]);
+        const float keep = warp_sum_split(part[0], part[1]);
         if (g.local > 0 && (threadIdx.x & 31) == 0) mbar_arrive(smem_u32(&ctl.empty[ring.stage]));
-        exchange_send<2, W>(part, ctl.ex, it, rank, nranks, a.status);
+        exchange_send_split<W>(keep, ctl.ex, it, rank, nranks, a.status);
         ring.advance(a.stages);
     };
     auto back = [&](const Regs& r, int it) {
         const int row = cluster + it * a.num_clusters;
         float sq[2];
-        exchange_receive<2>(ctl.ex, it, nranks, a.status, sq);
+        exchange_receive_split(ctl.ex, it, nranks, a.status, sq);
         float mean, var;
         moments_from_shifted(sq[0], sq[1], r.shift, a.cols, mean, var);
         const float rstd = rsqrtf(var + eps);
@@ -592,7 +653,7 @@ layernorm_bwd_reg_kernel(const T* __restrict__ x, const T* __restrict__ dy,
     float next_shift = (!HAS_STATS && my_rows > 0) ? row_first_element(x, cluster, a.cols) : 0.0f;
 
     // warp-reduced S1 = sum g and S2 = sum g * (x - mean) over this warp's columns
-    auto sums_of_g = [&](const Regs& r, float (&part)[2]) {
+    auto sums_of_g = [&](const Regs& r) -> float {
         const float2 neg_mean = splat(-r.mean);
         float2 s1 = splat(0.0f), s2 = splat(0.0f);
 #pragma unroll
@@ -612,8 +673,7 @@ layernorm_bwd_reg_kernel(const T* __restrict__ x, const T* __restrict__ dy,
             }
         }
         const float t1 = s1.x + s1.y, t2 = s2.x + s2.y;
-        part[0] = warp_sum(t1);
-        part[1] = warp_sum(sizeof(T) == 2 ? fmaf(-r.mean, t1, t2) : t2);
+        return warp_sum_split(t1, sizeof(T) == 2 ? fmaf(-r.mean, t1, t2) : t2);
     };
     auto front = [&](Regs& r, int it) {
         const int row = cluster + it * a.num_clusters;
@@ -635,45 +695,43 @@ layernorm_bwd_reg_kernel(const T* __restrict__ x, const T* __restrict__ dy,
             load_raw<THREADS, HELD, FULL>(
                 reinterpret_cast<const uint4*>(stage_tile<T, 2>(data, ring.stage, 1, a.slice_elems)), nvec, r.dy);
         }
-        float part[2];
+        float keep;   // the row's two partials, split over the halves of the warp
         if (HAS_STATS) {
-            sums_of_g(r, part);
+            keep = sums_of_g(r);
         } else if (REREAD) {
             uint4 raw[VPT];
+            float part[2];
             load_raw<THREADS, VPT, FULL>(
                 reinterpret_cast<const uint4*>(stage_tile<T, 2>(data, ring.stage, 0, a.slice_elems)), nvec, raw);
             shifted_partials<T, THREADS, VPT, FULL>(raw, nvec, r.mean, part[0], part[1]);
-            part[0] = warp_sum(part[0]);
-            part[1] = warp_sum(part[1]);
+            keep = warp_sum_split(part[0], part[1]);
         } else {
+            float part[2];
             shifted_partials<T, THREADS, HELD, FULL>(r.x, nvec, r.mean, part[0], part[1]);
-            part[0] = warp_sum(part[0]);
-            part[1] = warp_sum(part[1]);
+            keep = warp_sum_split(part[0], part[1]);
         }
         CREDIT_TRACE_POINT(4, it);
         // the stage is free once the row is in registers, or (REREAD) once its outputs are written
         if (!REREAD && g.local > 0 && (threadIdx.x & 31) == 0) mbar_arrive(smem_u32(&ctl.empty[ring.stage]));
-        exchange_send<2, W>(part, ctl.ex, it, rank, nranks, a.status);
+        exchange_send_split<W>(keep, ctl.ex, it, rank, nranks, a.status);
         ring.advance(a.stages);
         CREDIT_TRACE_POINT(6, it);
     };
     // stats recomputed only: finish the statistics, start the exchange of S1, S2
     auto middle = [&](Regs& r, int it) {
         float sq[2];
-        exchange_receive<2>(ctl.ex, it, nranks, a.status, sq);
+        exchange_receive_split(ctl.ex, it, nranks, a.status, sq);
         float mean, var;
         moments_from_shifted(sq[0], sq[1], r.mean, a.cols, mean, var);
         r.mean = mean;
         r.rstd = rsqrtf(var + eps);
-        float part[2];
-        sums_of_g(r, part);
-        exchange_send<2, W>(part, ctl.ex2, it, rank, nranks, a.status);
+        exchange_send_split<W>(sums_of_g(r), ctl.ex2, it, rank, nranks, a.status);
     };
     auto back = [&](const Regs& r, int it) {
         const int row = cluster + it * a.num_clusters;
         float sums[2];
         CREDIT_TRACE_POINT(7, it);
-        exchange_receive<2>(HAS_STATS ? ctl.ex : ctl.ex2, it, nranks, a.status, sums);
+        exchange_receive_split(HAS_STATS ? ctl.ex : ctl.ex2, it, nranks, a.status, sums);
         CREDIT_TRACE_POINT(8, it);
         const float2 neg_mean = splat(-r.mean), rstd2 = splat(r.rstd);
         const float2 ca = splat(-r.rstd * r.rstd * r.rstd * (sums[1] * inv_cols));
