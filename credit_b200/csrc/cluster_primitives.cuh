@@ -139,6 +139,14 @@ __device__ __forceinline__ void st_async_f32(uint32_t remote_addr, float v, uint
                  : "memory");
 }
 
+// Two floats (8-byte aligned destination) in one message.
+__device__ __forceinline__ void st_async_f32x2(uint32_t remote_addr, float v0, float v1, uint32_t remote_bar) {
+    asm volatile("st.async.shared::cluster.mbarrier::complete_tx::bytes.v2.f32 [%0], {%1, %2}, [%3];" ::"r"(
+                     remote_addr),
+                 "f"(v0), "f"(v1), "r"(remote_bar)
+                 : "memory");
+}
+
 // One try: may suspend the thread (without issuing) for up to about a microsecond
 // while the phase is still pending.
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {

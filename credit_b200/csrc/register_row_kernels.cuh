@@ -156,11 +156,9 @@ __device__ __forceinline__ void exchange_send_split(float keep, ExchangeStream<2
     for (int offset = W / 2; offset > 0; offset >>= 1) t += __shfl_xor_sync(0xffffffffu, t, offset);
     const float t0 = __shfl_sync(0xffffffffu, t, 0);
     const float t1 = __shfl_sync(0xffffffffu, t, 16);
-    if (lane < nranks) {
-        const uint32_t remote_bar = map_to_rank(bar, lane);
-        st_async_f32(map_to_rank(smem_u32(&s.slot[buf][0][rank]), lane), t0, remote_bar);
-        st_async_f32(map_to_rank(smem_u32(&s.slot[buf][1][rank]), lane), t1, remote_bar);
-    }
+    // the slots of a buffer are laid out [source rank][partial] here: one 8-byte message per peer
+    if (lane < nranks)
+        st_async_f32x2(map_to_rank(smem_u32(&s.slot[buf][0][0] + 2 * rank), lane), t0, t1, map_to_rank(bar, lane));
 }
 
 // exchange_receive for two partials, both folded in one shuffle tree.
@@ -173,7 +171,7 @@ __device__ __forceinline__ void exchange_receive_split(ExchangeStream<2>& s, int
     CREDIT_TRACE_POINT(10, it);
     const uint32_t lane = threadIdx.x & 31;
     const uint32_t half = lane >> 4, idx = lane & 15;
-    float t = idx < nranks ? s.slot[buf][half][idx] : 0.0f;
+    float t = idx < nranks ? (&s.slot[buf][0][0])[2 * idx + half] : 0.0f;
 #pragma unroll
     for (int offset = 8; offset > 0; offset >>= 1) t += __shfl_xor_sync(0xffffffffu, t, offset);
     total[0] = __shfl_sync(0xffffffffu, t, 0);
