@@ -205,12 +205,17 @@ def time_other_workloads(torch, dev) -> dict:
         b.synchronize()
         return a.elapsed_time(b) / iters
 
+    # (key, workload, rows, cols, iterations, launch options; None = the planner's own choice)
     cases = [
-        ("rmsnorm_forward", 1024, 32768, 20),
-        ("layernorm_forward", 4096, 131072, 8),
-        ("layernorm_backward_stats", 8192, 65536, 6),
+        ("rmsnorm_forward", "rmsnorm_forward", 1024, 32768, 20, None),
+        ("layernorm_forward", "layernorm_forward", 4096, 131072, 8, None),
+        # the measured-best configuration of the cluster-size sweep, which the planner's model
+        # ranks 3 % behind its own pick (P = 8, 512 threads)
+        ("layernorm_forward_p16_256", "layernorm_forward", 4096, 131072, 8,
+         {"cluster_size": 16, "threads": 256, "stages": 3}),
+        ("layernorm_backward_stats", "layernorm_backward_stats", 8192, 65536, 6, None),
     ]
-    for name, rows, cols, iters in cases:
+    for key, name, rows, cols, iters, config in cases:
         try:
             spec = W.WORKLOADS[name]
             sets = []
@@ -224,20 +229,24 @@ def time_other_workloads(torch, dev) -> dict:
                 kw["workspace"] = torch.empty(need, dtype=torch.uint8, device=dev)
             state = {"i": 0}
 
+            opts = dict(config) if config else None
+            cluster_size = opts.pop("cluster_size", 0) if opts else 0
+
             def call():
                 ins, outs = sets[state["i"] % nsets]
                 state["i"] += 1
-                L.NATIVE_LAUNCHERS[name](ins, outs, **kw)
+                L.NATIVE_LAUNCHERS[name](ins, outs, cluster_size, opts, **kw)
 
             ms = timed(call, iters)
             nbytes = W.algorithmic_bytes(name, rows, cols)
-            out[name] = {"shape": [rows, cols], "dtype": str(spec.dtype).replace("torch.", ""),
-                         "ms": round(ms, 4), "gbps": round(nbytes / ms / 1e6, 1),
-                         "rows_per_s": round(rows / ms * 1e3, 1)}
+            out[key] = {"shape": [rows, cols], "dtype": str(spec.dtype).replace("torch.", ""),
+                        "ms": round(ms, 4), "gbps": round(nbytes / ms / 1e6, 1),
+                        "rows_per_s": round(rows / ms * 1e3, 1),
+                        "config": config if config else "automatic"}
             del sets, kw
             torch.cuda.empty_cache()
         except Exception as exc:  # report, do not hide
-            out[name] = {"error": str(exc)[:200]}
+            out[key] = {"error": str(exc)[:200]}
     # the fused FFN (tensor-bound): TFLOP/s against the measured dense bf16 peak
     try:
         m, d, h = 2048, 4096, 16384
