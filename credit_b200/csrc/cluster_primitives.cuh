@@ -147,18 +147,20 @@ __device__ __forceinline__ void st_async_f32x2(uint32_t remote_addr, float v0, f
                  : "memory");
 }
 
-// One try: may suspend the thread (without issuing) for up to about a microsecond
-// while the phase is still pending.
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+// One poll, never suspends: true when the phase with this parity has completed. The suspending
+// form (mbarrier.try_wait) wakes a warp late when the phase completes shortly after the first
+// look, which is the usual case on the row path: measured on one GPU, polling is 0.8 % (LayerNorm
+// backward with column sums) to 3 % (LayerNorm forward) faster, and 0.4 % on the FFN.
+__device__ __forceinline__ bool mbar_poll(uint32_t bar, uint32_t parity) {
     uint32_t done;
     asm volatile(
         "{\n\t"
         ".reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t"
         "}"
         : "=r"(done)
-        : "r"(bar), "r"(parity), "r"(1000u)
+        : "r"(bar), "r"(parity)
         : "memory");
     return done != 0;
 }
@@ -168,10 +170,10 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // that every CTA of the cluster still reaches the same barriers and the launch
 // ends instead of hanging.
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, int* status) {
-    if (mbar_try_wait(bar, parity)) return true;
+    if (mbar_poll(bar, parity)) return true;
     const long long t0 = clock64();
     for (uint32_t i = 0; i < (1u << 24); ++i) {
-        if (mbar_try_wait(bar, parity)) return true;
+        if (mbar_poll(bar, parity)) return true;
         if (clock64() - t0 > (1ll << 31)) break;
     }
     if (status != nullptr) atomicOr(status, kStatusWaitTimeout);
