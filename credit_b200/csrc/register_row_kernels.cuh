@@ -134,7 +134,7 @@ __device__ __forceinline__ float warp_sum_split(float a, float b) {
 // exchange_send for two partials in the split form of warp_sum_split (`keep`: partial 0 in lanes
 // 0..15, partial 1 in lanes 16..31). The collector folds both partials in one shuffle tree, the
 // halves of the warp working on one partial each. W <= 16.
-template <int W>
+template <int W, int SLEEP_NS = 0>
 __device__ __forceinline__ void exchange_send_split(float keep, ExchangeStream<2>& s, int it, uint32_t rank,
                                                     uint32_t nranks, int* status) {
     static_assert(W <= 16, "one half of the collecting warp folds one partial of every warp");
@@ -147,7 +147,7 @@ __device__ __forceinline__ void exchange_send_split(float keep, ExchangeStream<2
     __syncwarp();                           // lane 16's store is ordered before lane 0's release
     if (lane == 0) mbar_arrive(local_bar);
     if (warp != 0) return;
-    mbar_wait_bounded(local_bar, (static_cast<uint32_t>(it) >> 1) & 1u, status);
+    mbar_wait_bounded<SLEEP_NS>(local_bar, (static_cast<uint32_t>(it) >> 1) & 1u, status);
     const int buf = it & (kExchangeBuffers - 1);
     const uint32_t bar = smem_u32(&s.bar[buf]);
     if (lane == 0) mbar_arrive_expect_tx(bar, nranks * 2u * static_cast<uint32_t>(sizeof(float)));
@@ -162,12 +162,13 @@ __device__ __forceinline__ void exchange_send_split(float keep, ExchangeStream<2
 }
 
 // exchange_receive for two partials, both folded in one shuffle tree.
+template <int SLEEP_NS = 0>
 __device__ __forceinline__ void exchange_receive_split(ExchangeStream<2>& s, int it, uint32_t nranks, int* status,
                                                        float (&total)[2]) {
     static_assert(kMaxClusterSize == 16, "one half of the warp reads the slots of one partial");
     const int buf = it & (kExchangeBuffers - 1);
     const uint32_t phase = (static_cast<uint32_t>(it) / kExchangeBuffers) & 1u;
-    mbar_wait_bounded(smem_u32(&s.bar[buf]), phase, status);
+    mbar_wait_bounded<SLEEP_NS>(smem_u32(&s.bar[buf]), phase, status);
     CREDIT_TRACE_POINT(10, it);
     const uint32_t lane = threadIdx.x & 31;
     const uint32_t half = lane >> 4, idx = lane & 15;
@@ -591,6 +592,9 @@ layernorm_bwd_reg_kernel(const T* __restrict__ x, const T* __restrict__ dy,
     // clusters, and the per-row overhead is spread over twice the work.
     constexpr bool REREAD = VPT * E > 16;
     constexpr int HELD = REREAD ? 1 : VPT;
+    // with the column sums this kernel is the one shortest of issue slots: its waiting warps sleep
+    // between polls (see mbar_wait_bounded)
+    constexpr int SLEEP = (HAS_STATS && PARAM_GRADS) ? 150 : 0;
 
     const uint32_t rank = cluster_cta_rank();
     const uint32_t nranks = cluster_cta_count();
@@ -684,7 +688,7 @@ layernorm_bwd_reg_kernel(const T* __restrict__ x, const T* __restrict__ dy,
             r.mean = next_shift;
             if (it + 1 < my_rows) next_shift = row_first_element(x, row + a.num_clusters, a.cols);
         }
-        if (g.local > 0) mbar_wait_bounded(smem_u32(&ctl.full[ring.stage]), ring.parity, a.status);
+        if (g.local > 0) mbar_wait_bounded<SLEEP>(smem_u32(&ctl.full[ring.stage]), ring.parity, a.status);
         CREDIT_TRACE_POINT(2, it);
         r.stage = ring.stage;
         if (!REREAD) {
@@ -711,7 +715,7 @@ layernorm_bwd_reg_kernel(const T* __restrict__ x, const T* __restrict__ dy,
         CREDIT_TRACE_POINT(4, it);
         // the stage is free once the row is in registers, or (REREAD) once its outputs are written
         if (!REREAD && g.local > 0 && (threadIdx.x & 31) == 0) mbar_arrive(smem_u32(&ctl.empty[ring.stage]));
-        exchange_send_split<W>(keep, ctl.ex, it, rank, nranks, a.status);
+        exchange_send_split<W, SLEEP>(keep, ctl.ex, it, rank, nranks, a.status);
         ring.advance(a.stages);
         CREDIT_TRACE_POINT(6, it);
     };
@@ -729,7 +733,7 @@ layernorm_bwd_reg_kernel(const T* __restrict__ x, const T* __restrict__ dy,
         const int row = cluster + it * a.num_clusters;
         float sums[2];
         CREDIT_TRACE_POINT(7, it);
-        exchange_receive_split(HAS_STATS ? ctl.ex : ctl.ex2, it, nranks, a.status, sums);
+        exchange_receive_split<SLEEP>(HAS_STATS ? ctl.ex : ctl.ex2, it, nranks, a.status, sums);
         CREDIT_TRACE_POINT(8, it);
         const float2 neg_mean = splat(-r.mean), rstd2 = splat(r.rstd);
         const float2 ca = splat(-r.rstd * r.rstd * r.rstd * (sums[1] * inv_cols));
