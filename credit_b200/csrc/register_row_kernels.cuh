@@ -179,6 +179,33 @@ __device__ __forceinline__ void exchange_receive_split(ExchangeStream<2>& s, int
     total[1] = __shfl_sync(0xffffffffu, t, 16);
 }
 
+// warp_sum_split of the NEXT row's two partials and exchange_receive_split of THIS row in one
+// step. The two shuffle trees are independent; issued round by round side by side they cost the
+// latency of one, and that latency is on every warp's per-row chain. Returns `keep` as
+// warp_sum_split does; `total` as exchange_receive_split does.
+template <int SLEEP_NS = 0>
+__device__ __forceinline__ float reduce_and_receive_split(float a, float b, ExchangeStream<2>& s, int it_recv,
+                                                          uint32_t nranks, int* status, float (&total)[2]) {
+    const int buf = it_recv & (kExchangeBuffers - 1);
+    const uint32_t phase = (static_cast<uint32_t>(it_recv) / kExchangeBuffers) & 1u;
+    mbar_wait_bounded<SLEEP_NS>(smem_u32(&s.bar[buf]), phase, status);
+    CREDIT_TRACE_POINT(10, it_recv);
+    const uint32_t lane = threadIdx.x & 31;
+    const uint32_t half = lane >> 4, idx = lane & 15;
+    float t = idx < nranks ? (&s.slot[buf][0][0])[2 * idx + half] : 0.0f;
+    float keep = half != 0 ? b : a;
+    const float give = half != 0 ? a : b;
+    keep += __shfl_xor_sync(0xffffffffu, give, 16);
+#pragma unroll
+    for (int offset = 8; offset > 0; offset >>= 1) {
+        t += __shfl_xor_sync(0xffffffffu, t, offset);
+        keep += __shfl_xor_sync(0xffffffffu, keep, offset);
+    }
+    total[0] = __shfl_sync(0xffffffffu, t, 0);
+    total[1] = __shfl_sync(0xffffffffu, t, 16);
+    return keep;
+}
+
 // A 16-byte vector of row elements as packed fp32 pairs, so that the elementwise
 // arithmetic can use the two-wide fp32 instructions of sm_100
 // (fma/add/mul.rn.f32x2 through __ffma2_rn, __fadd2_rn, __fmul2_rn): half the
@@ -321,6 +348,23 @@ __device__ __forceinline__ void pipeline_rows(int my_rows, Regs& r0, Regs& r1, F
             if (MIDDLE) middle(r1, it + 1);
             if (it + 2 < my_rows) front(r0, it + 2);
             back(r1, it + 1);
+        }
+    }
+}
+
+// The same two-deep pipeline for kernels with one reduction per row whose `fused(next, it + 1,
+// current, it)` does front(next) and back(current) with the two shuffle trees side by side:
+//   front(0); { fused(i+1, i); } ... back(last)
+template <typename Regs, typename Front, typename Fused, typename Back>
+__device__ __forceinline__ void pipeline_rows_fused(int my_rows, Regs& r0, Regs& r1, Front front, Fused fused,
+                                                    Back back) {
+    if (my_rows > 0) front(r0, 0);
+    for (int it = 0; it < my_rows; it += 2) {
+        if (it + 1 < my_rows) fused(r1, it + 1, r0, it);
+        else back(r0, it);
+        if (it + 1 < my_rows) {
+            if (it + 2 < my_rows) fused(r0, it + 2, r1, it + 1);
+            else back(r1, it + 1);
         }
     }
 }
@@ -509,24 +553,28 @@ layernorm_fwd_reg_kernel(const T* __restrict__ x, const float* __restrict__ gamm
     // the shift of the next row is fetched one step ahead so its latency is hidden
     float next_shift = my_rows > 0 ? row_first_element(x, cluster, a.cols) : 0.0f;
 
-    auto front = [&](Regs& r, int it) {
+    // the row into registers and this thread's two partial sums of it
+    auto front_load = [&](Regs& r, int it, float (&part)[2]) {
         if (fills_ring && it > 0) filler.recycle(it);
         r.shift = next_shift;
         if (it + 1 < my_rows) next_shift = row_first_element(x, cluster + (it + 1) * a.num_clusters, a.cols);
         if (g.local > 0) mbar_wait_bounded(smem_u32(&ctl.full[ring.stage]), ring.parity, a.status);
         load_raw<THREADS, VPT, FULL>(
             reinterpret_cast<const uint4*>(stage_tile<T, 1>(data, ring.stage, 0, a.slice_elems)), nvec, r.raw);
-        float part[2];
         shifted_partials<T, THREADS, VPT, FULL>(r.raw, nvec, r.shift, part[0], part[1]);
-        const float keep = warp_sum_split(part[0], part[1]);
         if (g.local > 0 && (threadIdx.x & 31) == 0) mbar_arrive(smem_u32(&ctl.empty[ring.stage]));
+    };
+    auto front_send = [&](float keep, int it) {
         exchange_send_split<W>(keep, ctl.ex, it, rank, nranks, a.status);
         ring.advance(a.stages);
     };
-    auto back = [&](const Regs& r, int it) {
+    auto front = [&](Regs& r, int it) {
+        float part[2];
+        front_load(r, it, part);
+        front_send(warp_sum_split(part[0], part[1]), it);
+    };
+    auto back_store = [&](const Regs& r, int it, const float (&sq)[2]) {
         const int row = cluster + it * a.num_clusters;
-        float sq[2];
-        exchange_receive_split(ctl.ex, it, nranks, a.status, sq);
         float mean, var;
         moments_from_shifted(sq[0], sq[1], r.shift, a.cols, mean, var);
         const float rstd = rsqrtf(var + eps);
@@ -554,8 +602,21 @@ layernorm_fwd_reg_kernel(const T* __restrict__ x, const float* __restrict__ gamm
             if (FULL || v < nvec) __stcs(out + v, PairVec<T>::pack(xv));
         }
     };
+    auto back = [&](const Regs& r, int it) {
+        float sq[2];
+        exchange_receive_split(ctl.ex, it, nranks, a.status, sq);
+        back_store(r, it, sq);
+    };
+    // front(next) and back(current) with the two shuffle trees side by side
+    auto fused = [&](Regs& rn, int itn, const Regs& ro, int ito) {
+        float part[2], sq[2];
+        front_load(rn, itn, part);
+        const float keep = reduce_and_receive_split(part[0], part[1], ctl.ex, ito, nranks, a.status, sq);
+        front_send(keep, itn);
+        back_store(ro, ito, sq);
+    };
     Regs r0, r1;
-    pipeline_rows<false>(my_rows, r0, r1, front, NoMiddle(), back);
+    pipeline_rows_fused(my_rows, r0, r1, front, fused, back);
 }
 
 // ---------------------------------------------------------------------------
@@ -655,7 +716,7 @@ layernorm_bwd_reg_kernel(const T* __restrict__ x, const T* __restrict__ dy,
     float next_shift = (!HAS_STATS && my_rows > 0) ? row_first_element(x, cluster, a.cols) : 0.0f;
 
     // warp-reduced S1 = sum g and S2 = sum g * (x - mean) over this warp's columns
-    auto sums_of_g = [&](const Regs& r) -> float {
+    auto partials_of_g = [&](const Regs& r, float (&part)[2]) {
         const float2 neg_mean = splat(-r.mean);
         float2 s1 = splat(0.0f), s2 = splat(0.0f);
 #pragma unroll
@@ -675,9 +736,16 @@ layernorm_bwd_reg_kernel(const T* __restrict__ x, const T* __restrict__ dy,
             }
         }
         const float t1 = s1.x + s1.y, t2 = s2.x + s2.y;
-        return warp_sum_split(t1, sizeof(T) == 2 ? fmaf(-r.mean, t1, t2) : t2);
+        part[0] = t1;
+        part[1] = sizeof(T) == 2 ? fmaf(-r.mean, t1, t2) : t2;
     };
-    auto front = [&](Regs& r, int it) {
+    auto sums_of_g = [&](const Regs& r) -> float {
+        float part[2];
+        partials_of_g(r, part);
+        return warp_sum_split(part[0], part[1]);
+    };
+    // the row into registers (or located in its stage) and this thread's two partial sums of it
+    auto front_load = [&](Regs& r, int it, float (&part)[2]) {
         const int row = cluster + it * a.num_clusters;
         CREDIT_TRACE_POINT(1, it);
         if (fills_ring && it > 0) filler.recycle(it, REREAD ? 2 : 1);
@@ -697,27 +765,29 @@ layernorm_bwd_reg_kernel(const T* __restrict__ x, const T* __restrict__ dy,
             load_raw<THREADS, HELD, FULL>(
                 reinterpret_cast<const uint4*>(stage_tile<T, 2>(data, ring.stage, 1, a.slice_elems)), nvec, r.dy);
         }
-        float keep;   // the row's two partials, split over the halves of the warp
         if (HAS_STATS) {
-            keep = sums_of_g(r);
+            partials_of_g(r, part);
         } else if (REREAD) {
             uint4 raw[VPT];
-            float part[2];
             load_raw<THREADS, VPT, FULL>(
                 reinterpret_cast<const uint4*>(stage_tile<T, 2>(data, ring.stage, 0, a.slice_elems)), nvec, raw);
             shifted_partials<T, THREADS, VPT, FULL>(raw, nvec, r.mean, part[0], part[1]);
-            keep = warp_sum_split(part[0], part[1]);
         } else {
-            float part[2];
             shifted_partials<T, THREADS, HELD, FULL>(r.x, nvec, r.mean, part[0], part[1]);
-            keep = warp_sum_split(part[0], part[1]);
         }
         CREDIT_TRACE_POINT(4, it);
         // the stage is free once the row is in registers, or (REREAD) once its outputs are written
         if (!REREAD && g.local > 0 && (threadIdx.x & 31) == 0) mbar_arrive(smem_u32(&ctl.empty[ring.stage]));
+    };
+    auto front_send = [&](float keep, int it) {   // keep: the two partials split over the halves of the warp
         exchange_send_split<W, SLEEP>(keep, ctl.ex, it, rank, nranks, a.status);
         ring.advance(a.stages);
         CREDIT_TRACE_POINT(6, it);
+    };
+    auto front = [&](Regs& r, int it) {
+        float part[2];
+        front_load(r, it, part);
+        front_send(warp_sum_split(part[0], part[1]), it);
     };
     // stats recomputed only: finish the statistics, start the exchange of S1, S2
     auto middle = [&](Regs& r, int it) {
@@ -729,11 +799,8 @@ layernorm_bwd_reg_kernel(const T* __restrict__ x, const T* __restrict__ dy,
         r.rstd = rsqrtf(var + eps);
         exchange_send_split<W>(sums_of_g(r), ctl.ex2, it, rank, nranks, a.status);
     };
-    auto back = [&](const Regs& r, int it) {
+    auto back_store = [&](const Regs& r, int it, const float (&sums)[2]) {
         const int row = cluster + it * a.num_clusters;
-        float sums[2];
-        CREDIT_TRACE_POINT(7, it);
-        exchange_receive_split<SLEEP>(HAS_STATS ? ctl.ex : ctl.ex2, it, nranks, a.status, sums);
         CREDIT_TRACE_POINT(8, it);
         const float2 neg_mean = splat(-r.mean), rstd2 = splat(r.rstd);
         const float2 ca = splat(-r.rstd * r.rstd * r.rstd * (sums[1] * inv_cols));
@@ -774,10 +841,26 @@ layernorm_bwd_reg_kernel(const T* __restrict__ x, const T* __restrict__ dy,
         }
         CREDIT_TRACE_POINT(9, it);
     };
+    auto back = [&](const Regs& r, int it) {
+        float sums[2];
+        CREDIT_TRACE_POINT(7, it);
+        exchange_receive_split<SLEEP>(HAS_STATS ? ctl.ex : ctl.ex2, it, nranks, a.status, sums);
+        back_store(r, it, sums);
+    };
+    // statistics given: front(next) and back(current) with the two shuffle trees side by side
+    auto fused = [&](Regs& rn, int itn, const Regs& ro, int ito) {
+        float part[2], sums[2];
+        front_load(rn, itn, part);
+        CREDIT_TRACE_POINT(7, ito);
+        const float keep = reduce_and_receive_split<SLEEP>(part[0], part[1], ctl.ex, ito, nranks, a.status, sums);
+        front_send(keep, itn);
+        back_store(ro, ito, sums);
+    };
 
     Regs r0, r1;
     r0.mean = r0.rstd = r1.mean = r1.rstd = 0.0f;
-    pipeline_rows<!HAS_STATS>(my_rows, r0, r1, front, middle, back);
+    if (HAS_STATS) pipeline_rows_fused(my_rows, r0, r1, front, fused, back);
+    else pipeline_rows<true>(my_rows, r0, r1, front, middle, back);
 
     if (PARAM_GRADS) {
         float* out_g = partials + (static_cast<size_t>(cluster) * 2 + 0) * a.cols + g.start;
