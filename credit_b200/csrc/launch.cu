@@ -469,8 +469,9 @@ int plan_static(int workload, const Shape& s, int dtype, const credit_launch_opt
     if (!p->aligned || p->schedule == CREDIT_SCHEDULE_ROW_PER_CLUSTER) {
         stages = 1;
     } else if (stages == 0) {
-        // measured on B200: two stages are best when two arrays are staged, three otherwise
-        stages = p->vectors_per_thread > 0 ? (nin == 2 ? 2 : 3)
+        // measured on B200: three stages, except two where two fp32 arrays (or two 16-bit arrays
+        // without the column sums) are staged
+        stages = p->vectors_per_thread > 0 ? ((nin == 2 && !(grads && s.elem_bytes == 2)) ? 2 : 3)
                                            : std::max(1, std::min(4, kAutoRingBytes / stage_bytes));
         while (stages > 1 && control_bytes + stages * stage_bytes > max_smem) --stages;
     }

@@ -179,6 +179,25 @@ __device__ __forceinline__ void exchange_receive_split(ExchangeStream<2>& s, int
     total[1] = __shfl_sync(0xffffffffu, t, 16);
 }
 
+// One partial per row: warp_sum of the NEXT row's partial and exchange_receive<1> of THIS row with
+// the two shuffle trees side by side (see reduce_and_receive_split).
+__device__ __forceinline__ float reduce_and_receive_one(float a, ExchangeStream<1>& s, int it_recv, uint32_t nranks,
+                                                        int* status, float& total) {
+    const int buf = it_recv & (kExchangeBuffers - 1);
+    const uint32_t phase = (static_cast<uint32_t>(it_recv) / kExchangeBuffers) & 1u;
+    mbar_wait_bounded(smem_u32(&s.bar[buf]), phase, status);
+    const uint32_t lane = threadIdx.x & 31;
+    float t = lane < nranks ? s.slot[buf][0][lane] : 0.0f;
+    a += __shfl_xor_sync(0xffffffffu, a, 16);
+#pragma unroll
+    for (int offset = kMaxClusterSize / 2; offset > 0; offset >>= 1) {
+        t += __shfl_xor_sync(0xffffffffu, t, offset);
+        a += __shfl_xor_sync(0xffffffffu, a, offset);
+    }
+    total = __shfl_sync(0xffffffffu, t, 0);
+    return a;
+}
+
 // warp_sum_split of the NEXT row's two partials and exchange_receive_split of THIS row in one
 // step. The two shuffle trees are independent; issued round by round side by side they cost the
 // latency of one, and that latency is on every warp's per-row chain. Returns `keep` as
@@ -369,6 +388,24 @@ __device__ __forceinline__ void pipeline_rows_fused(int my_rows, Regs& r0, Regs&
     }
 }
 
+// Kernels with two dependent reductions per row: middle(i) finishes the first, and front(i+1)
+// and back(i) are again one fused step.
+template <typename Regs, typename Front, typename Middle, typename Fused, typename Back>
+__device__ __forceinline__ void pipeline_rows_middle_fused(int my_rows, Regs& r0, Regs& r1, Front front,
+                                                           Middle middle, Fused fused, Back back) {
+    if (my_rows > 0) front(r0, 0);
+    for (int it = 0; it < my_rows; it += 2) {
+        middle(r0, it);
+        if (it + 1 < my_rows) fused(r1, it + 1, r0, it);
+        else back(r0, it);
+        if (it + 1 < my_rows) {
+            middle(r1, it + 1);
+            if (it + 2 < my_rows) fused(r0, it + 2, r1, it + 1);
+            else back(r1, it + 1);
+        }
+    }
+}
+
 struct NoMiddle {
     template <typename Regs>
     __device__ __forceinline__ void operator()(Regs&, int) const {}
@@ -416,7 +453,8 @@ rmsnorm_fwd_reg_kernel(const T* __restrict__ x, const float* __restrict__ gamma,
     const float inv_cols = 1.0f / static_cast<float>(a.cols);
     struct Regs { uint4 raw[VPT]; };
 
-    auto front = [&](Regs& r, int it) {
+    // the row into registers; returns this thread's sum of squares
+    auto front_load = [&](Regs& r, int it) -> float {
         if (fills_ring && it > 0) filler.recycle(it);
         if (g.local > 0) mbar_wait_bounded(smem_u32(&ctl.full[ring.stage]), ring.parity, a.status);
         load_raw<THREADS, VPT, FULL>(
@@ -432,16 +470,18 @@ rmsnorm_fwd_reg_kernel(const T* __restrict__ x, const float* __restrict__ gamma,
                 q1 = __ffma2_rn(xv[j + 1], xv[j + 1], q1);
             }
         }
-        float part[1] = {warp_sum((q0.x + q0.y) + (q1.x + q1.y))};
         if (g.local > 0 && (threadIdx.x & 31) == 0) mbar_arrive(smem_u32(&ctl.empty[ring.stage]));
+        return (q0.x + q0.y) + (q1.x + q1.y);
+    };
+    auto front_send = [&](float warp_total, int it) {
+        const float part[1] = {warp_total};
         exchange_send<1, W>(part, ctl.ex, it, rank, nranks, a.status);
         ring.advance(a.stages);
     };
-    auto back = [&](const Regs& r, int it) {
+    auto front = [&](Regs& r, int it) { front_send(warp_sum(front_load(r, it)), it); };
+    auto back_store = [&](const Regs& r, int it, float sumsq) {
         const int row = cluster + it * a.num_clusters;
-        float sumsq[1];
-        exchange_receive<1>(ctl.ex, it, nranks, a.status, sumsq);
-        const float2 scale = splat(rsqrtf(sumsq[0] * inv_cols + eps));
+        const float2 scale = splat(rsqrtf(sumsq * inv_cols + eps));
         uint4* out = reinterpret_cast<uint4*>(y + static_cast<size_t>(row) * a.cols + g.start);
 #pragma unroll
         for (int i = 0; i < VPT; ++i) {
@@ -453,8 +493,20 @@ rmsnorm_fwd_reg_kernel(const T* __restrict__ x, const float* __restrict__ gamma,
             if (FULL || v < nvec) __stcs(out + v, PairVec<T>::pack(xv));
         }
     };
+    auto back = [&](const Regs& r, int it) {
+        float sumsq[1];
+        exchange_receive<1>(ctl.ex, it, nranks, a.status, sumsq);
+        back_store(r, it, sumsq[0]);
+    };
+    // front(next) and back(current) with the two shuffle trees side by side
+    auto fused = [&](Regs& rn, int itn, const Regs& ro, int ito) {
+        float sumsq;
+        const float warp_total = reduce_and_receive_one(front_load(rn, itn), ctl.ex, ito, nranks, a.status, sumsq);
+        front_send(warp_total, itn);
+        back_store(ro, ito, sumsq);
+    };
     Regs r0, r1;
-    pipeline_rows<false>(my_rows, r0, r1, front, NoMiddle(), back);
+    pipeline_rows_fused(my_rows, r0, r1, front, fused, back);
 }
 
 // Shifted one-pass statistics of the vectors held in `raw`: with K = the first
@@ -847,12 +899,13 @@ layernorm_bwd_reg_kernel(const T* __restrict__ x, const T* __restrict__ dy,
         exchange_receive_split<SLEEP>(HAS_STATS ? ctl.ex : ctl.ex2, it, nranks, a.status, sums);
         back_store(r, it, sums);
     };
-    // statistics given: front(next) and back(current) with the two shuffle trees side by side
+    // front(next) and back(current) with the two shuffle trees side by side
     auto fused = [&](Regs& rn, int itn, const Regs& ro, int ito) {
         float part[2], sums[2];
         front_load(rn, itn, part);
         CREDIT_TRACE_POINT(7, ito);
-        const float keep = reduce_and_receive_split<SLEEP>(part[0], part[1], ctl.ex, ito, nranks, a.status, sums);
+        const float keep = reduce_and_receive_split<SLEEP>(part[0], part[1], HAS_STATS ? ctl.ex : ctl.ex2, ito, nranks,
+                                                           a.status, sums);
         front_send(keep, itn);
         back_store(ro, ito, sums);
     };
@@ -860,7 +913,7 @@ layernorm_bwd_reg_kernel(const T* __restrict__ x, const T* __restrict__ dy,
     Regs r0, r1;
     r0.mean = r0.rstd = r1.mean = r1.rstd = 0.0f;
     if (HAS_STATS) pipeline_rows_fused(my_rows, r0, r1, front, fused, back);
-    else pipeline_rows<true>(my_rows, r0, r1, front, middle, back);
+    else pipeline_rows_middle_fused(my_rows, r0, r1, front, middle, fused, back);
 
     if (PARAM_GRADS) {
         float* out_g = partials + (static_cast<size_t>(cluster) * 2 + 0) * a.cols + g.start;
