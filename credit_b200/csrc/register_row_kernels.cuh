@@ -25,16 +25,22 @@
 //   * a warp waits on its own CTA's mbarrier until all P contributions of the row
 //     have landed, folds them itself (same order in every warp of every CTA, so all
 //     agree bit for bit) and produces its outputs.
-// Rows are software-pipelined two deep per warp: the partials of row i+1 are sent
-// before the warp waits for row i, so the DSMEM round trip, the shuffle trees and
-// the shared-memory reads of one row overlap the arithmetic and stores of another
-// row and of other warps. Slot buffer and mbarrier of row i are number i mod 4: a
-// warp can only start row i+4 after it has seen row i+2 complete, i.e. after
-// every CTA has sent row i+2, which its warp 0 does after all its warps have
-// delivered their partials of row i+2, which each does after reading the slots of
-// row i; so a buffer is never overwritten while it is read, and its mbarrier is
-// never re-armed before its previous phase has completed. The same argument, one
-// level down, covers the two CTA-local partial buffers.
+// Rows are software-pipelined two deep per warp. One step of a warp: wait for row
+// i+1 in the ring, load it into registers, compute this thread's partial sums;
+// wait for row i's exchange; run the warp reduction of row i+1's partials and the
+// fold of row i's slots as two shuffle trees side by side (independent, so they
+// cost the latency of one); deliver row i+1's partials; write row i's outputs
+// from the registers that still hold row i. The DSMEM round trip of one row thus
+// overlaps the loads and arithmetic of the next, and other warps' work. Waits
+// poll (mbarrier.test_wait): a suspended try_wait wakes late.
+// Slot buffer and mbarrier of row i are number i mod 4. A CTA sends row i+4 only
+// after all its warps have delivered row i+4, each of which has by then received
+// row i+3, which every CTA sent only after all its warps had delivered row i+3,
+// i.e. after they had read the slots of row i+2 and, earlier, of row i: a buffer
+// is never overwritten while it is read, and its mbarrier is never re-armed
+// before every waiter has seen its previous phase complete (a peer's bytes may
+// land before the local arming arrival; the phase cannot complete without it).
+// The same argument, one level down, covers the two CTA-local partial buffers.
 //
 // Same arithmetic as the reference's cluster_bwd_staged_kernel family
 // (src/workloads/layernorm_backward.cu:376-438), re-designed for sm_100a.
