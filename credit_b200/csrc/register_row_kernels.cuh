@@ -357,28 +357,10 @@ __device__ __forceinline__ void load_raw(const uint4* tile, int nvec, uint4 (&ra
     }
 }
 
-// The two-deep software pipeline every compute warp runs:
-//   front(0); { front(i+1); back(i); } ...
-// `front` ends with the row's partials on their way, `back` starts by waiting for
-// them. MIDDLE (kernels with two dependent reductions) runs between them.
-template <bool MIDDLE, typename Regs, typename Front, typename Middle, typename Back>
-__device__ __forceinline__ void pipeline_rows(int my_rows, Regs& r0, Regs& r1, Front front,
-                                              Middle middle, Back back) {
-    if (my_rows > 0) front(r0, 0);
-    for (int it = 0; it < my_rows; it += 2) {
-        if (MIDDLE) middle(r0, it);
-        if (it + 1 < my_rows) front(r1, it + 1);
-        back(r0, it);
-        if (it + 1 < my_rows) {
-            if (MIDDLE) middle(r1, it + 1);
-            if (it + 2 < my_rows) front(r0, it + 2);
-            back(r1, it + 1);
-        }
-    }
-}
-
-// The same two-deep pipeline for kernels with one reduction per row whose `fused(next, it + 1,
-// current, it)` does front(next) and back(current) with the two shuffle trees side by side:
+// The two-deep software pipeline every compute warp runs, for kernels with one reduction per
+// row. `front` ends with the row's partials delivered, `back` starts by waiting for the row's
+// exchange; `fused(next, it + 1, current, it)` is front(next) and back(current) in one step with
+// their two shuffle trees side by side:
 //   front(0); { fused(i+1, i); } ... back(last)
 template <typename Regs, typename Front, typename Fused, typename Back>
 __device__ __forceinline__ void pipeline_rows_fused(int my_rows, Regs& r0, Regs& r1, Front front, Fused fused,
@@ -411,11 +393,6 @@ __device__ __forceinline__ void pipeline_rows_middle_fused(int my_rows, Regs& r0
         }
     }
 }
-
-struct NoMiddle {
-    template <typename Regs>
-    __device__ __forceinline__ void operator()(Regs&, int) const {}
-};
 
 // ---------------------------------------------------------------------------
 // RMSNorm forward
