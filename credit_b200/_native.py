@@ -149,6 +149,22 @@ PROTOTYPES: dict[str, tuple] = {
     "credit_row_reduce_host": (
         c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, _OPTS_P, c_void_p,
                 c_size_t, c_void_p]),
+    "credit_rmsnorm_forward_host_scratch_bytes": (c_size_t, [c_int64, c_int64, c_int]),
+    "credit_rmsnorm_forward_host": (
+        c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_float, c_int, _OPTS_P, c_void_p, c_size_t,
+                c_void_p]),
+    "credit_layernorm_forward_host_scratch_bytes": (c_size_t, [c_int64, c_int64, c_int]),
+    "credit_layernorm_forward_host": (
+        c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_float, c_int,
+                _OPTS_P, c_void_p, c_size_t, c_void_p]),
+    "credit_layernorm_backward_stats_host_scratch_bytes": (c_size_t, [c_int64, c_int64, c_int, _OPTS_P]),
+    "credit_layernorm_backward_stats_host": (
+        c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
+                c_int, _OPTS_P, c_void_p, c_size_t, c_void_p]),
+    "credit_ffn_forward_host_scratch_bytes": (c_size_t, [c_int64, c_int64, c_int64]),
+    "credit_ffn_forward_host": (
+        c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_float, c_void_p,
+                c_size_t, c_void_p]),
 }
 
 _lib: ctypes.CDLL | None = None

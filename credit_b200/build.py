@@ -36,6 +36,7 @@ LIB_SOURCES = [
     "tables_block_read.cu",
     "tables_row_ops.cu",
     "bench_entry.cu",
+    "host_entry.cu",
 ]
 OBJ_DIR = LIB_DIR / "obj"
 # name of the executable -> (source, links against the shared library)

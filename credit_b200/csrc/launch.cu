@@ -19,6 +19,7 @@
 
 #include "../../include/credit_b200.h"
 #include "cluster_primitives.cuh"
+#include "error_state.h"
 #include "kernel_tables.h"
 #include "launch_args.h"
 
@@ -42,6 +43,18 @@ int fail(int code, const char* fmt, ...) {
 int cuda_fail(cudaError_t err, const char* what) {
     return fail(CREDIT_ERR_CUDA, "%s: %s", what, cudaGetErrorString(err));
 }
+
+}  // namespace
+
+int report_error(int code, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(t_last_error, sizeof(t_last_error), fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+namespace {
 
 #define CREDIT_CUDA_TRY(expr)                                  \
     do {                                                       \
@@ -979,136 +992,32 @@ int credit_layernorm_backward_stats_static(const void* x, const void* dy, const 
                                            const float* mean, const float* rstd, void* dx,
                                            float* dgamma, float* dbeta, int64_t rows, int64_t cols,
                                            int dtype, const credit_launch_opts* opts, void* stream) {
-    // Size first: a shape whose partial sums do not fit is refused before any pointer is used.
-    const size_t need = credit_layernorm_backward_stats_workspace_bytes(rows, cols, dtype, opts);
-    if (need == 0 && rows > 0) {
-        // the planner has already recorded why this shape or these options are unusable
-        credit_plan_info ignored;
-        return credit_plan(CREDIT_WL_LAYERNORM_BACKWARD_STATS, rows, cols, dtype, opts, &ignored);
-    }
-    if (need > kStaticScratchBytes)
+    if ((dgamma == nullptr) != (dbeta == nullptr))
+        return fail(CREDIT_ERR_INVALID_ARGUMENT, "dgamma and dbeta must both be given or both be NULL");
+    // Without the column sums no scratch is used at all.
+    if (dgamma == nullptr)
+        return credit_layernorm_backward_stats(x, dy, gamma, mean, rstd, dx, nullptr, nullptr, rows, cols, dtype,
+                                               opts, nullptr, 0, stream);
+    // Size first: a shape whose partial sums do not fit is refused before any pointer is
+    // dereferenced. What counts is the path this very call would take: the built-in array is
+    // 256-byte aligned, so only the caller's own pointers decide between the register path
+    // (one partial per resident cluster) and the column-sum fallback (one per block of rows).
+    Resolved r;
+    int rc = resolve(CREDIT_WL_LAYERNORM_BACKWARD_STATS, rows, cols, dtype, opts,
+                     aligned16(x) && aligned16(dy) && aligned16(gamma) && aligned16(dx), true, &r);
+    if (rc != CREDIT_OK) return rc;
+    if (r.plan.workspace_bytes > kStaticScratchBytes)
         return fail(CREDIT_ERR_WORKSPACE,
                     "this shape needs %zu B of scratch but the built-in scratch holds %zu B; use "
                     "credit_layernorm_backward_stats with a caller workspace",
-                    need, kStaticScratchBytes);
+                    r.plan.workspace_bytes, kStaticScratchBytes);
     void* scratch = nullptr;
-    int rc = static_scratch_for_current_device(&scratch);
+    rc = static_scratch_for_current_device(&scratch);
     if (rc != CREDIT_OK) return rc;
     // Nothing in the scratch has to start at zero: every partial sum the finishing
     // kernel reads is written earlier in this same call.
     return credit_layernorm_backward_stats(x, dy, gamma, mean, rstd, dx, dgamma, dbeta, rows, cols,
                                            dtype, opts, scratch, kStaticScratchBytes, stream);
-}
-
-// ---------------------------------------------------------------------------
-// host-buffer path
-// ---------------------------------------------------------------------------
-namespace {
-
-struct HostPipe {
-    bool ready = false;
-    cudaStream_t copy_stream = nullptr;
-    cudaEvent_t loaded[2] = {nullptr, nullptr};   // block is on the device
-    cudaEvent_t consumed[2] = {nullptr, nullptr}; // block has been reduced
-};
-std::map<int, HostPipe> g_host_pipes;
-
-int host_pipe(int device, HostPipe** out) {
-    std::lock_guard<std::mutex> lock(g_mutex);
-    HostPipe& hp = g_host_pipes[device];
-    if (!hp.ready) {
-        CREDIT_CUDA_TRY(cudaStreamCreateWithFlags(&hp.copy_stream, cudaStreamNonBlocking));
-        for (int i = 0; i < 2; ++i) {
-            CREDIT_CUDA_TRY(cudaEventCreateWithFlags(&hp.loaded[i], cudaEventDisableTiming));
-            CREDIT_CUDA_TRY(cudaEventCreateWithFlags(&hp.consumed[i], cudaEventDisableTiming));
-        }
-        hp.ready = true;
-    }
-    *out = &hp;
-    return CREDIT_OK;
-}
-
-constexpr size_t kHostOutAlign = 256;
-size_t host_out_bytes(int64_t rows) {
-    // sum, max (fp32) and argmax (int64) on the device, each 256-byte aligned
-    const size_t a = (static_cast<size_t>(rows) * 4 + kHostOutAlign - 1) / kHostOutAlign * kHostOutAlign;
-    const size_t b = (static_cast<size_t>(rows) * 8 + kHostOutAlign - 1) / kHostOutAlign * kHostOutAlign;
-    return 2 * a + b;
-}
-constexpr int64_t kHostMinBlockBytes = 32ll << 20;
-
-}  // namespace
-
-size_t credit_row_reduce_host_scratch_bytes(int64_t rows, int64_t cols) {
-    if (rows <= 0 || cols <= 0) return 0;
-    const int64_t row_bytes = cols * 4;
-    int64_t block_rows = std::max<int64_t>(1, kHostMinBlockBytes / row_bytes);
-    block_rows = std::min(block_rows, rows);
-    const size_t in_bytes = (static_cast<size_t>(block_rows * row_bytes) + 255) / 256 * 256;
-    return 2 * in_bytes + host_out_bytes(rows);
-}
-
-int credit_row_reduce_host(const float* x_host, float* out_sum_host, float* out_max_host,
-                           int64_t* out_argmax_host, int64_t rows, int64_t cols,
-                           const credit_launch_opts* opts, void* scratch, size_t scratch_bytes,
-                           void* stream) {
-    if (x_host == nullptr || out_sum_host == nullptr || out_max_host == nullptr ||
-        out_argmax_host == nullptr)
-        return fail(CREDIT_ERR_INVALID_ARGUMENT, "host input and outputs must not be NULL");
-    Shape shape;
-    int rc = check_shape(rows, cols, CREDIT_F32, &shape);
-    if (rc != CREDIT_OK) return rc;
-    if (rows == 0) return CREDIT_OK;
-    const size_t need = credit_row_reduce_host_scratch_bytes(rows, cols);
-    if (scratch == nullptr || scratch_bytes < need || !aligned16(scratch))
-        return fail(CREDIT_ERR_WORKSPACE, "scratch of %zu B given, %zu B (16-byte aligned) needed",
-                    scratch_bytes, need);
-    int device = 0;
-    CREDIT_CUDA_TRY(cudaGetDevice(&device));
-    HostPipe* hp = nullptr;
-    rc = host_pipe(device, &hp);
-    if (rc != CREDIT_OK) return rc;
-    cudaStream_t compute = static_cast<cudaStream_t>(stream);
-
-    const size_t out_bytes = host_out_bytes(rows);
-    const size_t row_bytes = static_cast<size_t>(cols) * 4;
-    const size_t per_buffer = ((scratch_bytes - out_bytes) / 2) / 256 * 256;
-    int64_t block_rows = std::min<int64_t>(rows, static_cast<int64_t>(per_buffer / row_bytes));
-    if (block_rows < 1) return fail(CREDIT_ERR_WORKSPACE, "scratch cannot hold one row twice");
-    char* base = static_cast<char*>(scratch);
-    float* in_buf[2] = {reinterpret_cast<float*>(base), reinterpret_cast<float*>(base + per_buffer)};
-    char* outs = base + 2 * per_buffer;
-    const size_t a = (static_cast<size_t>(rows) * 4 + kHostOutAlign - 1) / kHostOutAlign * kHostOutAlign;
-    float* d_sum = reinterpret_cast<float*>(outs);
-    float* d_max = reinterpret_cast<float*>(outs + a);
-    int64_t* d_arg = reinterpret_cast<int64_t*>(outs + 2 * a);
-
-    int block = 0;
-    for (int64_t r0 = 0; r0 < rows; r0 += block_rows, ++block) {
-        const int64_t n = std::min(block_rows, rows - r0);
-        const int b = block & 1;
-        if (block >= 2) CREDIT_CUDA_TRY(cudaStreamWaitEvent(hp->copy_stream, hp->consumed[b], 0));
-        CREDIT_CUDA_TRY(cudaMemcpyAsync(in_buf[b], x_host + static_cast<size_t>(r0) * cols,
-                                        static_cast<size_t>(n) * row_bytes, cudaMemcpyHostToDevice,
-                                        hp->copy_stream));
-        CREDIT_CUDA_TRY(cudaEventRecord(hp->loaded[b], hp->copy_stream));
-        CREDIT_CUDA_TRY(cudaStreamWaitEvent(compute, hp->loaded[b], 0));
-        rc = credit_row_reduce(in_buf[b], d_sum + r0, d_max + r0, d_arg + r0, n, cols, opts, stream);
-        if (rc != CREDIT_OK) {
-            cudaStreamSynchronize(hp->copy_stream);
-            cudaStreamSynchronize(compute);
-            return rc;
-        }
-        CREDIT_CUDA_TRY(cudaEventRecord(hp->consumed[b], compute));
-    }
-    CREDIT_CUDA_TRY(cudaMemcpyAsync(out_sum_host, d_sum, static_cast<size_t>(rows) * 4,
-                                    cudaMemcpyDeviceToHost, compute));
-    CREDIT_CUDA_TRY(cudaMemcpyAsync(out_max_host, d_max, static_cast<size_t>(rows) * 4,
-                                    cudaMemcpyDeviceToHost, compute));
-    CREDIT_CUDA_TRY(cudaMemcpyAsync(out_argmax_host, d_arg, static_cast<size_t>(rows) * 8,
-                                    cudaMemcpyDeviceToHost, compute));
-    CREDIT_CUDA_TRY(cudaStreamSynchronize(compute));
-    return CREDIT_OK;
 }
 
 }  // extern "C"

@@ -12,9 +12,12 @@
 //   * unrolled 128-bit read-only loads straight into registers (also the path
 //     for rows that are not 16-byte aligned, then with scalar loads).
 //
-// Maximum semantics: fmaxf-style (a NaN element never becomes the maximum, as in
-// the reference's fmaxf(fabsf()) scan); ties resolve to the lowest column, which
-// is what torch.argmax returns.
+// Maximum semantics are those of torch.amax / torch.argmax: ties resolve to the
+// lowest column, and a NaN element wins over every number (max = NaN, argmax = the
+// column of the row's first NaN). The streaming loop itself is NaN-blind (fmaxf and
+// '>' skip NaNs); a NaN element always turns the row's running sum into NaN, so a CTA
+// whose partial sum is NaN scans its slice once more for the first NaN before the
+// partials are exchanged (rows without NaN or inf - inf never take that path).
 #pragma once
 
 #include <limits.h>
@@ -28,9 +31,23 @@ struct RowBest {
     int index;
 };
 
+// NaN ranks above every number; among equals (two NaNs included) the lower column wins.
 __device__ __forceinline__ RowBest better_of(RowBest a, RowBest b) {
-    const bool take_b = (b.value > a.value) || (b.value == a.value && b.index < a.index);
+    const bool a_nan = a.value != a.value, b_nan = b.value != b.value;
+    const bool same = (a_nan && b_nan) || b.value == a.value;
+    const bool take_b = same ? b.index < a.index : (b_nan || (!a_nan && b.value > a.value));
     return take_b ? b : a;
+}
+
+// Slow path of a CTA whose partial sum came out NaN: the column of the first NaN among this
+// thread's share of the slice (scalar loads from global memory), or INT_MAX.
+template <int THREADS>
+__device__ __noinline__ int first_nan_column(const float* __restrict__ slice, int local, int start) {
+    for (int c = threadIdx.x; c < local; c += THREADS) {
+        const float v = slice[c];
+        if (v != v) return start + c;   // a thread visits its columns in increasing order
+    }
+    return INT_MAX;
 }
 
 __device__ __forceinline__ RowBest warp_best(RowBest v) {
@@ -76,11 +93,16 @@ struct ReduceControl {
 template <int THREADS>
 __device__ __forceinline__ void finish_row(ReduceControl& ctl, float total, RowBest best, int row,
                                            uint32_t parity, uint32_t rank, uint32_t nranks,
+                                           const float* __restrict__ slice, const SliceGeom& g,
                                            float* __restrict__ out_sum, float* __restrict__ out_max,
                                            long long* __restrict__ out_argmax) {
     constexpr int kWarps = THREADS / 32;
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
+    if (__syncthreads_or(total != total)) {
+        const int col = first_nan_column<THREADS>(slice, g.local, g.start);
+        if (col != INT_MAX) best = RowBest{__int_as_float(0x7fc00000), col};
+    }
     total = warp_sum(total);
     best = warp_best(best);
     if (lane == 0) {
@@ -190,7 +212,8 @@ row_reduce_tma_kernel(const float* __restrict__ x, float* __restrict__ out_sum,
             cur.advance(a.stages);
         }
         finish_row<THREADS>(ctl, (acc.x + acc.y) + (acc.z + acc.w), best, row, row_parity, rank,
-                            nranks, out_sum, out_max, out_argmax);
+                            nranks, x + static_cast<size_t>(row) * a.cols + g.start, g, out_sum, out_max,
+                            out_argmax);
         row_parity ^= 1u;
     }
 }
@@ -248,7 +271,7 @@ row_reduce_ldg_kernel(const float* __restrict__ x, float* __restrict__ out_sum,
             }
         }
         finish_row<THREADS>(ctl, (acc.x + acc.y) + (acc.z + acc.w), best, row, row_parity, rank,
-                            nranks, out_sum, out_max, out_argmax);
+                            nranks, src, g, out_sum, out_max, out_argmax);
         row_parity ^= 1u;
     }
 }

@@ -492,9 +492,9 @@ rmsnorm_fwd_reg_kernel(const T* __restrict__ x, const float* __restrict__ gamma,
     pipeline_rows_fused(my_rows, r0, r1, front, fused, back);
 }
 
-// Shifted one-pass statistics of the vectors held in `raw`: with K = the first
-// element of the ROW (the same K in every CTA, so the partials of all CTAs simply
-// add), accumulates sum(x-K) and sum((x-K)^2). K is within a few standard
+// Shifted one-pass statistics of the vectors held in `raw`: with K = a sample of
+// the ROW (row_shift_sample: the same K in every CTA, so the partials of all CTAs
+// simply add), accumulates sum(x-K) and sum((x-K)^2). K is within a few standard
 // deviations of the mean, so the final subtraction loses about one digit instead
 // of log10(mean^2/var). Outputs the per-thread partials.
 template <typename T, int THREADS, int VPT, bool FULL>
@@ -530,9 +530,18 @@ __device__ __forceinline__ void moments_from_shifted(float S, float Q, float shi
     var = fmaxf(Q * inv_n - ds * ds, 0.0f);
 }
 
+// The shift of a row: the median of three of its elements (first, middle, last). Any shift
+// within about ten standard deviations of the mean keeps the relative error of the variance
+// below 1e-5 in fp32 (the error is eps * (shift - mean)^2 / var); a single element can be an
+// outlier far outside that range, the median of three is not unless two of them are. Every
+// thread of every CTA of the cluster reads the same three elements, so all use the same shift.
 template <typename T>
-__device__ __forceinline__ float row_first_element(const T* x, int row, int cols) {
-    return RowVec<T>::to_float(__ldg(x + static_cast<size_t>(row) * cols));
+__device__ __forceinline__ float row_shift_sample(const T* x, int row, int cols) {
+    const T* p = x + static_cast<size_t>(row) * cols;
+    const float a = RowVec<T>::to_float(__ldg(p));
+    const float b = RowVec<T>::to_float(__ldg(p + (cols >> 1)));
+    const float c = RowVec<T>::to_float(__ldg(p + (cols - 1)));
+    return fmaxf(fminf(a, b), fminf(fmaxf(a, b), c));
 }
 
 // ---------------------------------------------------------------------------
@@ -586,13 +595,13 @@ layernorm_fwd_reg_kernel(const T* __restrict__ x, const float* __restrict__ gamm
     RingCursor ring{0, 0u};
     struct Regs { uint4 raw[VPT]; float shift; };
     // the shift of the next row is fetched one step ahead so its latency is hidden
-    float next_shift = my_rows > 0 ? row_first_element(x, cluster, a.cols) : 0.0f;
+    float next_shift = my_rows > 0 ? row_shift_sample(x, cluster, a.cols) : 0.0f;
 
     // the row into registers and this thread's two partial sums of it
     auto front_load = [&](Regs& r, int it, float (&part)[2]) {
         if (fills_ring && it > 0) filler.recycle(it);
         r.shift = next_shift;
-        if (it + 1 < my_rows) next_shift = row_first_element(x, cluster + (it + 1) * a.num_clusters, a.cols);
+        if (it + 1 < my_rows) next_shift = row_shift_sample(x, cluster + (it + 1) * a.num_clusters, a.cols);
         if (g.local > 0) mbar_wait_bounded(smem_u32(&ctl.full[ring.stage]), ring.parity, a.status);
         load_raw<THREADS, VPT, FULL>(
             reinterpret_cast<const uint4*>(stage_tile<T, 1>(data, ring.stage, 0, a.slice_elems)), nvec, r.raw);
@@ -748,7 +757,7 @@ layernorm_bwd_reg_kernel(const T* __restrict__ x, const T* __restrict__ dy,
             dr = r.dy[REREAD ? 0 : i];
         }
     };
-    float next_shift = (!HAS_STATS && my_rows > 0) ? row_first_element(x, cluster, a.cols) : 0.0f;
+    float next_shift = (!HAS_STATS && my_rows > 0) ? row_shift_sample(x, cluster, a.cols) : 0.0f;
 
     // warp-reduced S1 = sum g and S2 = sum g * (x - mean) over this warp's columns
     auto partials_of_g = [&](const Regs& r, float (&part)[2]) {
@@ -789,7 +798,7 @@ layernorm_bwd_reg_kernel(const T* __restrict__ x, const T* __restrict__ dy,
             r.rstd = __ldg(rstd_in + row);
         } else {
             r.mean = next_shift;
-            if (it + 1 < my_rows) next_shift = row_first_element(x, row + a.num_clusters, a.cols);
+            if (it + 1 < my_rows) next_shift = row_shift_sample(x, row + a.num_clusters, a.cols);
         }
         if (g.local > 0) mbar_wait_bounded<SLEEP>(smem_u32(&ctl.full[ring.stage]), ring.parity, a.status);
         CREDIT_TRACE_POINT(2, it);

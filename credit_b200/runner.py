@@ -16,16 +16,16 @@ from __future__ import annotations
 import csv
 import json
 import math
-import statistics
 import subprocess
 import time
 from collections import defaultdict
-from dataclasses import asdict, dataclass
+from dataclasses import asdict, dataclass, fields, replace
 from pathlib import Path
 from typing import Any, Iterable
 
 from . import cost_model
 from .report import write_report
+from .timing import event_timed_batches, quantiles
 from .profile import make_b200_calibration, make_device_profile, parse_primitive_output, profile_as_dict
 from .workloads import WORKLOADS
 
@@ -43,6 +43,9 @@ _WORKLOAD_IDS = {"rmsnorm_forward": 0, "row_reduce": 1, "layernorm_forward": 2, 
 
 @dataclass(frozen=True)
 class RunConfig:
+    """What a sweep runs. The field names are the keys of the reference's configuration dict
+    (`dsmem_eval/runner.py:34-60`) so that saved configurations stay interchangeable; `rows`
+    (0 = each workload's default) is an addition."""
     workloads: tuple[str, ...] = CLI_WORKLOADS
     n_values: tuple[int, ...] = DEFAULT_N_VALUES
     cluster_sizes: tuple[int, ...] = DEFAULT_CLUSTER_SIZES
@@ -51,45 +54,51 @@ class RunConfig:
     trials: int = 5
     quick: bool = False
     profile_only: bool = False
-    rows: int = 0   # 0 = each workload's default
+    rows: int = 0
 
     @classmethod
     def from_dict(cls, raw: dict[str, Any]) -> "RunConfig":
-        config = cls(
-            workloads=tuple(raw.get("workloads", CLI_WORKLOADS)),
-            n_values=tuple(int(v) for v in raw.get("n_values", DEFAULT_N_VALUES)),
-            cluster_sizes=tuple(int(v) for v in raw.get("cluster_sizes", DEFAULT_CLUSTER_SIZES)),
-            warmup=int(raw.get("warmup", 20)),
-            iterations=int(raw.get("iterations", 100)),
-            trials=int(raw.get("trials", 5)),
-            quick=bool(raw.get("quick", False)),
-            profile_only=bool(raw.get("profile_only", False)),
-            rows=int(raw.get("rows", 0)),
-        )
+        """Builds a validated configuration from a plain dict; absent keys keep their defaults and
+        every value is coerced to its field's type (lists become tuples of int or str)."""
+        coerced: dict[str, Any] = {}
+        for field in fields(cls):
+            if field.name not in raw:
+                continue
+            value = raw[field.name]
+            if isinstance(field.default, tuple):
+                item = type(field.default[0])
+                value = tuple(item(v) for v in value)
+            else:
+                value = type(field.default)(value)
+            coerced[field.name] = value
+        config = cls(**coerced)
         config.validate()
         return config
 
     def validate(self) -> None:
-        unknown = sorted(set(self.workloads) - set(CLI_WORKLOADS))
-        if unknown:
-            raise ValueError(f"unknown workloads: {', '.join(unknown)}")
-        if not self.workloads and not self.profile_only:
-            raise ValueError("at least one workload is required")
-        if not self.n_values or any(v <= 0 for v in self.n_values):
-            raise ValueError("n_values must contain positive integers")
-        if not self.cluster_sizes or any(v not in (2, 4, 8, 16) for v in self.cluster_sizes):
-            raise ValueError("cluster_sizes must be selected from 2, 4, 8 and 16")
-        if min(self.warmup, self.iterations, self.trials) <= 0:
-            raise ValueError("warmup, iterations, and trials must be positive")
+        problems = []
+        strangers = [w for w in self.workloads if w not in CLI_WORKLOADS]
+        if strangers:
+            problems.append("unknown workloads: " + ", ".join(sorted(set(strangers))))
+        if not (self.workloads or self.profile_only):
+            problems.append("at least one workload is required")
+        if not self.n_values or min(self.n_values) <= 0:
+            problems.append("n_values must contain positive integers")
+        if not self.cluster_sizes or not set(self.cluster_sizes) <= {2, 4, 8, 16}:
+            problems.append("cluster_sizes must be selected from 2, 4, 8 and 16")
+        if self.warmup <= 0 or self.iterations <= 0 or self.trials <= 0:
+            problems.append("warmup, iterations, and trials must be positive")
         if self.rows < 0:
-            raise ValueError("rows must not be negative")
+            problems.append("rows must not be negative")
+        if problems:
+            raise ValueError("; ".join(problems))
 
     def effective(self) -> "RunConfig":
         """--quick: first two widths, the largest requested cluster, 2/5/1 warm-up/iterations/trials."""
         if not self.quick:
             return self
-        return RunConfig(self.workloads, self.n_values[:2], (max(self.cluster_sizes),), 2, 5, 1, True,
-                         self.profile_only, self.rows)
+        return replace(self, n_values=self.n_values[:2], cluster_sizes=(max(self.cluster_sizes),), warmup=2,
+                       iterations=5, trials=1)
 
 
 def run_checked(command: list[str], *, cwd: Path | None = None, timeout: int | None = None):
@@ -101,59 +110,38 @@ def run_checked(command: list[str], *, cwd: Path | None = None, timeout: int | N
 
 
 def write_csv(path: Path, rows: list[dict[str, Any]]) -> None:
-    path.parent.mkdir(parents=True, exist_ok=True)
+    """One CSV file from a list of records. The header is the union of the records' keys in order
+    of first appearance (records of one table may carry different optional columns); nothing is
+    written for an empty table."""
     if not rows:
         return
+    header: dict[str, None] = {}
+    for record in rows:
+        header.update(dict.fromkeys(record))
+    path.parent.mkdir(parents=True, exist_ok=True)
     with path.open("w", newline="", encoding="utf-8") as out:
-        writer = csv.DictWriter(out, fieldnames=list(rows[0]))
+        writer = csv.DictWriter(out, fieldnames=list(header), restval="")
         writer.writeheader()
         writer.writerows(rows)
 
 
-def percentile(samples: Iterable[float], fraction: float) -> float:
-    ordered = sorted(samples)
-    if not ordered:
-        return math.nan
-    position = fraction * (len(ordered) - 1)
-    lower, upper = int(math.floor(position)), int(math.ceil(position))
-    if lower == upper:
-        return ordered[lower]
-    weight = position - lower
-    return ordered[lower] * (1.0 - weight) + ordered[upper] * weight
-
-
 def summarize(samples: Iterable[float]) -> dict[str, float]:
-    finite = [float(v) for v in samples if math.isfinite(float(v))]
-    if not finite:
-        return {"median": math.nan, "p20": math.nan, "p80": math.nan}
-    return {"median": statistics.median(finite), "p20": percentile(finite, 0.2), "p80": percentile(finite, 0.8)}
+    """Median and the 20th / 80th percentiles of the finite samples, the three statistics the
+    reference reports for every timing (`dsmem_eval/runner.py:143-151`)."""
+    p20, median, p80 = quantiles(list(samples), (0.2, 0.5, 0.8))
+    return {"median": median, "p20": p20, "p80": p80}
 
 
 def safe_ratio(numerator: float, denominator: float) -> float:
-    if not math.isfinite(numerator) or not math.isfinite(denominator) or denominator <= 0:
-        return math.nan
-    return numerator / denominator
+    """numerator / denominator, NaN unless both are finite and the denominator is positive."""
+    ok = math.isfinite(numerator) and math.isfinite(denominator) and denominator > 0
+    return numerator / denominator if ok else math.nan
 
 
 def benchmark_callable(function, warmup: int, iterations: int, trials: int) -> list[float]:
-    """ms per call over `trials` event-timed batches of `iterations` calls (reference:
-    benchmark_callable, runner.py:166-182)."""
-    import torch
-
-    for _ in range(warmup):
-        function()
-    torch.cuda.synchronize()
-    samples: list[float] = []
-    for _ in range(trials):
-        start = torch.cuda.Event(enable_timing=True)
-        stop = torch.cuda.Event(enable_timing=True)
-        start.record()
-        for _ in range(iterations):
-            function()
-        stop.record()
-        stop.synchronize()
-        samples.append(start.elapsed_time(stop) / iterations)
-    return samples
+    """ms per call over `trials` event-timed batches of `iterations` calls (the role of the
+    reference's benchmark_callable, runner.py:166-182)."""
+    return event_timed_batches(function, warmup, iterations, trials)
 
 
 def assert_outputs_close(name: str, outputs, references, atol: float, rtol: float) -> list[dict[str, float | int]]:

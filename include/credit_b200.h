@@ -258,13 +258,19 @@ int credit_ffn_forward(const void* x, const void* w1_packed, const void* w2_pack
  * no allocator of its own). The partial column sums go into a 16 MiB array that
  * is built into the library image, so nothing is allocated or freed by this call
  * or by anything it calls; credit_layernorm_backward_stats_static_capacity()
- * returns that size. Shapes whose workspace (see
- * credit_layernorm_backward_stats_workspace_bytes) exceeds it are refused with
- * CREDIT_ERR_WORKSPACE and a message; inputs and outputs are still the caller's.
+ * returns that size. The array counts as aligned, so the scratch a call needs is
+ * that of the path its own pointers select: for 16-byte aligned x, dy, gamma and dx
+ * one [2, cols] fp32 partial per resident cluster (7.5 MiB at bf16 8192 x 65536),
+ * otherwise one per block of 128 rows. A call that needs more is refused with
+ * CREDIT_ERR_WORKSPACE and a message before any pointer is used; with dgamma and
+ * dbeta NULL no scratch is used and no size is checked. Inputs and outputs are
+ * still the caller's.
  *
  * The first call on each device looks up the array's device address
- * (cudaGetSymbolAddress) and reads the device's properties; make that first call
- * before any stream capture begins. All calls on a device share the one array and
+ * (cudaGetSymbolAddress) and reads the device's properties, and the CUDA runtime
+ * may load the library's device code, which contains the array, at that moment:
+ * make that first call before any stream capture begins, and count the 16 MiB as
+ * held by every device that has made it. All calls on a device share the one array and
  * it keeps whatever the last call left there; no part of it needs clearing,
  * because a call writes every partial sum it later reads. For the same reason two
  * calls whose kernels overlap on the GPU (different streams, or different host
@@ -277,24 +283,55 @@ int credit_layernorm_backward_stats_static(const void* x, const void* dy, const 
                                            float* dgamma, float* dbeta, int64_t rows, int64_t cols,
                                            int dtype, const credit_launch_opts* opts, void* stream);
 
-/* Host-buffer entry point ------------------------------------------------ */
+/* Host-buffer entry points ----------------------------------------------- */
 
-/* credit_row_reduce on HOST data: x_host [rows, cols] fp32 is copied to the device
- * in row blocks through `scratch` (two input buffers, so the copy of one block
- * overlaps the reduction of the previous one), reduced there, and the three
- * result vectors are copied back to out_*_host. Pinned host memory makes the
- * copies asynchronous to each other; pageable memory works but serialises.
- * `scratch` is caller-owned device memory of at least
- * credit_row_reduce_host_scratch_bytes(rows, cols) bytes (more lets the blocks
- * grow, up to the whole matrix). The call returns after the results are in host
- * memory (it synchronises `stream`). This is the shape of the reference
- * executables' run_shape (layernorm_backward.cu:767-805), which own their device
- * buffers, with the allocation moved to the caller. */
+/* The workloads above on HOST data. Every matrix and vector argument named *_host is
+ * host memory; `scratch` is caller-owned DEVICE memory (256-byte aligned) of at least
+ * the matching *_host_scratch_bytes(). A matrix is streamed through the scratch in row
+ * blocks on three streams: the upload of block k+1, the kernels of block k and the
+ * download of block k-1 overlap. More scratch than the minimum lets the blocks grow,
+ * up to the whole matrix. Pinned host memory makes the copies asynchronous to each
+ * other; pageable memory works but serialises them. A call returns after its results
+ * are in host memory (it synchronises `stream`). Calls on one device run one after
+ * the other (the library holds one set of copy streams per device). This is the shape
+ * of run_shape in the reference executables (layernorm_backward.cu:767-805), which own
+ * their device buffers, with the allocation moved to the caller and the copies
+ * pipelined; the kernels are the ones of the device-pointer entry points. */
 size_t credit_row_reduce_host_scratch_bytes(int64_t rows, int64_t cols);
 int credit_row_reduce_host(const float* x_host, float* out_sum_host, float* out_max_host,
                            int64_t* out_argmax_host, int64_t rows, int64_t cols,
                            const credit_launch_opts* opts, void* scratch, size_t scratch_bytes,
                            void* stream);
+
+size_t credit_rmsnorm_forward_host_scratch_bytes(int64_t rows, int64_t cols, int dtype);
+int credit_rmsnorm_forward_host(const void* x_host, const float* gamma_host, void* y_host, int64_t rows,
+                                int64_t cols, float eps, int dtype, const credit_launch_opts* opts,
+                                void* scratch, size_t scratch_bytes, void* stream);
+
+size_t credit_layernorm_forward_host_scratch_bytes(int64_t rows, int64_t cols, int dtype);
+int credit_layernorm_forward_host(const void* x_host, const float* gamma_host, const float* beta_host,
+                                  void* y_host, float* mean_host, float* rstd_host, int64_t rows,
+                                  int64_t cols, float eps, int dtype, const credit_launch_opts* opts,
+                                  void* scratch, size_t scratch_bytes, void* stream);
+
+/* dgamma_host / dbeta_host are required here. Column sums are kept per row block on the
+ * device and added in block order at the end (deterministic). */
+size_t credit_layernorm_backward_stats_host_scratch_bytes(int64_t rows, int64_t cols, int dtype,
+                                                          const credit_launch_opts* opts);
+int credit_layernorm_backward_stats_host(const void* x_host, const void* dy_host, const float* gamma_host,
+                                         const float* mean_host, const float* rstd_host, void* dx_host,
+                                         float* dgamma_host, float* dbeta_host, int64_t rows, int64_t cols,
+                                         int dtype, const credit_launch_opts* opts, void* scratch,
+                                         size_t scratch_bytes, void* stream);
+
+/* Fused FFN with the activations in host memory: x_host and y_host are bf16 [m, d] on
+ * the host; the packed weights and gamma are the DEVICE pointers credit_ffn_forward
+ * takes (parameters stay resident between calls). Every row needs both weight matrices
+ * in full, so the rows are not cut into blocks. */
+size_t credit_ffn_forward_host_scratch_bytes(int64_t m, int64_t d, int64_t h);
+int credit_ffn_forward_host(const void* x_host, const void* w1_packed, const void* w2_packed,
+                            const float* gamma, void* y_host, int64_t m, int64_t d, int64_t h, float eps,
+                            void* scratch, size_t scratch_bytes, void* stream);
 
 #ifdef __cplusplus
 }

@@ -191,6 +191,36 @@ def test_row_reduce_ties_take_the_lowest_column(load_path):
         assert m[3].item() == float("-inf")
 
 
+@pytest.mark.parametrize("load_path", [N.LOAD_TMA, N.LOAD_LDG])
+@pytest.mark.parametrize("cols", [65536, 33333])
+def test_row_reduce_nan_propagates_like_torch(load_path, cols):
+    """torch.amax / torch.argmax (the oracle) let a NaN win over every number and report the FIRST
+    NaN's column; the row sum is NaN. +inf and -inf in one row make the sum NaN without any NaN
+    element: maximum and argmax then stay ordinary."""
+    if load_path == N.LOAD_TMA and cols % 4:
+        pytest.skip("bulk copies need 16-byte rows")
+    rows = 6
+    torch.manual_seed(3)
+    x = torch.randn(rows, cols)
+    nan, inf = float("nan"), float("inf")
+    x[0, cols - 1] = nan                                   # last column, last CTA
+    x[1, [40000 % cols, 123, 30000]] = nan                 # several: the lowest column counts
+    x[1, 7] = inf                                          # an infinity before the first NaN loses to it
+    x[2, 0] = nan                                          # first column
+    x[3, 100] = inf
+    x[3, 20000] = -inf                                     # sum is NaN, no NaN element
+    x[4, :] = nan                                          # every element
+    want_sum, want_max, want_arg = O.row_reduce(x)
+    assert want_arg.tolist()[:5] == [cols - 1, 123, 0, 100, 0]
+    for p in (1, 4, 16):
+        s, m, a = run("row_reduce", (x,), p, {"load_path": load_path})
+        assert torch.equal(a, want_arg), (p, a.tolist())
+        assert torch.equal(torch.isnan(m), torch.isnan(want_max))
+        assert torch.equal(m[~torch.isnan(m)], want_max[~torch.isnan(want_max)])
+        assert torch.equal(torch.isnan(s), torch.isnan(want_sum))
+        assert bool(torch.isnan(s[:5]).all()) and not bool(torch.isnan(s[5]))
+
+
 def test_row_reduce_headline_width_few_rows():
     rows, cols = 6, 1048576
     (x,) = W.make_row_reduce_inputs(rows, cols, "cpu", seed=0)
@@ -241,6 +271,31 @@ def test_layernorm_forward_large_offset_has_no_cancellation():
         _, want_mean, want_rstd = O.layernorm_forward(x, gamma, beta, dtype=torch.float64)
         close(mean, want_mean, FP32_RTOL, scale=0.0, what="mean")
         close(rstd, want_rstd, 1.0e-3, what="rstd")   # limited by fp32 storage of x itself
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("sigmas", [100.0, 1000.0])
+def test_layernorm_statistics_survive_an_outlier_in_the_first_column(dtype, sigmas):
+    """x[:, 0] far from the row mean: a one-pass variance shifted by the row's first element
+    would lose 1e-3 and more of the variance to cancellation. Covers the forward and the
+    statistics-recomputing backward on the register path (aligned rows) at several cluster sizes."""
+    rows, cols = 6, 65536
+    torch.manual_seed(11)
+    x = torch.randn(rows, cols)
+    x[:, 0] = sigmas
+    x[1, cols - 1] = -sigmas          # one row with two outliers, one of them a sampled position
+    x = x.to(dtype)
+    gamma = torch.rand(cols) + 0.5
+    beta = torch.zeros(cols)
+    dy = torch.randn(rows, cols).to(dtype)
+    _, want_mean, want_rstd = O.layernorm_forward(x, gamma, beta, dtype=torch.float64)
+    want_dx = O.layernorm_backward(x.double(), dy.double(), gamma.double())
+    for p in (2, 8, 16):
+        y, mean, rstd = run("layernorm_forward", (x, gamma, beta), p)
+        close(rstd, want_rstd, FP32_RTOL, what=f"rstd P={p}")
+        close(mean, want_mean, FP32_RTOL, scale=1.0, what=f"mean P={p}")
+        (dx,) = run("layernorm_backward", (x, dy, gamma), p)
+        close(dx, want_dx, FP32_RTOL if dtype == torch.float32 else BF16_RTOL, scale=2.0, what=f"dx P={p}")
 
 
 def test_layernorm_forward_headline_width():
