@@ -5,6 +5,7 @@
 #include "kernel_tables.h"
 #include "norm_kernels.cuh"
 #include "register_row_kernels.cuh"
+#include "ws_row_kernels.cuh"
 
 namespace credit {
 namespace {
@@ -39,6 +40,20 @@ const void* layernorm_bwd_reg_kernel_f32(int threads, int vpt, bool full, bool h
                                              bool grads) {
     return full ? reg_func<float, true>(threads, vpt, has_stats, grads)
                 : reg_func<float, false>(threads, vpt, has_stats, grads);
+}
+
+// The warp-specialised kernel (given statistics + parameter gradients): 16 output warps, each thread
+// owning `vpt` 16-byte vectors of its CTA's slice, plus a producer and a collector warp.
+const void* layernorm_bwd_ws_kernel_f32(int vpt, bool full) {
+    switch (vpt) {
+        case 1: return full ? (const void*)layernorm_bwd_ws_kernel<float, 1, true>
+                            : (const void*)layernorm_bwd_ws_kernel<float, 1, false>;
+        case 2: return full ? (const void*)layernorm_bwd_ws_kernel<float, 2, true>
+                            : (const void*)layernorm_bwd_ws_kernel<float, 2, false>;
+        case 4: return full ? (const void*)layernorm_bwd_ws_kernel<float, 4, true>
+                            : (const void*)layernorm_bwd_ws_kernel<float, 4, false>;
+        default: return nullptr;
+    }
 }
 
 }  // namespace credit

@@ -294,6 +294,7 @@ def test_layernorm_statistics_survive_an_outlier_in_the_first_column(dtype, sigm
         y, mean, rstd = run("layernorm_forward", (x, gamma, beta), p)
         close(rstd, want_rstd, FP32_RTOL, what=f"rstd P={p}")
         close(mean, want_mean, FP32_RTOL, scale=1.0, what=f"mean P={p}")
+    for p in (4, 8, 16):   # x and dy staged: two fp32 half rows do not fit one CTA
         (dx,) = run("layernorm_backward", (x, dy, gamma), p)
         close(dx, want_dx, FP32_RTOL if dtype == torch.float32 else BF16_RTOL, scale=2.0, what=f"dx P={p}")
 
@@ -396,6 +397,32 @@ def test_layernorm_backward_stats_register_paths(opts, cluster_size):
     inputs = W.make_layernorm_backward_stats_inputs(rows, cols, "cpu", seed=13)
     check_backward_stats(inputs, try_run("layernorm_backward_stats", inputs, cluster_size, opts),
                          BF16_RTOL)
+
+
+@pytest.mark.parametrize("stages", [0, 3, 4, 5, 8])
+@pytest.mark.parametrize("cluster_size", [1, 2, 4, 8, 16])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_layernorm_backward_stats_warp_specialised_kernel(dtype, cluster_size, stages):
+    """threads = 576: producer warp, collector warp and 16 output warps whose two passes run one or
+    two rows apart (by ring depth). 20+ rows per cluster, so the ring, the four CTA-local partial
+    buffers and the eight cluster slot buffers all wrap several times; the second shape leaves
+    ragged tiles and CTAs with empty slices."""
+    opts = {"threads": 576, "stages": stages}
+    for rows, cols in ((3100, 4096), (2999, 1096)):
+        inputs = W.make_layernorm_backward_stats_inputs(rows, cols, "cpu", seed=rows, dtype=dtype)
+        got = try_run("layernorm_backward_stats", inputs, cluster_size, opts)
+        check_backward_stats(inputs, got, BF16_RTOL if dtype == torch.bfloat16 else FP32_RTOL)
+        plan = N.plan(N.WL_LAYERNORM_BACKWARD_STATS, rows, cols, N.BF16 if dtype == torch.bfloat16 else N.F32,
+                      dict(opts, cluster_size=cluster_size))
+        assert plan.threads == 576 and plan.stages >= 3
+
+
+def test_layernorm_backward_stats_automatic_plan_is_warp_specialised():
+    plan = N.plan(N.WL_LAYERNORM_BACKWARD_STATS, 8192, 65536, N.BF16)
+    assert (plan.threads, plan.cluster_size, plan.vectors_per_thread, plan.full_tiles) == (576, 8, 2, 1)
+    assert plan.stages == 6 and plan.smem_bytes == 4096 + 6 * 32768
+    # explicit thread counts keep the lock-step register kernels
+    assert N.plan(N.WL_LAYERNORM_BACKWARD_STATS, 8192, 65536, N.BF16, {"threads": 512}).threads == 512
 
 
 def test_layernorm_backward_stats_headline_width():
