@@ -115,7 +115,7 @@ def estimate(spec: WorkloadModelSpec, cols: int, cluster_size: int, control_over
 # ---------------------------------------------------------------------------
 @dataclass(frozen=True)
 class B200Calibration:
-    """Constants measured on B200 (profiles/primitive_benchmark_b200.txt and the cluster-size
+    """Constants measured on B200 (the output of primitive_benchmark and the cluster-size
     sweeps); cycles are SM cycles at `clock_ghz`."""
     clock_ghz: float = 1.93                    # SM clock under these memory-bound kernels
     hbm_gbps: float = 6538.6                   # copy ceiling

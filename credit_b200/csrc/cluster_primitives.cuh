@@ -16,31 +16,6 @@
 namespace credit {
 
 // ---------------------------------------------------------------------------
-// optional timeline probe (development builds only, -DCREDIT_TRACE): two threads
-// of one CTA record (point, iteration, clock) triples
-// ---------------------------------------------------------------------------
-#ifdef CREDIT_TRACE
-constexpr int kTraceCapacity = 8192;
-static __device__ long long g_trace[2][kTraceCapacity][3];
-static __device__ int g_trace_count[2];
-__device__ __forceinline__ void trace_point(int id, int it) {
-    if (blockIdx.x != 0) return;
-    const int who = threadIdx.x == 0 ? 0 : (threadIdx.x == 96 ? 1 : -1);
-    if (who < 0) return;
-    const int n = g_trace_count[who];
-    if (n < kTraceCapacity) {
-        g_trace[who][n][0] = id;
-        g_trace[who][n][1] = it;
-        g_trace[who][n][2] = clock64();
-        g_trace_count[who] = n + 1;
-    }
-}
-#define CREDIT_TRACE_POINT(id, it) ::credit::trace_point((id), (it))
-#else
-#define CREDIT_TRACE_POINT(id, it) ((void)0)
-#endif
-
-// ---------------------------------------------------------------------------
 // addressing
 // ---------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -181,6 +156,30 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
     for (uint32_t i = 0; i < (1u << 24); ++i) {
         if (SLEEP_NS > 0) __nanosleep(SLEEP_NS);
         if (mbar_poll(bar, parity)) return true;
+        if (clock64() - t0 > (1ll << 31)) break;
+    }
+    if (status != nullptr) atomicOr(status, kStatusWaitTimeout);
+    return false;
+}
+
+// Suspending wait for warps that have nothing else to do (the producer and collector warps of the
+// warp-specialised kernels): mbarrier.try_wait parks the warp in hardware until the phase completes
+// or a time limit passes, so the waiting warp issues a handful of instructions per wake-up instead
+// of competing for issue slots with the warps that have work. Bounded like mbar_wait_bounded.
+__device__ __forceinline__ bool mbar_wait_parked_bounded(uint32_t bar, uint32_t parity, int* status) {
+    const long long t0 = clock64();
+    for (uint32_t i = 0; i < (1u << 22); ++i) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t"
+            ".reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t"
+            "}"
+            : "=r"(done)
+            : "r"(bar), "r"(parity), "r"(100000u)   // suspend-time hint in ns
+            : "memory");
+        if (done != 0) return true;
         if (clock64() - t0 > (1ll << 31)) break;
     }
     if (status != nullptr) atomicOr(status, kStatusWaitTimeout);

@@ -247,9 +247,10 @@ int check_opts(const credit_launch_opts* o, credit_launch_opts* out) {
     if (z.stages < 0 || z.stages > kMaxStages)
         return fail(CREDIT_ERR_INVALID_ARGUMENT, "stages must be in [0, %d] (got %d)", kMaxStages,
                     z.stages);
-    if (z.threads != 0 && z.threads != 256 && z.threads != 512 && z.threads != kWsThreadsPerCta)
-        return fail(CREDIT_ERR_INVALID_ARGUMENT, "threads must be 0, 256, 512 or %d (got %d)", kWsThreadsPerCta,
-                    z.threads);
+    if (z.threads != 0 && z.threads != 256 && z.threads != 512 && z.threads != kWsThreadsPerCta &&
+        z.threads != kWsThreadsPerCtaWide)
+        return fail(CREDIT_ERR_INVALID_ARGUMENT, "threads must be 0, 256, 512, %d or %d (got %d)",
+                    kWsThreadsPerCtaWide, kWsThreadsPerCta, z.threads);
     if (z.schedule < CREDIT_SCHEDULE_AUTO || z.schedule > CREDIT_SCHEDULE_PERSISTENT)
         return fail(CREDIT_ERR_INVALID_ARGUMENT, "unknown schedule %d", z.schedule);
     if (z.load_path < CREDIT_LOAD_AUTO || z.load_path > CREDIT_LOAD_LDG)
@@ -423,18 +424,19 @@ int plan_static(int workload, const Shape& s, int dtype, const credit_launch_opt
         return nin * round_up((s.cols + cluster - 1) / cluster, 64) * s.elem_bytes;
     };
 
-    // LayerNorm backward with column sums: the warp-specialised kernel (16 output warps of 16 row
-    // elements per thread, a producer and a collector warp) whenever the slice fits it and a ring
-    // of at least three stages fits shared memory. threads = 256 / 512 keep the lock-step
-    // register kernels.
-    if (grads && p->aligned && !(o.flags & CREDIT_FLAG_NO_REGISTER_PATH) &&
-        (o.threads == 0 || o.threads == kWsThreadsPerCta) && o.schedule != CREDIT_SCHEDULE_ROW_PER_CLUSTER &&
-        (o.stages == 0 || o.stages >= 3) && o.variant != CREDIT_VARIANT_BLOCK_SMEM) {
-        const int out_threads = kWsThreadsPerCta - 64;
-        const int max_vpt = 16 / s.vec_elems;
+    // LayerNorm backward with column sums: the warp-specialised kernel (16 output warps of up to 16
+    // row elements per thread, or 8 of up to 32, plus a producer and a collector warp) whenever the
+    // slice fits it and a ring of at least three stages fits shared memory. threads = 256 / 512
+    // keep the lock-step register kernels.
+    const bool ws_threads = o.threads == kWsThreadsPerCta || o.threads == kWsThreadsPerCtaWide;
+    if (grads && p->aligned && !(o.flags & CREDIT_FLAG_NO_REGISTER_PATH) && (o.threads == 0 || ws_threads) &&
+        o.schedule != CREDIT_SCHEDULE_ROW_PER_CLUSTER && (o.stages == 0 || o.stages >= 3) &&
+        o.variant != CREDIT_VARIANT_BLOCK_SMEM) {
+        const int threads = o.threads ? o.threads : kWsThreadsPerCtaWide;   // measured faster at the target shape
+        const int out_threads = threads - 96;   // three service warps
+        const int max_slice = 512 * 16;   // row elements per CTA in either form
         auto ws_fits = [&](int c) {
-            const int slice = round_up((s.cols + c - 1) / c, 64);
-            return slice / s.vec_elems <= out_threads * max_vpt && kControlBytes + 3 * stage_bytes_for(c) <= max_smem;
+            return round_up((s.cols + c - 1) / c, 64) <= max_slice && kWsControlBytes + 3 * stage_bytes_for(c) <= max_smem;
         };
         int c = o.cluster_size;
         if (c == 0) {
@@ -449,23 +451,23 @@ int plan_static(int workload, const Shape& s, int dtype, const credit_launch_opt
             while (vpt * out_threads < nvec) vpt *= 2;
             const int stage_bytes = stage_bytes_for(c);
             int stages = o.stages ? o.stages : 6;
-            while (stages > 3 && kControlBytes + stages * stage_bytes > max_smem) --stages;
-            p->threads = kWsThreadsPerCta;
+            while (stages > 3 && kWsControlBytes + stages * stage_bytes > max_smem) --stages;
+            p->threads = threads;
             p->vectors_per_thread = vpt;
             p->full_tiles = (vpt * out_threads == nvec && 1ll * p->slice_elems * c == s.cols) ? 1 : 0;
             p->schedule = CREDIT_SCHEDULE_PERSISTENT;
             p->stages = stages;
-            p->smem_bytes = kControlBytes + stages * stage_bytes;
+            p->smem_bytes = kWsControlBytes + stages * stage_bytes;
             return CREDIT_OK;
         }
-        if (o.threads == kWsThreadsPerCta)
+        if (ws_threads)
             return fail(CREDIT_ERR_UNSUPPORTED,
                         "the warp-specialised kernel needs slices of at most %d elements and three stages of %d B",
-                        out_threads * 16, stage_bytes_for(std::max(o.cluster_size, 1)));
-    } else if (o.threads == kWsThreadsPerCta) {
+                        max_slice, stage_bytes_for(std::max(o.cluster_size, 1)));
+    } else if (ws_threads) {
         return fail(CREDIT_ERR_UNSUPPORTED,
                     "threads = %d selects the warp-specialised kernel: LayerNorm backward with column sums on "
-                    "16-byte aligned rows, persistent schedule, at least three stages", kWsThreadsPerCta);
+                    "16-byte aligned rows, persistent schedule, at least three stages", o.threads);
     }
     int cluster = o.cluster_size;
     if (cluster == 0) {
@@ -624,7 +626,9 @@ void choose_cluster_by_model(int device, const DeviceState& dev, int workload, c
     if (o->variant == CREDIT_VARIANT_BLOCK_READ || o->variant == CREDIT_VARIANT_BLOCK_SMEM) return;
     if (o->schedule == CREDIT_SCHEDULE_ROW_PER_CLUSTER) return;
     // the warp-specialised kernel takes the smallest cluster whose slice fits it (plan_static)
-    if (workload == CREDIT_WL_LAYERNORM_BACKWARD_STATS && grads && (o->threads == 0 || o->threads == kWsThreadsPerCta)) return;
+    if (workload == CREDIT_WL_LAYERNORM_BACKWARD_STATS && grads &&
+        (o->threads == 0 || o->threads == kWsThreadsPerCta || o->threads == kWsThreadsPerCtaWide))
+        return;
     const auto key = std::make_tuple(device, workload, s.rows, s.cols, dtype, pointers_aligned, grads, o->variant,
                                      o->threads, o->stages, o->flags);
     {

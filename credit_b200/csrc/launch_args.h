@@ -7,8 +7,12 @@ namespace credit {
 constexpr int kMaxClusterSize = 16;   // 8 portable, 16 with the non-portable opt-in
 constexpr int kMaxWarpsPerCta = 32;
 constexpr int kMaxStages = 8;
-// Threads per CTA of the warp-specialised kernels: 16 output warps, a producer warp and a collector warp.
-constexpr int kWsThreadsPerCta = 576;
+// Threads per CTA of the warp-specialised kernels: 16 (or, "wide", 8) output warps plus three
+// service warps (producer, collector, receiver); their control block at the start of dynamic
+// shared memory holds one pair of partial sums per output thread for four rows.
+constexpr int kWsThreadsPerCta = 608;
+constexpr int kWsThreadsPerCtaWide = 352;
+constexpr int kWsControlBytes = 20480;
 // Bytes reserved at the start of dynamic shared memory for barriers and
 // reduction scratch; row data starts after it (keeps 1024-byte alignment).
 constexpr int kControlBytes = 4096;

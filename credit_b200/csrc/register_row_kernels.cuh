@@ -113,7 +113,6 @@ __device__ __forceinline__ void exchange_receive(ExchangeStream<K>& s, int it, u
     const int buf = it & (kExchangeBuffers - 1);
     const uint32_t phase = (static_cast<uint32_t>(it) / kExchangeBuffers) & 1u;
     mbar_wait_bounded(smem_u32(&s.bar[buf]), phase, status);
-    CREDIT_TRACE_POINT(10, it);
     const uint32_t lane = threadIdx.x & 31;
 #pragma unroll
     for (int k = 0; k < K; ++k) {
@@ -175,7 +174,6 @@ __device__ __forceinline__ void exchange_receive_split(ExchangeStream<2>& s, int
     const int buf = it & (kExchangeBuffers - 1);
     const uint32_t phase = (static_cast<uint32_t>(it) / kExchangeBuffers) & 1u;
     mbar_wait_bounded<SLEEP_NS>(smem_u32(&s.bar[buf]), phase, status);
-    CREDIT_TRACE_POINT(10, it);
     const uint32_t lane = threadIdx.x & 31;
     const uint32_t half = lane >> 4, idx = lane & 15;
     float t = idx < nranks ? (&s.slot[buf][0][0])[2 * idx + half] : 0.0f;
@@ -214,7 +212,6 @@ __device__ __forceinline__ float reduce_and_receive_split(float a, float b, Exch
     const int buf = it_recv & (kExchangeBuffers - 1);
     const uint32_t phase = (static_cast<uint32_t>(it_recv) / kExchangeBuffers) & 1u;
     mbar_wait_bounded<SLEEP_NS>(smem_u32(&s.bar[buf]), phase, status);
-    CREDIT_TRACE_POINT(10, it_recv);
     const uint32_t lane = threadIdx.x & 31;
     const uint32_t half = lane >> 4, idx = lane & 15;
     float t = idx < nranks ? (&s.slot[buf][0][0])[2 * idx + half] : 0.0f;
@@ -791,7 +788,6 @@ layernorm_bwd_reg_kernel(const T* __restrict__ x, const T* __restrict__ dy,
     // the row into registers (or located in its stage) and this thread's two partial sums of it
     auto front_load = [&](Regs& r, int it, float (&part)[2]) {
         const int row = cluster + it * a.num_clusters;
-        CREDIT_TRACE_POINT(1, it);
         if (fills_ring && it > 0) filler.recycle(it, REREAD ? 2 : 1);
         if (HAS_STATS) {
             r.mean = __ldg(mean_in + row);
@@ -801,7 +797,6 @@ layernorm_bwd_reg_kernel(const T* __restrict__ x, const T* __restrict__ dy,
             if (it + 1 < my_rows) next_shift = row_shift_sample(x, row + a.num_clusters, a.cols);
         }
         if (g.local > 0) mbar_wait_bounded<SLEEP>(smem_u32(&ctl.full[ring.stage]), ring.parity, a.status);
-        CREDIT_TRACE_POINT(2, it);
         r.stage = ring.stage;
         if (!REREAD) {
             load_raw<THREADS, HELD, FULL>(
@@ -819,14 +814,12 @@ layernorm_bwd_reg_kernel(const T* __restrict__ x, const T* __restrict__ dy,
         } else {
             shifted_partials<T, THREADS, HELD, FULL>(r.x, nvec, r.mean, part[0], part[1]);
         }
-        CREDIT_TRACE_POINT(4, it);
         // the stage is free once the row is in registers, or (REREAD) once its outputs are written
         if (!REREAD && g.local > 0 && (threadIdx.x & 31) == 0) mbar_arrive(smem_u32(&ctl.empty[ring.stage]));
     };
     auto front_send = [&](float keep, int it) {   // keep: the two partials split over the halves of the warp
         exchange_send_split<W, SLEEP>(keep, ctl.ex, it, rank, nranks, a.status);
         ring.advance(a.stages);
-        CREDIT_TRACE_POINT(6, it);
     };
     auto front = [&](Regs& r, int it) {
         float part[2];
@@ -845,7 +838,6 @@ layernorm_bwd_reg_kernel(const T* __restrict__ x, const T* __restrict__ dy,
     };
     auto back_store = [&](const Regs& r, int it, const float (&sums)[2]) {
         const int row = cluster + it * a.num_clusters;
-        CREDIT_TRACE_POINT(8, it);
         const float2 neg_mean = splat(-r.mean), rstd2 = splat(r.rstd);
         const float2 ca = splat(-r.rstd * r.rstd * r.rstd * (sums[1] * inv_cols));
         const float2 cb = splat(-r.rstd * (sums[0] * inv_cols));
@@ -883,11 +875,9 @@ layernorm_bwd_reg_kernel(const T* __restrict__ x, const T* __restrict__ dy,
             __syncwarp();   // every lane has read its vectors of the stage
             if ((threadIdx.x & 31) == 0) mbar_arrive(smem_u32(&ctl.empty[r.stage]));
         }
-        CREDIT_TRACE_POINT(9, it);
     };
     auto back = [&](const Regs& r, int it) {
         float sums[2];
-        CREDIT_TRACE_POINT(7, it);
         exchange_receive_split<SLEEP>(HAS_STATS ? ctl.ex : ctl.ex2, it, nranks, a.status, sums);
         back_store(r, it, sums);
     };
@@ -895,7 +885,6 @@ layernorm_bwd_reg_kernel(const T* __restrict__ x, const T* __restrict__ dy,
     auto fused = [&](Regs& rn, int itn, const Regs& ro, int ito) {
         float part[2], sums[2];
         front_load(rn, itn, part);
-        CREDIT_TRACE_POINT(7, ito);
         const float keep = reduce_and_receive_split<SLEEP>(part[0], part[1], HAS_STATS ? ctl.ex : ctl.ex2, ito, nranks,
                                                            a.status, sums);
         front_send(keep, itn);

@@ -22,7 +22,9 @@ SHAPES = [(3, 96), (2, 1000)]
 
 
 def main() -> None:
-    ref_root = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: python tests/golden/make_golden.py /path/to/reference")
+    ref_root = Path(sys.argv[1])
     sys.path.insert(0, str(ref_root))
     from dsmem_eval.workloads import WORKLOADS  # type: ignore
 

@@ -402,25 +402,27 @@ def test_layernorm_backward_stats_register_paths(opts, cluster_size):
 @pytest.mark.parametrize("stages", [0, 3, 4, 5, 8])
 @pytest.mark.parametrize("cluster_size", [1, 2, 4, 8, 16])
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
-def test_layernorm_backward_stats_warp_specialised_kernel(dtype, cluster_size, stages):
-    """threads = 576: producer warp, collector warp and 16 output warps whose two passes run one or
-    two rows apart (by ring depth). 20+ rows per cluster, so the ring, the four CTA-local partial
-    buffers and the eight cluster slot buffers all wrap several times; the second shape leaves
-    ragged tiles and CTAs with empty slices."""
-    opts = {"threads": 576, "stages": stages}
+@pytest.mark.parametrize("threads", [608, 352])
+def test_layernorm_backward_stats_warp_specialised_kernel(threads, dtype, cluster_size, stages):
+    """threads = 608 / 352: producer, collector and receiver warps and 16 / 8 output warps whose two passes
+    run one or two rows apart (by ring depth). 20+ rows per cluster, so the ring, the four CTA-local
+    partial buffers and the eight cluster slot buffers all wrap several times; the second shape
+    leaves ragged tiles and CTAs with empty slices."""
+    opts = {"threads": threads, "stages": stages}
     for rows, cols in ((3100, 4096), (2999, 1096)):
         inputs = W.make_layernorm_backward_stats_inputs(rows, cols, "cpu", seed=rows, dtype=dtype)
         got = try_run("layernorm_backward_stats", inputs, cluster_size, opts)
         check_backward_stats(inputs, got, BF16_RTOL if dtype == torch.bfloat16 else FP32_RTOL)
         plan = N.plan(N.WL_LAYERNORM_BACKWARD_STATS, rows, cols, N.BF16 if dtype == torch.bfloat16 else N.F32,
                       dict(opts, cluster_size=cluster_size))
-        assert plan.threads == 576 and plan.stages >= 3
+        assert plan.threads == threads and plan.stages >= 3
 
 
 def test_layernorm_backward_stats_automatic_plan_is_warp_specialised():
     plan = N.plan(N.WL_LAYERNORM_BACKWARD_STATS, 8192, 65536, N.BF16)
-    assert (plan.threads, plan.cluster_size, plan.vectors_per_thread, plan.full_tiles) == (576, 8, 2, 1)
-    assert plan.stages == 6 and plan.smem_bytes == 4096 + 6 * 32768
+    assert plan.threads in (608, 352) and plan.cluster_size == 8 and plan.full_tiles == 1
+    assert plan.vectors_per_thread == (2 if plan.threads == 608 else 4)
+    assert plan.stages == 6 and plan.smem_bytes == 20480 + 6 * 32768
     # explicit thread counts keep the lock-step register kernels
     assert N.plan(N.WL_LAYERNORM_BACKWARD_STATS, 8192, 65536, N.BF16, {"threads": 512}).threads == 512
 
