@@ -37,6 +37,9 @@ LIB_SOURCES = [
     "tables_row_ops.cu",
     "bench_entry.cu",
     "host_entry.cu",
+    "tables_ws_rmsnorm.cu",
+    "tables_ws_layernorm_fwd.cu",
+    "tables_ws_layernorm_bwd.cu",
 ]
 OBJ_DIR = LIB_DIR / "obj"
 # name of the executable -> (source, links against the shared library)

@@ -17,6 +17,11 @@ const void* layernorm_fwd_kernel_for(int dtype, int threads, int vpt, bool full,
 const void* layernorm_bwd_kernel_for(int dtype, int threads, int vpt, bool full, bool aligned,
                                      bool has_stats, bool grads);
 const void* row_reduce_kernel_for(int load_path, int threads, bool aligned);
+// Warp-specialised kernels (ws_row_kernels.cuh): `out_warps` output warps (16 or 8) of `vpt` 16-byte
+// vectors per thread plus three service warps; arguments (NormParams, StagedArgs).
+const void* ws_rmsnorm_kernel_for(int dtype, int out_warps, int vpt, bool full);
+const void* ws_layernorm_fwd_kernel_for(int dtype, int out_warps, int vpt, bool full);
+const void* ws_layernorm_bwd_kernel_for(int dtype, int out_warps, int vpt, bool full);
 // One CTA of 512 threads per row, nothing staged (CREDIT_VARIANT_BLOCK_READ).
 const void* block_read_kernel_for(int workload, int dtype, bool aligned);
 // Reference-sweep workloads (CREDIT_WL_WEIGHTED_VAR_BACKWARD ... CREDIT_WL_ROWWISE_QUANT), fp32;

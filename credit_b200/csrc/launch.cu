@@ -285,6 +285,16 @@ const void* workload_func(int workload, int dtype, const credit_plan_info& p, bo
     if (p.variant == CREDIT_VARIANT_BLOCK_READ) return block_read_kernel_for(workload, dtype, al);
     const int vpt = p.vectors_per_thread;
     const bool full = p.full_tiles != 0;
+    if (p.threads == kWsThreadsPerCta || p.threads == kWsThreadsPerCtaWide) {
+        const int out_warps = p.threads / 32 - 3;   // three service warps
+        switch (workload) {
+            case CREDIT_WL_RMSNORM_FORWARD: return ws_rmsnorm_kernel_for(dtype, out_warps, vpt, full);
+            case CREDIT_WL_LAYERNORM_FORWARD: return ws_layernorm_fwd_kernel_for(dtype, out_warps, vpt, full);
+            case CREDIT_WL_LAYERNORM_BACKWARD_STATS:
+                return want_grads ? ws_layernorm_bwd_kernel_for(dtype, out_warps, vpt, full) : nullptr;
+            default: return nullptr;
+        }
+    }
     switch (workload) {
         case CREDIT_WL_RMSNORM_FORWARD:
             return rmsnorm_kernel_for(dtype, p.threads, vpt, full, al);
@@ -424,17 +434,22 @@ int plan_static(int workload, const Shape& s, int dtype, const credit_launch_opt
         return nin * round_up((s.cols + cluster - 1) / cluster, 64) * s.elem_bytes;
     };
 
-    // LayerNorm backward with column sums: the warp-specialised kernel (16 output warps of up to 16
-    // row elements per thread, or 8 of up to 32, plus a producer and a collector warp) whenever the
-    // slice fits it and a ring of at least three stages fits shared memory. threads = 256 / 512
-    // keep the lock-step register kernels.
+    // The warp-specialised kernels (ws_row_kernels.cuh: 16 or 8 output warps plus producer, collector
+    // and receiver warps) serve RMSNorm forward, LayerNorm forward and LayerNorm backward with column
+    // sums whenever the rows are 16-byte aligned, the slice fits the output threads' registers and a
+    // ring of at least three stages fits shared memory. threads = 256 / 512 keep the lock-step
+    // register kernels.
     const bool ws_threads = o.threads == kWsThreadsPerCta || o.threads == kWsThreadsPerCtaWide;
-    if (grads && p->aligned && !(o.flags & CREDIT_FLAG_NO_REGISTER_PATH) && (o.threads == 0 || ws_threads) &&
+    const bool ws_workload = workload == CREDIT_WL_RMSNORM_FORWARD || workload == CREDIT_WL_LAYERNORM_FORWARD || grads;
+    if (ws_workload && p->aligned && !(o.flags & CREDIT_FLAG_NO_REGISTER_PATH) && (o.threads == 0 || ws_threads) &&
         o.schedule != CREDIT_SCHEDULE_ROW_PER_CLUSTER && (o.stages == 0 || o.stages >= 3) &&
         o.variant != CREDIT_VARIANT_BLOCK_SMEM) {
-        const int threads = o.threads ? o.threads : kWsThreadsPerCtaWide;   // measured faster at the target shape
+        // measured at the target shapes: 8 output warps with twice the elements per thread win for the
+        // backward kernel (per-row work of a warp is paid by half as many warps)
+        const int threads = o.threads ? o.threads : (grads ? kWsThreadsPerCtaWide : kWsThreadsPerCta);
+        const bool wide = threads == kWsThreadsPerCtaWide;
         const int out_threads = threads - 96;   // three service warps
-        const int max_slice = 512 * 16;   // row elements per CTA in either form
+        const int max_slice = out_threads * ws_max_elems_per_thread(grads, wide);
         auto ws_fits = [&](int c) {
             return round_up((s.cols + c - 1) / c, 64) <= max_slice && kWsControlBytes + 3 * stage_bytes_for(c) <= max_smem;
         };
@@ -466,8 +481,9 @@ int plan_static(int workload, const Shape& s, int dtype, const credit_launch_opt
                         max_slice, stage_bytes_for(std::max(o.cluster_size, 1)));
     } else if (ws_threads) {
         return fail(CREDIT_ERR_UNSUPPORTED,
-                    "threads = %d selects the warp-specialised kernel: LayerNorm backward with column sums on "
-                    "16-byte aligned rows, persistent schedule, at least three stages", o.threads);
+                    "threads = %d selects a warp-specialised kernel: RMSNorm / LayerNorm forward or LayerNorm "
+                    "backward with column sums, 16-byte aligned rows, persistent schedule, at least three stages",
+                    o.threads);
     }
     int cluster = o.cluster_size;
     if (cluster == 0) {
@@ -625,10 +641,9 @@ void choose_cluster_by_model(int device, const DeviceState& dev, int workload, c
     if (workload == CREDIT_WL_ROW_REDUCE || is_row_op(workload)) return;
     if (o->variant == CREDIT_VARIANT_BLOCK_READ || o->variant == CREDIT_VARIANT_BLOCK_SMEM) return;
     if (o->schedule == CREDIT_SCHEDULE_ROW_PER_CLUSTER) return;
-    // the warp-specialised kernel takes the smallest cluster whose slice fits it (plan_static)
-    if (workload == CREDIT_WL_LAYERNORM_BACKWARD_STATS && grads &&
-        (o->threads == 0 || o->threads == kWsThreadsPerCta || o->threads == kWsThreadsPerCtaWide))
-        return;
+    // the warp-specialised kernels take the smallest cluster whose slice fits them (plan_static)
+    if (o->threads == kWsThreadsPerCta || o->threads == kWsThreadsPerCtaWide) return;
+    if (workload == CREDIT_WL_LAYERNORM_BACKWARD_STATS && grads && o->threads == 0) return;
     const auto key = std::make_tuple(device, workload, s.rows, s.cols, dtype, pointers_aligned, grads, o->variant,
                                      o->threads, o->stages, o->flags);
     {
@@ -709,6 +724,10 @@ Launch make_launch(const Resolved& r, void* stream) {
     return l;
 }
 
+bool is_ws_plan(const credit_plan_info& p) {
+    return p.threads == kWsThreadsPerCta || p.threads == kWsThreadsPerCtaWide;
+}
+
 StagedArgs staged_args(const Resolved& r) {
     StagedArgs a;
     a.rows = r.shape.rows;
@@ -778,6 +797,15 @@ int credit_rmsnorm_forward(const void* x, const float* gamma, void* y, int64_t r
         return launch_cluster_kernel(make_launch(r, stream), args);
     }
     StagedArgs a = staged_args(r);
+    if (is_ws_plan(r.plan)) {
+        NormParams prm{};
+        prm.x = x;
+        prm.gamma = gamma;
+        prm.y = y;
+        prm.eps = eps;
+        void* args[] = {&prm, &a};
+        return launch_cluster_kernel(make_launch(r, stream), args);
+    }
     void* args[] = {&x, &gamma, &y, &eps, &a};
     return launch_cluster_kernel(make_launch(r, stream), args);
 }
@@ -819,6 +847,18 @@ int credit_layernorm_forward(const void* x, const float* gamma, const float* bet
         return launch_cluster_kernel(make_launch(r, stream), args);
     }
     StagedArgs a = staged_args(r);
+    if (is_ws_plan(r.plan)) {
+        NormParams prm{};
+        prm.x = x;
+        prm.gamma = gamma;
+        prm.beta = beta;
+        prm.y = y;
+        prm.mean_out = mean;
+        prm.rstd_out = rstd;
+        prm.eps = eps;
+        void* args[] = {&prm, &a};
+        return launch_cluster_kernel(make_launch(r, stream), args);
+    }
     void* args[] = {&x, &gamma, &beta, &y, &mean, &rstd, &eps, &a};
     return launch_cluster_kernel(make_launch(r, stream), args);
 }
@@ -896,6 +936,17 @@ int credit_layernorm_backward_stats(const void* x, const void* dy, const float* 
     float eps = 0.0f;
     if (r.plan.variant == CREDIT_VARIANT_BLOCK_READ) {
         void* args[] = {&x, &dy, &gamma, &mean, &rstd, &dx, &eps, &r.shape.rows, &r.shape.cols};
+        rc = launch_cluster_kernel(make_launch(r, stream), args);
+    } else if (is_ws_plan(r.plan)) {
+        NormParams prm{};
+        prm.x = x;
+        prm.dy = dy;
+        prm.gamma = gamma;
+        prm.mean_in = mean;
+        prm.rstd_in = rstd;
+        prm.y = dx;
+        prm.partials = partials;
+        void* args[] = {&prm, &a};
         rc = launch_cluster_kernel(make_launch(r, stream), args);
     } else if (r.plan.vectors_per_thread > 0) {
         void* args[] = {&x, &dy, &gamma, &mean, &rstd, &dx, &partials, &eps, &a};

@@ -31,6 +31,27 @@ struct StagedArgs {
     int* status;        // device status word
 };
 
+// Pointers of the normalisation workloads, as the warp-specialised kernels take them (one struct
+// for RMSNorm forward, LayerNorm forward and LayerNorm backward; unused members are NULL).
+struct NormParams {
+    const void* x;
+    const void* dy;
+    const float* gamma;
+    const float* beta;
+    const float* mean_in;    // given statistics (backward)
+    const float* rstd_in;
+    void* y;                 // y (forward) or dx (backward)
+    float* mean_out;         // computed statistics (LayerNorm forward)
+    float* rstd_out;
+    float* partials;         // [num_clusters][2][cols] partial column sums (backward)
+    float eps;
+};
+
+// Row elements one output thread of a warp-specialised kernel may own (what it keeps per element
+// in registers bounds it): forward kernels 32 in either form; backward with column sums 16 with
+// 16 output warps, 32 with 8.
+constexpr int ws_max_elems_per_thread(bool backward, bool wide) { return backward && !wide ? 16 : 32; }
+
 // Pointers of a reference-sweep workload (weighted variance, Pearson, softmax
 // backward, LARS, int8 quantisation).
 struct RowOpArgs {

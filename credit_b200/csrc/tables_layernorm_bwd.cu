@@ -75,17 +75,10 @@ const void* generic_func(int threads, bool aligned, bool has_stats) {
 
 const void* layernorm_bwd_reg_kernel_f32(int threads, int vpt, bool full, bool has_stats, bool grads);
 const void* layernorm_bwd_reg_kernel_bf16(int threads, int vpt, bool full, bool has_stats, bool grads);
-const void* layernorm_bwd_ws_kernel_f32(int out_warps, int vpt, bool full);
-const void* layernorm_bwd_ws_kernel_bf16(int out_warps, int vpt, bool full);
 
 const void* layernorm_bwd_kernel_for(int dtype, int threads, int vpt, bool full, bool aligned,
                                      bool has_stats, bool grads) {
     const bool f32 = dtype == CREDIT_F32;
-    if (vpt > 0 && (threads == kWsThreadsPerCta || threads == kWsThreadsPerCtaWide)) {
-        const int out_warps = threads / 32 - 3;   // three service warps
-        if (!has_stats || !grads) return nullptr;
-        return f32 ? layernorm_bwd_ws_kernel_f32(out_warps, vpt, full) : layernorm_bwd_ws_kernel_bf16(out_warps, vpt, full);
-    }
     if (vpt > 0)
         return f32 ? layernorm_bwd_reg_kernel_f32(threads, vpt, full, has_stats, grads)
                    : layernorm_bwd_reg_kernel_bf16(threads, vpt, full, has_stats, grads);

@@ -5,7 +5,6 @@
 #include "kernel_tables.h"
 #include "norm_kernels.cuh"
 #include "register_row_kernels.cuh"
-#include "ws_row_kernels.cuh"
 
 namespace credit {
 namespace {
@@ -39,30 +38,6 @@ const void* layernorm_bwd_reg_kernel_bf16(int threads, int vpt, bool full, bool 
                                              bool grads) {
     return full ? reg_func<__nv_bfloat16, true>(threads, vpt, has_stats, grads)
                 : reg_func<__nv_bfloat16, false>(threads, vpt, has_stats, grads);
-}
-
-// The warp-specialised kernel (given statistics + parameter gradients): 16 output warps of up to 16
-// row elements per thread or 8 output warps of up to 32, each thread owning `vpt` 16-byte vectors of
-// its CTA's slice, plus a producer and a collector warp.
-const void* layernorm_bwd_ws_kernel_bf16(int out_warps, int vpt, bool full) {
-    if (out_warps == 16) {
-        switch (vpt) {
-        case 1: return full ? (const void*)layernorm_bwd_ws_kernel<__nv_bfloat16, 16, 1, true>
-                            : (const void*)layernorm_bwd_ws_kernel<__nv_bfloat16, 16, 1, false>;
-        case 2: return full ? (const void*)layernorm_bwd_ws_kernel<__nv_bfloat16, 16, 2, true>
-                            : (const void*)layernorm_bwd_ws_kernel<__nv_bfloat16, 16, 2, false>;
-            default: return nullptr;
-        }
-    }
-    switch (vpt) {
-        case 1: return full ? (const void*)layernorm_bwd_ws_kernel<__nv_bfloat16, 8, 1, true>
-                            : (const void*)layernorm_bwd_ws_kernel<__nv_bfloat16, 8, 1, false>;
-        case 2: return full ? (const void*)layernorm_bwd_ws_kernel<__nv_bfloat16, 8, 2, true>
-                            : (const void*)layernorm_bwd_ws_kernel<__nv_bfloat16, 8, 2, false>;
-        case 4: return full ? (const void*)layernorm_bwd_ws_kernel<__nv_bfloat16, 8, 4, true>
-                            : (const void*)layernorm_bwd_ws_kernel<__nv_bfloat16, 8, 4, false>;
-        default: return nullptr;
-    }
 }
 
 }  // namespace credit

@@ -5,7 +5,6 @@
 #include "kernel_tables.h"
 #include "norm_kernels.cuh"
 #include "register_row_kernels.cuh"
-#include "ws_row_kernels.cuh"
 
 namespace credit {
 namespace {
@@ -40,34 +39,6 @@ const void* layernorm_bwd_reg_kernel_f32(int threads, int vpt, bool full, bool h
                                              bool grads) {
     return full ? reg_func<float, true>(threads, vpt, has_stats, grads)
                 : reg_func<float, false>(threads, vpt, has_stats, grads);
-}
-
-// The warp-specialised kernel (given statistics + parameter gradients): 16 output warps of up to 16
-// row elements per thread or 8 output warps of up to 32, each thread owning `vpt` 16-byte vectors of
-// its CTA's slice, plus a producer and a collector warp.
-const void* layernorm_bwd_ws_kernel_f32(int out_warps, int vpt, bool full) {
-    if (out_warps == 16) {
-        switch (vpt) {
-        case 1: return full ? (const void*)layernorm_bwd_ws_kernel<float, 16, 1, true>
-                            : (const void*)layernorm_bwd_ws_kernel<float, 16, 1, false>;
-        case 2: return full ? (const void*)layernorm_bwd_ws_kernel<float, 16, 2, true>
-                            : (const void*)layernorm_bwd_ws_kernel<float, 16, 2, false>;
-        case 4: return full ? (const void*)layernorm_bwd_ws_kernel<float, 16, 4, true>
-                            : (const void*)layernorm_bwd_ws_kernel<float, 16, 4, false>;
-            default: return nullptr;
-        }
-    }
-    switch (vpt) {
-        case 1: return full ? (const void*)layernorm_bwd_ws_kernel<float, 8, 1, true>
-                            : (const void*)layernorm_bwd_ws_kernel<float, 8, 1, false>;
-        case 2: return full ? (const void*)layernorm_bwd_ws_kernel<float, 8, 2, true>
-                            : (const void*)layernorm_bwd_ws_kernel<float, 8, 2, false>;
-        case 4: return full ? (const void*)layernorm_bwd_ws_kernel<float, 8, 4, true>
-                            : (const void*)layernorm_bwd_ws_kernel<float, 8, 4, false>;
-        case 8: return full ? (const void*)layernorm_bwd_ws_kernel<float, 8, 8, true>
-                            : (const void*)layernorm_bwd_ws_kernel<float, 8, 8, false>;
-        default: return nullptr;
-    }
 }
 
 }  // namespace credit

@@ -1,24 +1,22 @@
-// Warp-specialised wide-row kernels: LayerNorm backward with given statistics and
-// parameter gradients (dx, dgamma, dbeta).
+// Warp-specialised wide-row kernels: RMSNorm forward, LayerNorm forward and LayerNorm
+// backward with given statistics and parameter gradients, on one pipeline.
 //
 // The register-resident kernels (register_row_kernels.cuh) run every warp through one
 // latency chain per row: ring wait -> loads -> partial sums -> shuffle tree -> DSMEM
-// exchange -> fold -> outputs, two rows deep. With the column sums in registers as well,
-// that kernel sits at 128 registers and 16 warps per SM, and the chain (about 2900 cycles
-// per row), not HBM, sets its pace. Here the chain is cut up and handed to specialised
-// warps, and the two halves that stay in the arithmetic warps run `ahead` rows apart, so
-// that no arithmetic warp waits for an exchange it has just started, or runs a shuffle
-// tree at all:
+// exchange -> fold -> outputs, two rows deep. That chain (about 2900 cycles per row for
+// LayerNorm backward at 16 warps per SM), not HBM, sets their pace. Here the chain is cut
+// up and handed to specialised warps, and the two halves that stay in the arithmetic
+// warps run `ahead` rows apart, so that no arithmetic warp waits for an exchange it has
+// just started, or runs a shuffle tree at all:
 //
 //   producer warp (1 lane)  keeps a ring of D stages full with bulk-async (TMA) copies
-//                           of the CTA's x and dy slices of the cluster's next rows;
+//                           of the CTA's slices of the cluster's next rows;
 //   output warps (16 or 8)  iteration i: pass 1 of row i (read the slice from its stage,
-//                           S1 = sum g, S2 = sum g (x - mean) over the thread's own
-//                           columns, leave the pair in shared memory, arrive on a
-//                           CTA-local mbarrier), then pass 2 of row i - ahead (whose
-//                           cluster-wide sums were published long ago: read the slice
-//                           again, write dx, accumulate dgamma / dbeta in registers,
-//                           free the stage);
+//                           the thread's share of the row's one or two sums, left in
+//                           shared memory; one arrival per warp on a CTA-local
+//                           mbarrier), then pass 2 of row i - ahead (whose cluster-wide
+//                           sums were published long ago: read the slice again, write
+//                           the outputs, free the stage);
 //   collector warp          per row: waits for the output threads' pairs, adds them up
 //                           and pushes the CTA's pair to every CTA of the cluster with
 //                           st.async, which lands data and arrival on the receiver's
@@ -27,12 +25,12 @@
 //                           rank order (every CTA gets the same bits) and publishes the
 //                           row's two sums to the output warps behind one more mbarrier.
 //
-// A row's slice is read from shared memory twice (3 x 32 KiB of shared-memory traffic
-// per 48 KiB of HBM traffic at the target shape, well inside the SM's bandwidth) instead
-// of being held in registers across the exchange; that frees the registers that kept
-// two rows and lets the ring run D - ahead - 1 rows ahead of the arithmetic. The service
-// warps wait with the suspending mbarrier.try_wait so that they do not take issue slots
-// from the output warps.
+// A row's slice is read from shared memory twice instead of being held in registers
+// across the exchange (for LayerNorm backward 3 x 32 KiB of shared-memory traffic per
+// 48 KiB of HBM traffic at the target shape, well inside the SM's bandwidth); that frees
+// the registers that kept two rows and lets the ring run D - ahead - 1 rows ahead of the
+// arithmetic. The service warps wait with the suspending mbarrier.try_wait so that they
+// do not take issue slots from the output warps.
 //
 // Buffer depths: CTA-local partial buffers 4 >= ahead + 1 (an output warp writes row r + 4
 // only after it finished pass 2 of row r + 3 - ahead, for which the collector has long read
@@ -41,15 +39,23 @@
 // CTA finished pass 2 of row r + 6 - 2 * ahead >= r). The same distances keep an mbarrier
 // from being re-armed before all its waiters have seen the previous phase.
 //
-// Arithmetic per element is that of layernorm_bwd_reg_kernel, i.e. of the reference's
-// cluster_bwd_staged_kernel (src/workloads/layernorm_backward.cu:401-437) extended to
-// given statistics and parameter gradients; only the order in which a row's partial sums
-// are added differs (fixed, so results are deterministic).
+// A workload is a policy struct (RmsNormFwdOp, LayerNormFwdOp, LayerNormBwdOp below): what a
+// thread keeps for the whole kernel, the per-row scalars it fetches one row early, its
+// share of pass 1 and its share of pass 2. Arithmetic per element is that of the
+// register-resident kernels, i.e. of the reference's cluster_bwd_staged_kernel family
+// (src/workloads/layernorm_backward.cu:376-438); only the order in which a row's partial
+// sums are added differs (fixed, so results are deterministic).
 #pragma once
 
 #include "cluster_primitives.cuh"
 #include "norm_kernels.cuh"
 #include "register_row_kernels.cuh"
+
+#ifdef CREDIT_WS_NO_STORES   /* experiment */
+#define WS_STORE(ptr, val) do { const uint4 v__ = (val); if (v__.x == 0x12345678u) __stcs((ptr), v__); } while (0)
+#else
+#define WS_STORE(ptr, val) __stcs((ptr), (val))
+#endif
 
 namespace credit {
 
@@ -67,6 +73,8 @@ struct alignas(16) WsControl {
     uint64_t local_bar[kWsLocalBuffers];       // every output warp has left its pairs of a row
     uint64_t ex_bar[kWsSlotBuffers];           // the P pairs of a row are in slot
     uint64_t ready_bar[kWsSlotBuffers];        // the row's two sums are in total
+    uint64_t info_bar[kWsSlotBuffers];         // the row's scalars are in row_info
+    float4 row_info[kWsSlotBuffers];           // per-row scalars, published kWsInfoLead rows early
     float2 total[kWsSlotBuffers];
     float slot[kWsSlotBuffers][2 * kMaxClusterSize];   // [source rank][partial]
     float2 thread_part[kWsLocalBuffers][kWsMaxOutputWarps * 32];   // [row % 4][output thread]
@@ -76,27 +84,42 @@ static_assert(sizeof(WsControl) <= kWsControlBytes, "control block overflows its
 // Rows between pass 1 and pass 2 of an output warp, from the ring depth the host chose.
 __device__ __forceinline__ int ws_rows_ahead(int stages) { return stages >= 5 ? 2 : 1; }
 
-// OUT_WARPS output warps: 16, or 8 with twice the row elements per thread (the per-row work of a
-// warp that does not depend on its element count -- waits, row scalars, addresses -- is then paid
-// by half as many warps).
-template <typename T, int OUT_WARPS, int VPT, bool FULL>
-__global__ void __launch_bounds__((OUT_WARPS + kWsServiceWarps) * 32, 1)
-layernorm_bwd_ws_kernel(const T* __restrict__ x, const T* __restrict__ dy, const float* __restrict__ gamma,
-                        const float* __restrict__ mean_in, const float* __restrict__ rstd_in,
-                        T* __restrict__ dx, float* __restrict__ partials, float /*eps*/, StagedArgs a) {
+// Per-row scalars (given statistics, or the three samples the shift of the one-pass variance is the
+// median of). The output warps never load them from global memory: the lines are cold (each is used
+// during a few rows only while gigabytes stream through the L2), and a warp that waits two
+// microseconds for one stalls its whole row step. One lane of the collector warp loads them
+// kWsInfoLead + 1 rows ahead and publishes them in shared memory kWsInfoLead rows ahead.
+struct WsRow {
+    float a, b, c;
+};
+constexpr int kWsInfoLead = 3;   // > ahead: the output warps run at most `ahead` rows before the collector
+
+// ---------------------------------------------------------------------------
+// the pipeline
+// ---------------------------------------------------------------------------
+// Op::kOutWarps output warps: 16, or 8 with twice the row elements per thread (the per-row work of
+// a warp that does not depend on its element count -- waits, row scalars, addresses -- is then
+// paid by half as many warps).
+template <class Op>
+__global__ void __launch_bounds__((Op::kOutWarps + kWsServiceWarps) * 32, 1)
+ws_row_kernel(NormParams prm, StagedArgs a) {
+    using T = typename Op::Elem;
+    constexpr int NIN = Op::kInputs;
+    constexpr int OUT_WARPS = Op::kOutWarps;
+    constexpr int THREADS = OUT_WARPS * 32;
+    constexpr int VPT = Op::kVectors;
+    constexpr bool FULL = Op::kFull;
+    constexpr int E = PairVec<T>::kElems;
+
     extern __shared__ __align__(1024) unsigned char smem[];
     auto& ctl = *reinterpret_cast<WsControl*>(smem);
     unsigned char* data = smem + kWsControlBytes;
-    constexpr int E = PairVec<T>::kElems;
-    constexpr int PAIRS = PairVec<T>::kPairs;
-    constexpr int THREADS = OUT_WARPS * 32;
 
     const uint32_t rank = cluster_cta_rank();
     const uint32_t nranks = cluster_cta_count();
     const int cluster = blockIdx.x / nranks;
     const SliceGeom g = slice_geometry(a.cols, a.slice_elems, rank);
     const int nvec = g.local / E;
-    const T* const src[2] = {x, dy};
     const int my_rows = cluster < a.rows ? (a.rows - cluster + a.num_clusters - 1) / a.num_clusters : 0;
     const int stages = a.stages;
     const int ahead = ws_rows_ahead(stages);
@@ -112,6 +135,7 @@ layernorm_bwd_ws_kernel(const T* __restrict__ x, const T* __restrict__ dy, const
         for (int b = 0; b < kWsSlotBuffers; ++b) {
             mbar_init(smem_u32(&ctl.ex_bar[b]), 1);
             mbar_init(smem_u32(&ctl.ready_bar[b]), 1);
+            mbar_init(smem_u32(&ctl.info_bar[b]), 1);
         }
         fence_mbar_init();
     }
@@ -124,11 +148,14 @@ layernorm_bwd_ws_kernel(const T* __restrict__ x, const T* __restrict__ dy, const
     // ---- producer: one lane keeps the ring full
     if (warp == OUT_WARPS) {
         if (lane == 0 && g.local > 0) {
+            const T* src[NIN];
+            Op::sources(prm, src);
+            const T* const(&csrc)[NIN] = src;
             int stage = 0;
             uint32_t parity = 1;   // parity of the phase the LAST use of the stage completed
             for (int it = 0; it < my_rows; ++it) {
                 if (it >= stages) mbar_wait_parked_bounded(smem_u32(&ctl.empty[stage]), parity, a.status);
-                issue_slice_fill<T, 2>(src, data, ctl.full, stage, cluster + it * a.num_clusters, a, g);
+                issue_slice_fill<T, NIN>(csrc, data, ctl.full, stage, cluster + it * a.num_clusters, a, g);
                 if (++stage == stages) {
                     stage = 0;
                     parity ^= 1u;
@@ -138,9 +165,29 @@ layernorm_bwd_ws_kernel(const T* __restrict__ x, const T* __restrict__ dy, const
         return;
     }
 
-    // ---- collector: the output threads' pairs of a row -> one pair -> every CTA of the cluster
+    // ---- collector: the output threads' pairs of a row -> one pair -> every CTA of the cluster;
+    // lane 0 also publishes the rows' scalars ahead of the output warps
     if (warp == OUT_WARPS + 1) {
+        auto publish = [&](int r, const WsRow& info) {
+            const int ib = r & (kWsSlotBuffers - 1);
+            ctl.row_info[ib] = Op::publish_row(info);
+            mbar_arrive(smem_u32(&ctl.info_bar[ib]));   // release
+        };
+        WsRow next_info{0.0f, 0.0f, 0.0f};
+        if (Op::kRowInfo && lane == 0) {
+            for (int r = 0; r < kWsInfoLead && r < my_rows; ++r)
+                publish(r, Op::fetch_row(prm, cluster + r * a.num_clusters, a.cols));
+            if (kWsInfoLead < my_rows) next_info = Op::fetch_row(prm, cluster + kWsInfoLead * a.num_clusters, a.cols);
+        }
         for (int it = 0; it < my_rows; ++it) {
+            if (Op::kRowInfo && lane == 0) {
+                // row it + lead was loaded one iteration ago; row it + lead + 1 is requested now. Buffer
+                // (it + lead) % 8 last held row it + lead - 8, which every output warp finished before it
+                // delivered the row the previous iteration waited for.
+                if (it + kWsInfoLead < my_rows) publish(it + kWsInfoLead, next_info);
+                if (it + kWsInfoLead + 1 < my_rows)
+                    next_info = Op::fetch_row(prm, cluster + (it + kWsInfoLead + 1) * a.num_clusters, a.cols);
+            }
             const int lb = it & (kWsLocalBuffers - 1);
             const int xb = it & (kWsSlotBuffers - 1);
             mbar_wait_parked_bounded(smem_u32(&ctl.local_bar[lb]), (static_cast<uint32_t>(it) / kWsLocalBuffers) & 1u, a.status);
@@ -155,7 +202,8 @@ layernorm_bwd_ws_kernel(const T* __restrict__ x, const T* __restrict__ dy, const
                 acc1 = __fadd2_rn(acc1, make_float2(v.z, v.w));
             }
             const float2 mine = __fadd2_rn(acc0, acc1);
-            // both sums over the warp in one tree (warp_sum_split): S1 ends in lanes 0..15, S2 in 16..31
+            // both sums over the warp in one tree (warp_sum_split): the first ends in lanes 0..15, the
+            // second in lanes 16..31
             const float t = warp_sum_split(mine.x, mine.y);
             const float t0 = __shfl_sync(0xffffffffu, t, 0);
             const float t1 = __shfl_sync(0xffffffffu, t, 16);
@@ -174,9 +222,9 @@ layernorm_bwd_ws_kernel(const T* __restrict__ x, const T* __restrict__ dy, const
             float t = idx < nranks ? ctl.slot[xb][2 * idx + half] : 0.0f;
 #pragma unroll
             for (int offset = 8; offset > 0; offset >>= 1) t += __shfl_xor_sync(0xffffffffu, t, offset);
-            const float sum2 = __shfl_sync(0xffffffffu, t, 16);
+            const float second = __shfl_sync(0xffffffffu, t, 16);
             if (lane == 0) {
-                ctl.total[xb] = make_float2(t, sum2);
+                ctl.total[xb] = make_float2(t, second);
                 mbar_arrive(smem_u32(&ctl.ready_bar[xb]));   // release: the pair is visible to whoever sees the phase
             }
         }
@@ -184,73 +232,29 @@ layernorm_bwd_ws_kernel(const T* __restrict__ x, const T* __restrict__ dy, const
     }
 
     // ---- output warps
-    float2 gam[VPT][PAIRS], dgam[VPT][PAIRS], dbet[VPT][PAIRS];
-#pragma unroll
-    for (int i = 0; i < VPT; ++i) {
-        const int v = threadIdx.x + i * THREADS;
-#pragma unroll
-        for (int j = 0; j < PAIRS; ++j) {
-            gam[i][j] = splat(0.0f);
-            dgam[i][j] = splat(0.0f);
-            dbet[i][j] = splat(0.0f);
-        }
-        if (FULL || v < nvec) load_param_pairs<PAIRS>(gamma + g.start + v * E, gam[i]);
-    }
-    const float inv_cols = 1.0f / static_cast<float>(a.cols);
-
-    // Row statistics travel through a short shift register: [0] row it + 1 (fetched one iteration
-    // early), [1] row it (pass 1), [2] row it - 1, [3] row it - 2 (pass 2, by `ahead`).
-    float mean_q[4] = {0.0f, 0.0f, 0.0f, 0.0f}, rstd_q[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-    if (my_rows > 0) {
-        mean_q[0] = __ldg(mean_in + cluster);
-        rstd_q[0] = __ldg(rstd_in + cluster);
-    }
+    typename Op::State st;
+    Op::init(st, prm, g.start, nvec);
 
     int stage1 = 0;               // ring stage of pass 1's row
     uint32_t parity1 = 0;
     int stage2 = 0;               // ring stage of pass 2's row
 
     for (int it = 0; it < my_rows + ahead; ++it) {
-#pragma unroll
-        for (int k = 3; k > 0; --k) {
-            mean_q[k] = mean_q[k - 1];
-            rstd_q[k] = rstd_q[k - 1];
-        }
-        if (it + 1 < my_rows) {
-            const int next_row = cluster + (it + 1) * a.num_clusters;
-            mean_q[0] = __ldg(mean_in + next_row);
-            rstd_q[0] = __ldg(rstd_in + next_row);
-        }
-
-        // ---- pass 1 of row `it`: this thread's share of S1 = sum g and S2 = sum g * (x - mean)
+        // ---- pass 1 of row `it`: this thread's share of the row's sums
         if (it < my_rows) {
-            const float mean = mean_q[1];
             if (g.local > 0) mbar_wait_bounded(smem_u32(&ctl.full[stage1]), parity1, a.status);
-            const uint4* xt = reinterpret_cast<const uint4*>(stage_tile<T, 2>(data, stage1, 0, a.slice_elems));
-            const uint4* dt = reinterpret_cast<const uint4*>(stage_tile<T, 2>(data, stage1, 1, a.slice_elems));
-            const float2 neg_mean = splat(-mean);
-            float2 s1[2] = {splat(0.0f), splat(0.0f)}, s2[2] = {splat(0.0f), splat(0.0f)};   // two chains each
+            const uint4* tiles[NIN];
 #pragma unroll
-            for (int i = 0; i < VPT; ++i) {
-                const int v = threadIdx.x + i * THREADS;
-                if (FULL || v < nvec) {
-                    float2 xv[PAIRS], dv[PAIRS];
-                    PairVec<T>::unpack(xt[v], xv);
-                    PairVec<T>::unpack(dt[v], dv);
-#pragma unroll
-                    for (int j = 0; j < PAIRS; ++j) {
-                        const float2 gg = __fmul2_rn(dv[j], gam[i][j]);
-                        s1[j & 1] = __fadd2_rn(s1[j & 1], gg);
-                        // 16-bit rows: sum g * x here, mean * sum g comes off once per row below
-                        s2[j & 1] = sizeof(T) == 2 ? __ffma2_rn(gg, xv[j], s2[j & 1])
-                                                   : __ffma2_rn(gg, __fadd2_rn(xv[j], neg_mean), s2[j & 1]);
-                    }
-                }
-            }
-            const float2 s1t = __fadd2_rn(s1[0], s1[1]), s2t = __fadd2_rn(s2[0], s2[1]);
-            const float t1 = s1t.x + s1t.y, t2 = s2t.x + s2t.y;
+            for (int n = 0; n < NIN; ++n)
+                tiles[n] = reinterpret_cast<const uint4*>(stage_tile<T, NIN>(data, stage1, n, a.slice_elems));
             const int lb = it & (kWsLocalBuffers - 1);
-            ctl.thread_part[lb][threadIdx.x] = make_float2(t1, sizeof(T) == 2 ? fmaf(-mean, t1, t2) : t2);
+            float4 info = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            if (Op::kRowInfo) {
+                const int ib = it & (kWsSlotBuffers - 1);
+                mbar_wait_bounded(smem_u32(&ctl.info_bar[ib]), (static_cast<uint32_t>(it) / kWsSlotBuffers) & 1u, a.status);
+                info = ctl.row_info[ib];
+            }
+            ctl.thread_part[lb][threadIdx.x] = Op::pass1(st, tiles, nvec, info);
             __syncwarp();   // the other lanes' stores are ordered before lane 0's release
             if (lane == 0) mbar_arrive(smem_u32(&ctl.local_bar[lb]));
             if (++stage1 == stages) {
@@ -259,51 +263,20 @@ layernorm_bwd_ws_kernel(const T* __restrict__ x, const T* __restrict__ dy, const
             }
         }
 
-        // ---- pass 2 of row `it - ahead`: dx from the staged slice, column sums into registers
+        // ---- pass 2 of row `it - ahead`: outputs from the staged slice
         if (it >= ahead) {
             const int it2 = it - ahead;
             const int row = cluster + it2 * a.num_clusters;
-            const float mean = ahead == 2 ? mean_q[3] : mean_q[2];
-            const float rstd = ahead == 2 ? rstd_q[3] : rstd_q[2];
             const int xb = it2 & (kWsSlotBuffers - 1);
             mbar_wait_bounded(smem_u32(&ctl.ready_bar[xb]), (static_cast<uint32_t>(it2) / kWsSlotBuffers) & 1u, a.status);
             const float2 sums = ctl.total[xb];
-
-            const uint4* xt = reinterpret_cast<const uint4*>(stage_tile<T, 2>(data, stage2, 0, a.slice_elems));
-            const uint4* dt = reinterpret_cast<const uint4*>(stage_tile<T, 2>(data, stage2, 1, a.slice_elems));
-            const float2 neg_mean = splat(-mean), rstd2 = splat(rstd);
-            const float2 ca = splat(-rstd * rstd * rstd * (sums.y * inv_cols));
-            const float2 cb = splat(-rstd * (sums.x * inv_cols));
-            // 16-bit rows work on xhat = x * rstd - mean * rstd (one fused operation; the rounding of
-            // the constant is far below the output's 2^-9): dx = xhat * ca_hat + g * rstd + cb and
-            // dgamma += dy * xhat, one operation less per pair than the (x - mean) form fp32 rows keep.
-            const float2 shift2 = splat(-mean * rstd);
-            const float2 ca_hat = splat(-rstd * rstd * (sums.y * inv_cols));
-            uint4* out = reinterpret_cast<uint4*>(dx + static_cast<size_t>(row) * a.cols + g.start);
+            // the row's scalars were published before its pass 1, which this warp has run
+            const float4 info = Op::kRowInfo ? ctl.row_info[xb] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            const uint4* tiles[NIN];
 #pragma unroll
-            for (int i = 0; i < VPT; ++i) {
-                const int v = threadIdx.x + i * THREADS;
-                if (FULL || v < nvec) {
-                    float2 xv[PAIRS], dv[PAIRS], o[PAIRS];
-                    PairVec<T>::unpack(xt[v], xv);
-                    PairVec<T>::unpack(dt[v], dv);
-#pragma unroll
-                    for (int j = 0; j < PAIRS; ++j) {
-                        const float2 gg = __fmul2_rn(dv[j], gam[i][j]);
-                        if (sizeof(T) == 2) {
-                            const float2 xhat = __ffma2_rn(xv[j], rstd2, shift2);
-                            o[j] = __ffma2_rn(xhat, ca_hat, __ffma2_rn(gg, rstd2, cb));
-                            dgam[i][j] = __ffma2_rn(dv[j], xhat, dgam[i][j]);
-                        } else {
-                            const float2 c = __fadd2_rn(xv[j], neg_mean);
-                            o[j] = __ffma2_rn(c, ca, __ffma2_rn(gg, rstd2, cb));
-                            dgam[i][j] = __ffma2_rn(__fmul2_rn(dv[j], c), rstd2, dgam[i][j]);
-                        }
-                        dbet[i][j] = __fadd2_rn(dbet[i][j], dv[j]);
-                    }
-                    __stcs(out + v, PairVec<T>::pack(o));
-                }
-            }
+            for (int n = 0; n < NIN; ++n)
+                tiles[n] = reinterpret_cast<const uint4*>(stage_tile<T, NIN>(data, stage2, n, a.slice_elems));
+            Op::pass2(st, tiles, nvec, info, sums, prm, row, a.cols, g.start, rank);
             if (g.local > 0) {
                 __syncwarp();   // every lane has read its vectors of the stage
                 if (lane == 0) mbar_arrive(smem_u32(&ctl.empty[stage2]));
@@ -311,22 +284,285 @@ layernorm_bwd_ws_kernel(const T* __restrict__ x, const T* __restrict__ dy, const
             if (++stage2 == stages) stage2 = 0;
         }
     }
+    Op::finish(st, prm, cluster, a.cols, g.start, nvec);
+}
 
-    float* out_g = partials + (static_cast<size_t>(cluster) * 2 + 0) * a.cols + g.start;
-    float* out_b = partials + (static_cast<size_t>(cluster) * 2 + 1) * a.cols + g.start;
+// ---------------------------------------------------------------------------
+// RMSNorm forward: y = x * rsqrt(mean(x^2) + eps) * gamma. One sum per row.
+// ---------------------------------------------------------------------------
+template <typename T, int OUT_WARPS, int VPT, bool FULL>
+struct RmsNormFwdOp {
+    using Elem = T;
+    static constexpr int kInputs = 1, kOutWarps = OUT_WARPS, kVectors = VPT, THREADS = OUT_WARPS * 32;
+    static constexpr bool kFull = FULL;
+    static constexpr int E = PairVec<T>::kElems, PAIRS = PairVec<T>::kPairs;
+    struct State {
+        float2 gam[VPT][PAIRS];
+    };
+    __device__ __forceinline__ static void sources(const NormParams& p, const T* (&src)[1]) {
+        src[0] = static_cast<const T*>(p.x);
+    }
+    static constexpr bool kRowInfo = false;
+    __device__ __forceinline__ static WsRow fetch_row(const NormParams&, int, int) { return WsRow{0.0f, 0.0f, 0.0f}; }
+    __device__ __forceinline__ static float4 publish_row(const WsRow&) { return make_float4(0.0f, 0.0f, 0.0f, 0.0f); }
+    __device__ __forceinline__ static void init(State& st, const NormParams& p, int col0, int nvec) {
 #pragma unroll
-    for (int i = 0; i < VPT; ++i) {
-        const int v = threadIdx.x + i * THREADS;
-        if (FULL || v < nvec) {
+        for (int i = 0; i < VPT; ++i) {
+            const int v = threadIdx.x + i * THREADS;
 #pragma unroll
-            for (int j = 0; j < PAIRS; j += 2) {
-                *reinterpret_cast<float4*>(out_g + v * E + 2 * j) =
-                    make_float4(dgam[i][j].x, dgam[i][j].y, dgam[i][j + 1].x, dgam[i][j + 1].y);
-                *reinterpret_cast<float4*>(out_b + v * E + 2 * j) =
-                    make_float4(dbet[i][j].x, dbet[i][j].y, dbet[i][j + 1].x, dbet[i][j + 1].y);
+            for (int j = 0; j < PAIRS; ++j) st.gam[i][j] = splat(0.0f);
+            if (FULL || v < nvec) load_param_pairs<PAIRS>(p.gamma + col0 + v * E, st.gam[i]);
+        }
+    }
+    __device__ __forceinline__ static float2 pass1(State&, const uint4* const (&tiles)[1], int nvec, const float4&) {
+        float2 q[2] = {splat(0.0f), splat(0.0f)};
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+            const int v = threadIdx.x + i * THREADS;
+            if (FULL || v < nvec) {
+                float2 xv[PAIRS];
+                PairVec<T>::unpack(tiles[0][v], xv);
+#pragma unroll
+                for (int j = 0; j < PAIRS; ++j) q[j & 1] = __ffma2_rn(xv[j], xv[j], q[j & 1]);
+            }
+        }
+        const float2 t = __fadd2_rn(q[0], q[1]);
+        return make_float2(t.x + t.y, 0.0f);
+    }
+    __device__ __forceinline__ static void pass2(State& st, const uint4* const (&tiles)[1], int nvec, const float4&,
+                                                 float2 sums, const NormParams& p, int row, int cols, int col0, uint32_t) {
+        const float2 scale = splat(rsqrtf(sums.x * (1.0f / static_cast<float>(cols)) + p.eps));
+        uint4* out = reinterpret_cast<uint4*>(static_cast<T*>(p.y) + static_cast<size_t>(row) * cols + col0);
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+            const int v = threadIdx.x + i * THREADS;
+            if (FULL || v < nvec) {
+                float2 xv[PAIRS];
+                PairVec<T>::unpack(tiles[0][v], xv);
+#pragma unroll
+                for (int j = 0; j < PAIRS; ++j) xv[j] = __fmul2_rn(__fmul2_rn(xv[j], scale), st.gam[i][j]);
+                WS_STORE(out + v, PairVec<T>::pack(xv));
             }
         }
     }
-}
+    __device__ __forceinline__ static void finish(State&, const NormParams&, int, int, int, int) {}
+};
+
+// ---------------------------------------------------------------------------
+// LayerNorm forward: y = (x - mean) * rstd * gamma + beta, plus mean and rstd. Shifted one-pass
+// sums S = sum(x - K), Q = sum((x - K)^2) with K = row_shift_sample (median of three elements of
+// the row, the same in every CTA).
+// ---------------------------------------------------------------------------
+template <typename T, int OUT_WARPS, int VPT, bool FULL>
+struct LayerNormFwdOp {
+    using Elem = T;
+    static constexpr int kInputs = 1, kOutWarps = OUT_WARPS, kVectors = VPT, THREADS = OUT_WARPS * 32;
+    static constexpr bool kFull = FULL;
+    static constexpr int E = PairVec<T>::kElems, PAIRS = PairVec<T>::kPairs;
+    struct State {
+        float2 gam[VPT][PAIRS], bet[VPT][PAIRS];
+    };
+    __device__ __forceinline__ static void sources(const NormParams& p, const T* (&src)[1]) {
+        src[0] = static_cast<const T*>(p.x);
+    }
+    __device__ __forceinline__ static WsRow fetch_row(const NormParams& p, int row, int cols) {
+        const T* r = static_cast<const T*>(p.x) + static_cast<size_t>(row) * cols;
+        return WsRow{RowVec<T>::to_float(__ldg(r)), RowVec<T>::to_float(__ldg(r + (cols >> 1))),
+                     RowVec<T>::to_float(__ldg(r + (cols - 1)))};
+    }
+    static constexpr bool kRowInfo = true;
+    // the row's shift: the median of its three samples (see row_shift_sample)
+    __device__ __forceinline__ static float4 publish_row(const WsRow& r) {
+        return make_float4(fmaxf(fminf(r.a, r.b), fminf(fmaxf(r.a, r.b), r.c)), 0.0f, 0.0f, 0.0f);
+    }
+    __device__ __forceinline__ static void init(State& st, const NormParams& p, int col0, int nvec) {
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+            const int v = threadIdx.x + i * THREADS;
+#pragma unroll
+            for (int j = 0; j < PAIRS; ++j) {
+                st.gam[i][j] = splat(0.0f);
+                st.bet[i][j] = splat(0.0f);
+            }
+            if (FULL || v < nvec) {
+                load_param_pairs<PAIRS>(p.gamma + col0 + v * E, st.gam[i]);
+                load_param_pairs<PAIRS>(p.beta + col0 + v * E, st.bet[i]);
+            }
+        }
+    }
+    __device__ __forceinline__ static float2 pass1(State&, const uint4* const (&tiles)[1], int nvec, const float4& r) {
+        const float2 neg_shift = splat(-r.x);
+        float2 s[2] = {splat(0.0f), splat(0.0f)}, q[2] = {splat(0.0f), splat(0.0f)};
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+            const int v = threadIdx.x + i * THREADS;
+            if (FULL || v < nvec) {
+                float2 xv[PAIRS];
+                PairVec<T>::unpack(tiles[0][v], xv);
+#pragma unroll
+                for (int j = 0; j < PAIRS; ++j) {
+                    const float2 d = __fadd2_rn(xv[j], neg_shift);
+                    s[j & 1] = __fadd2_rn(s[j & 1], d);
+                    q[j & 1] = __ffma2_rn(d, d, q[j & 1]);
+                }
+            }
+        }
+        const float2 st = __fadd2_rn(s[0], s[1]), qt = __fadd2_rn(q[0], q[1]);
+        return make_float2(st.x + st.y, qt.x + qt.y);
+    }
+    __device__ __forceinline__ static void pass2(State& st, const uint4* const (&tiles)[1], int nvec, const float4& r,
+                                                 float2 sums, const NormParams& p, int row, int cols, int col0,
+                                                 uint32_t rank) {
+        float mean, var;
+        moments_from_shifted(sums.x, sums.y, r.x, cols, mean, var);
+        const float rstd = rsqrtf(var + p.eps);
+        if (rank == 0 && threadIdx.x == 0) {
+            p.mean_out[row] = mean;
+            p.rstd_out[row] = rstd;
+        }
+        const float2 neg_mean = splat(-mean), rstd2 = splat(rstd);
+        // 16-bit rows: xhat = x * rstd - mean * rstd in one fused operation (the rounding of the
+        // constant costs |mean| / std * 6e-8 on xhat, far below the output's own 2^-9); fp32 rows
+        // keep the exact (x - mean) * rstd.
+        const float2 shift2 = splat(-mean * rstd);
+        uint4* out = reinterpret_cast<uint4*>(static_cast<T*>(p.y) + static_cast<size_t>(row) * cols + col0);
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+            const int v = threadIdx.x + i * THREADS;
+            if (FULL || v < nvec) {
+                float2 xv[PAIRS];
+                PairVec<T>::unpack(tiles[0][v], xv);
+#pragma unroll
+                for (int j = 0; j < PAIRS; ++j) {
+                    const float2 xhat = sizeof(T) == 2 ? __ffma2_rn(xv[j], rstd2, shift2)
+                                                       : __fmul2_rn(__fadd2_rn(xv[j], neg_mean), rstd2);
+                    xv[j] = __ffma2_rn(xhat, st.gam[i][j], st.bet[i][j]);
+                }
+                WS_STORE(out + v, PairVec<T>::pack(xv));
+            }
+        }
+    }
+    __device__ __forceinline__ static void finish(State&, const NormParams&, int, int, int, int) {}
+};
+
+// ---------------------------------------------------------------------------
+// LayerNorm backward with given statistics: dx, and the column sums dgamma / dbeta of the rows
+// this cluster handled (written at the end to partials[cluster][2][cols]). With c = x - mean,
+// xhat = c * rstd, g = dy * gamma, S1 = sum_row g and S2 = sum_row g * c:
+//   dx = g * rstd + c * (-rstd^3 * S2 / N) + (-rstd * S1 / N)
+// ---------------------------------------------------------------------------
+template <typename T, int OUT_WARPS, int VPT, bool FULL>
+struct LayerNormBwdOp {
+    using Elem = T;
+    static constexpr int kInputs = 2, kOutWarps = OUT_WARPS, kVectors = VPT, THREADS = OUT_WARPS * 32;
+    static constexpr bool kFull = FULL;
+    static constexpr int E = PairVec<T>::kElems, PAIRS = PairVec<T>::kPairs;
+    struct State {
+        float2 gam[VPT][PAIRS], dgam[VPT][PAIRS], dbet[VPT][PAIRS];
+    };
+    __device__ __forceinline__ static void sources(const NormParams& p, const T* (&src)[2]) {
+        src[0] = static_cast<const T*>(p.x);
+        src[1] = static_cast<const T*>(p.dy);
+    }
+    __device__ __forceinline__ static WsRow fetch_row(const NormParams& p, int row, int) {
+        return WsRow{__ldg(p.mean_in + row), __ldg(p.rstd_in + row), 0.0f};
+    }
+    static constexpr bool kRowInfo = true;
+    __device__ __forceinline__ static float4 publish_row(const WsRow& r) { return make_float4(r.a, r.b, 0.0f, 0.0f); }
+    __device__ __forceinline__ static void init(State& st, const NormParams& p, int col0, int nvec) {
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+            const int v = threadIdx.x + i * THREADS;
+#pragma unroll
+            for (int j = 0; j < PAIRS; ++j) {
+                st.gam[i][j] = splat(0.0f);
+                st.dgam[i][j] = splat(0.0f);
+                st.dbet[i][j] = splat(0.0f);
+            }
+            if (FULL || v < nvec) load_param_pairs<PAIRS>(p.gamma + col0 + v * E, st.gam[i]);
+        }
+    }
+    // this thread's share of S1 = sum g and S2 = sum g * (x - mean)
+    __device__ __forceinline__ static float2 pass1(State& st, const uint4* const (&tiles)[2], int nvec, const float4& r) {
+        const float mean = r.x;
+        const float2 neg_mean = splat(-mean);
+        float2 s1[2] = {splat(0.0f), splat(0.0f)}, s2[2] = {splat(0.0f), splat(0.0f)};   // two chains each
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+            const int v = threadIdx.x + i * THREADS;
+            if (FULL || v < nvec) {
+                float2 xv[PAIRS], dv[PAIRS];
+                PairVec<T>::unpack(tiles[0][v], xv);
+                PairVec<T>::unpack(tiles[1][v], dv);
+#pragma unroll
+                for (int j = 0; j < PAIRS; ++j) {
+                    const float2 gg = __fmul2_rn(dv[j], st.gam[i][j]);
+                    s1[j & 1] = __fadd2_rn(s1[j & 1], gg);
+                    // 16-bit rows: sum g * x here, mean * sum g comes off once per row below
+                    s2[j & 1] = sizeof(T) == 2 ? __ffma2_rn(gg, xv[j], s2[j & 1])
+                                               : __ffma2_rn(gg, __fadd2_rn(xv[j], neg_mean), s2[j & 1]);
+                }
+            }
+        }
+        const float2 s1t = __fadd2_rn(s1[0], s1[1]), s2t = __fadd2_rn(s2[0], s2[1]);
+        const float t1 = s1t.x + s1t.y, t2 = s2t.x + s2t.y;
+        return make_float2(t1, sizeof(T) == 2 ? fmaf(-mean, t1, t2) : t2);
+    }
+    __device__ __forceinline__ static void pass2(State& st, const uint4* const (&tiles)[2], int nvec, const float4& r,
+                                                 float2 sums, const NormParams& p, int row, int cols, int col0, uint32_t) {
+        const float mean = r.x, rstd = r.y;
+        const float inv_cols = 1.0f / static_cast<float>(cols);
+        const float2 neg_mean = splat(-mean), rstd2 = splat(rstd);
+        const float2 ca = splat(-rstd * rstd * rstd * (sums.y * inv_cols));
+        const float2 cb = splat(-rstd * (sums.x * inv_cols));
+        // 16-bit rows work on xhat = x * rstd - mean * rstd (one fused operation; the rounding of
+        // the constant is far below the output's 2^-9): dx = xhat * ca_hat + g * rstd + cb and
+        // dgamma += dy * xhat, one operation less per pair than the (x - mean) form fp32 rows keep.
+        const float2 shift2 = splat(-mean * rstd);
+        const float2 ca_hat = splat(-rstd * rstd * (sums.y * inv_cols));
+        uint4* out = reinterpret_cast<uint4*>(static_cast<T*>(p.y) + static_cast<size_t>(row) * cols + col0);
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+            const int v = threadIdx.x + i * THREADS;
+            if (FULL || v < nvec) {
+                float2 xv[PAIRS], dv[PAIRS], o[PAIRS];
+                PairVec<T>::unpack(tiles[0][v], xv);
+                PairVec<T>::unpack(tiles[1][v], dv);
+#pragma unroll
+                for (int j = 0; j < PAIRS; ++j) {
+                    const float2 gg = __fmul2_rn(dv[j], st.gam[i][j]);
+                    if (sizeof(T) == 2) {
+                        const float2 xhat = __ffma2_rn(xv[j], rstd2, shift2);
+                        o[j] = __ffma2_rn(xhat, ca_hat, __ffma2_rn(gg, rstd2, cb));
+                        st.dgam[i][j] = __ffma2_rn(dv[j], xhat, st.dgam[i][j]);
+                    } else {
+                        const float2 c = __fadd2_rn(xv[j], neg_mean);
+                        o[j] = __ffma2_rn(c, ca, __ffma2_rn(gg, rstd2, cb));
+                        st.dgam[i][j] = __ffma2_rn(__fmul2_rn(dv[j], c), rstd2, st.dgam[i][j]);
+                    }
+                    st.dbet[i][j] = __fadd2_rn(st.dbet[i][j], dv[j]);
+                }
+                WS_STORE(out + v, PairVec<T>::pack(o));
+            }
+        }
+    }
+    __device__ __forceinline__ static void finish(State& st, const NormParams& p, int cluster, int cols, int col0, int nvec) {
+        float* out_g = p.partials + (static_cast<size_t>(cluster) * 2 + 0) * cols + col0;
+        float* out_b = p.partials + (static_cast<size_t>(cluster) * 2 + 1) * cols + col0;
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+            const int v = threadIdx.x + i * THREADS;
+            if (FULL || v < nvec) {
+#pragma unroll
+                for (int j = 0; j < PAIRS; j += 2) {
+                    *reinterpret_cast<float4*>(out_g + v * E + 2 * j) =
+                        make_float4(st.dgam[i][j].x, st.dgam[i][j].y, st.dgam[i][j + 1].x, st.dgam[i][j + 1].y);
+                    *reinterpret_cast<float4*>(out_b + v * E + 2 * j) =
+                        make_float4(st.dbet[i][j].x, st.dbet[i][j].y, st.dbet[i][j + 1].x, st.dbet[i][j + 1].y);
+                }
+            }
+        }
+    }
+};
 
 }  // namespace credit

@@ -290,8 +290,8 @@ def test_layernorm_statistics_survive_an_outlier_in_the_first_column(dtype, sigm
     dy = torch.randn(rows, cols).to(dtype)
     _, want_mean, want_rstd = O.layernorm_forward(x, gamma, beta, dtype=torch.float64)
     want_dx = O.layernorm_backward(x.double(), dy.double(), gamma.double())
-    for p in (2, 8, 16):
-        y, mean, rstd = run("layernorm_forward", (x, gamma, beta), p)
+    for p, opts in ((2, None), (8, None), (16, None), (8, {"threads": 608}), (16, {"threads": 352}), (8, {"threads": 512})):
+        y, mean, rstd = run("layernorm_forward", (x, gamma, beta), p, opts)
         close(rstd, want_rstd, FP32_RTOL, what=f"rstd P={p}")
         close(mean, want_mean, FP32_RTOL, scale=1.0, what=f"mean P={p}")
     for p in (4, 8, 16):   # x and dy staged: two fp32 half rows do not fit one CTA
@@ -416,6 +416,28 @@ def test_layernorm_backward_stats_warp_specialised_kernel(threads, dtype, cluste
         plan = N.plan(N.WL_LAYERNORM_BACKWARD_STATS, rows, cols, N.BF16 if dtype == torch.bfloat16 else N.F32,
                       dict(opts, cluster_size=cluster_size))
         assert plan.threads == threads and plan.stages >= 3
+
+
+@pytest.mark.parametrize("stages", [0, 3, 5])
+@pytest.mark.parametrize("cluster_size", [1, 2, 4, 8, 16])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("threads", [608, 352])
+def test_forward_warp_specialised_kernels(threads, dtype, cluster_size, stages):
+    """RMSNorm and LayerNorm forward on the warp-specialised pipeline (threads = 608 / 352): many
+    rows per cluster so every ring and buffer wraps; an aligned-but-ragged width leaves partial
+    tiles and empty slices; a wide row exercises the largest vector counts."""
+    opts = {"threads": threads, "stages": stages}
+    for rows, cols in ((2500, 2048), (1999, 1096), (40, 16384 * cluster_size if cluster_size <= 4 else 65536)):
+        x, gamma = W.make_rmsnorm_inputs(rows, cols, "cpu", seed=rows)
+        x = x.to(dtype)
+        (y,) = try_run("rmsnorm_forward", (x, gamma), cluster_size, opts)
+        close(y, O.rmsnorm_forward(x, gamma, dtype=torch.float64), BF16_RTOL if dtype == torch.bfloat16 else FP32_RTOL,
+              what="rmsnorm y")
+        inputs = W.make_layernorm_forward_inputs(rows, cols, "cpu", seed=rows + 1, dtype=dtype)
+        got = try_run("layernorm_forward", inputs, cluster_size, opts)
+        check_layernorm_forward(inputs, got, BF16_RTOL if dtype == torch.bfloat16 else FP32_RTOL)
+        code = N.BF16 if dtype == torch.bfloat16 else N.F32
+        assert N.plan(N.WL_LAYERNORM_FORWARD, rows, cols, code, dict(opts, cluster_size=cluster_size)).threads == threads
 
 
 def test_layernorm_backward_stats_automatic_plan_is_warp_specialised():
