@@ -444,9 +444,9 @@ int plan_static(int workload, const Shape& s, int dtype, const credit_launch_opt
     if (ws_workload && p->aligned && !(o.flags & CREDIT_FLAG_NO_REGISTER_PATH) && (o.threads == 0 || ws_threads) &&
         o.schedule != CREDIT_SCHEDULE_ROW_PER_CLUSTER && (o.stages == 0 || o.stages >= 3) &&
         o.variant != CREDIT_VARIANT_BLOCK_SMEM) {
-        // measured at the target shapes: 8 output warps with twice the elements per thread win for the
-        // backward kernel (per-row work of a warp is paid by half as many warps)
-        const int threads = o.threads ? o.threads : (grads ? kWsThreadsPerCtaWide : kWsThreadsPerCta);
+        // measured at the target shapes: 8 output warps with twice the elements per thread win over 16
+        // (the per-row work of a warp is paid by half as many warps)
+        const int threads = o.threads ? o.threads : kWsThreadsPerCtaWide;
         const bool wide = threads == kWsThreadsPerCtaWide;
         const int out_threads = threads - 96;   // three service warps
         const int max_slice = out_threads * ws_max_elems_per_thread(grads, wide);
@@ -590,6 +590,9 @@ size_t grads_workspace_bytes(const Shape& s, const credit_plan_info& p) {
     return partials * 2 * static_cast<size_t>(s.cols) * sizeof(float);
 }
 
+bool is_ws_plan_threads(int threads) { return threads == kWsThreadsPerCta || threads == kWsThreadsPerCtaWide; }
+bool is_ws_plan(const credit_plan_info& p) { return is_ws_plan_threads(p.threads); }
+
 struct Resolved {
     DeviceState* dev = nullptr;
     int device = 0;
@@ -630,6 +633,28 @@ double predicted_ms(int workload, const Shape& s, const credit_plan_info& p, boo
     return std::sqrt(hbm_ms * hbm_ms + latency_ms * latency_ms);
 }
 
+// The warp-specialised kernels: a cluster's row period is the larger of its CTAs' share of the HBM
+// bandwidth (the SMs the co-resident clusters cover share the copy ceiling; one SM pulls at most
+// about 58 GB/s through bulk copies) and the output warps' issue time for one row (a fixed part per
+// row plus a part per row element a thread owns); a kernel costs rows-per-cluster + 3 such periods
+// (ring fill, the rows between the two passes, the last cluster's extra row). Constants measured on
+// B200 with 8 output warps: fixed part 400 cycles (1100 in clusters of 16), 25 cycles per element
+// forward and 40 backward, 12 % more with a ring too short to run the passes two rows apart.
+double predicted_ws_ms(int workload, const Shape& s, const credit_plan_info& p, bool grads) {
+    const int nin = inputs_staged(workload);
+    const double bytes_per_cta_row = static_cast<double>(nin + 1) * p.slice_elems * s.elem_bytes;
+    const double sms = static_cast<double>(std::max(p.num_clusters, 1)) * p.cluster_size;
+    const double per_sm_gbps = std::min(6538.6 / sms, 58.0);
+    const double hbm_us = bytes_per_cta_row / (per_sm_gbps * 1.0e3);
+    const int out_threads = p.threads - 96;
+    const double elems = std::ceil(static_cast<double>(p.slice_elems) / out_threads);
+    const double issue_us = ((p.cluster_size >= 16 ? 1100.0 : 400.0) + (grads ? 40.0 : 25.0) * elems) / 1930.0;
+    double row_us = std::max(hbm_us, issue_us);
+    if (p.stages < 5) row_us *= 1.12;
+    const double rows_per_cluster = std::ceil(static_cast<double>(s.rows) / std::max(p.num_clusters, 1));
+    return row_us * (rows_per_cluster + 3.0) * 1.0e-3;
+}
+
 // (device, workload, rows, cols, dtype, aligned, grads, variant, threads, stages, flags) -> chosen size
 std::map<std::tuple<int, int, int, int, int, bool, bool, int, int, int, int>, int> g_auto_cluster;
 
@@ -641,9 +666,6 @@ void choose_cluster_by_model(int device, const DeviceState& dev, int workload, c
     if (workload == CREDIT_WL_ROW_REDUCE || is_row_op(workload)) return;
     if (o->variant == CREDIT_VARIANT_BLOCK_READ || o->variant == CREDIT_VARIANT_BLOCK_SMEM) return;
     if (o->schedule == CREDIT_SCHEDULE_ROW_PER_CLUSTER) return;
-    // the warp-specialised kernels take the smallest cluster whose slice fits them (plan_static)
-    if (o->threads == kWsThreadsPerCta || o->threads == kWsThreadsPerCtaWide) return;
-    if (workload == CREDIT_WL_LAYERNORM_BACKWARD_STATS && grads && o->threads == 0) return;
     const auto key = std::make_tuple(device, workload, s.rows, s.cols, dtype, pointers_aligned, grads, o->variant,
                                      o->threads, o->stages, o->flags);
     {
@@ -654,8 +676,11 @@ void choose_cluster_by_model(int device, const DeviceState& dev, int workload, c
             return;
         }
     }
-    int best = 0;
-    double best_ms = 0.0;
+    // two passes, as cost_model.best_cluster_size does: the fastest prediction, then the smallest
+    // cluster within 1 % of it
+    int sizes[8];
+    double times[8];
+    int candidates = 0;
     for (int c = o->variant == CREDIT_VARIANT_CLUSTER_SMEM ? 2 : 1; c <= kMaxClusterSize; c *= 2) {
         credit_launch_opts trial = *o;
         trial.cluster_size = c;
@@ -665,17 +690,21 @@ void choose_cluster_by_model(int device, const DeviceState& dev, int workload, c
         // never below the smallest cluster whose stage fits the budget (larger stages measured
         // slower with inputs that are not in L2); the model decides whether to go above it
         const bool two_reads = inputs_staged(workload) == 2 && !grads;
-        if (c < kMaxClusterSize &&
+        if (!is_ws_plan(plan) && c < kMaxClusterSize &&
             inputs_staged(workload) * plan.slice_elems * s.elem_bytes > (two_reads ? 2 : 1) * kAutoStageBytes)
             continue;
         const void* func = workload_func(workload, dtype, plan, grads);
         if (func == nullptr || prepare_function(device, func, dev.info.max_dynamic_smem_per_block) != CREDIT_OK) continue;
         if (plan_grid(device, func, s, &plan) != CREDIT_OK) continue;
-        const double ms = predicted_ms(workload, s, plan, grads);
-        if (best == 0 || ms < best_ms * 0.99) {   // within 1 %: the smaller cluster stays
-            best = c;
-            best_ms = ms;
-        }
+        sizes[candidates] = c;
+        times[candidates] = is_ws_plan(plan) ? predicted_ws_ms(workload, s, plan, grads) : predicted_ms(workload, s, plan, grads);
+        ++candidates;
+    }
+    int best = 0;
+    if (candidates > 0) {
+        const double fastest = *std::min_element(times, times + candidates);
+        for (int i = 0; i < candidates && best == 0; ++i)
+            if (times[i] <= fastest * 1.01) best = sizes[i];
     }
     t_last_error[0] = '\0';   // failed trials are not errors of this call
     if (best == 0) return;
@@ -722,10 +751,6 @@ Launch make_launch(const Resolved& r, void* stream) {
     l.smem = r.plan.smem_bytes;
     l.stream = static_cast<cudaStream_t>(stream);
     return l;
-}
-
-bool is_ws_plan(const credit_plan_info& p) {
-    return p.threads == kWsThreadsPerCta || p.threads == kWsThreadsPerCtaWide;
 }
 
 StagedArgs staged_args(const Resolved& r) {

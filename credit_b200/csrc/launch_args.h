@@ -48,9 +48,9 @@ struct NormParams {
 };
 
 // Row elements one output thread of a warp-specialised kernel may own (what it keeps per element
-// in registers bounds it): forward kernels 32 in either form; backward with column sums 16 with
-// 16 output warps, 32 with 8.
-constexpr int ws_max_elems_per_thread(bool backward, bool wide) { return backward && !wide ? 16 : 32; }
+// in registers bounds it): forward kernels 32 with 16 output warps and 64 with 8; backward with
+// column sums 16 and 32.
+constexpr int ws_max_elems_per_thread(bool backward, bool wide) { return (backward ? 16 : 32) * (wide ? 2 : 1); }
 
 // Pointers of a reference-sweep workload (weighted variance, Pearson, softmax
 // backward, LARS, int8 quantisation).

@@ -51,12 +51,6 @@
 #include "norm_kernels.cuh"
 #include "register_row_kernels.cuh"
 
-#ifdef CREDIT_WS_NO_STORES   /* experiment */
-#define WS_STORE(ptr, val) do { const uint4 v__ = (val); if (v__.x == 0x12345678u) __stcs((ptr), v__); } while (0)
-#else
-#define WS_STORE(ptr, val) __stcs((ptr), (val))
-#endif
-
 namespace credit {
 
 constexpr int kWsMaxOutputWarps = 16;
@@ -341,7 +335,7 @@ struct RmsNormFwdOp {
                 PairVec<T>::unpack(tiles[0][v], xv);
 #pragma unroll
                 for (int j = 0; j < PAIRS; ++j) xv[j] = __fmul2_rn(__fmul2_rn(xv[j], scale), st.gam[i][j]);
-                WS_STORE(out + v, PairVec<T>::pack(xv));
+                __stcs(out + v, PairVec<T>::pack(xv));
             }
         }
     }
@@ -438,7 +432,7 @@ struct LayerNormFwdOp {
                                                        : __fmul2_rn(__fadd2_rn(xv[j], neg_mean), rstd2);
                     xv[j] = __ffma2_rn(xhat, st.gam[i][j], st.bet[i][j]);
                 }
-                WS_STORE(out + v, PairVec<T>::pack(xv));
+                __stcs(out + v, PairVec<T>::pack(xv));
             }
         }
     }
@@ -542,7 +536,7 @@ struct LayerNormBwdOp {
                     }
                     st.dbet[i][j] = __fadd2_rn(st.dbet[i][j], dv[j]);
                 }
-                WS_STORE(out + v, PairVec<T>::pack(o));
+                __stcs(out + v, PairVec<T>::pack(o));
             }
         }
     }

@@ -18,6 +18,7 @@ const void* ws_pick(int vpt, bool full) {
     if constexpr (2 * E <= MAX_ELEMS) { if (vpt == 2) return ws_entry<Op, T, W, 2>(full); }
     if constexpr (4 * E <= MAX_ELEMS) { if (vpt == 4) return ws_entry<Op, T, W, 4>(full); }
     if constexpr (8 * E <= MAX_ELEMS) { if (vpt == 8) return ws_entry<Op, T, W, 8>(full); }
+    if constexpr (16 * E <= MAX_ELEMS) { if (vpt == 16) return ws_entry<Op, T, W, 16>(full); }
     return nullptr;
 }
 

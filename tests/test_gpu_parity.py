@@ -442,9 +442,13 @@ def test_forward_warp_specialised_kernels(threads, dtype, cluster_size, stages):
 
 def test_layernorm_backward_stats_automatic_plan_is_warp_specialised():
     plan = N.plan(N.WL_LAYERNORM_BACKWARD_STATS, 8192, 65536, N.BF16)
-    assert plan.threads in (608, 352) and plan.cluster_size == 8 and plan.full_tiles == 1
-    assert plan.vectors_per_thread == (2 if plan.threads == 608 else 4)
+    assert (plan.threads, plan.cluster_size, plan.vectors_per_thread, plan.full_tiles) == (352, 8, 4, 1)
     assert plan.stages == 6 and plan.smem_bytes == 20480 + 6 * 32768
+    # the forward kernels at their target shapes: same pipeline
+    plan = N.plan(N.WL_LAYERNORM_FORWARD, 4096, 131072, N.BF16)
+    assert (plan.threads, plan.cluster_size, plan.vectors_per_thread) == (352, 8, 8)
+    plan = N.plan(N.WL_RMSNORM_FORWARD, 1024, 32768, N.F32)
+    assert plan.threads == 352 and plan.cluster_size in (8, 16)
     # explicit thread counts keep the lock-step register kernels
     assert N.plan(N.WL_LAYERNORM_BACKWARD_STATS, 8192, 65536, N.BF16, {"threads": 512}).threads == 512
 
