@@ -40,6 +40,7 @@ LIB_SOURCES = [
     "tables_ws_rmsnorm.cu",
     "tables_ws_layernorm_fwd.cu",
     "tables_ws_layernorm_bwd.cu",
+    "tables_ws_row_ops.cu",
 ]
 OBJ_DIR = LIB_DIR / "obj"
 # name of the executable -> (source, links against the shared library)

@@ -122,6 +122,15 @@ __device__ __forceinline__ void st_async_f32x2(uint32_t remote_addr, float v0, f
                  : "memory");
 }
 
+// Four floats (16-byte aligned destination) in one message.
+__device__ __forceinline__ void st_async_f32x4(uint32_t remote_addr, float v0, float v1, float v2, float v3,
+                                               uint32_t remote_bar) {
+    asm volatile("st.async.shared::cluster.mbarrier::complete_tx::bytes.v4.f32 [%0], {%1, %2, %3, %4}, [%5];" ::"r"(
+                     remote_addr),
+                 "f"(v0), "f"(v1), "f"(v2), "f"(v3), "r"(remote_bar)
+                 : "memory");
+}
+
 // One poll, never suspends: true when the phase with this parity has completed. The suspending
 // form (mbarrier.try_wait) wakes a warp late when the phase completes shortly after the first
 // look, which is the usual case on the row path: measured on one GPU, polling is 0.8 % (LayerNorm

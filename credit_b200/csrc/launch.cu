@@ -281,6 +281,8 @@ bool is_row_op(int workload) {
 
 const void* workload_func(int workload, int dtype, const credit_plan_info& p, bool want_grads) {
     const bool al = p.aligned != 0;
+    if (is_row_op(workload) && (p.threads == kWsThreadsPerCta || p.threads == kWsThreadsPerCtaWide))
+        return ws_row_op_kernel_for(workload);
     if (is_row_op(workload)) return row_op_kernel_for(workload, p.threads, al, p.variant != CREDIT_VARIANT_BLOCK_READ);
     if (p.variant == CREDIT_VARIANT_BLOCK_READ) return block_read_kernel_for(workload, dtype, al);
     const int vpt = p.vectors_per_thread;
@@ -440,7 +442,9 @@ int plan_static(int workload, const Shape& s, int dtype, const credit_launch_opt
     // ring of at least three stages fits shared memory. threads = 256 / 512 keep the lock-step
     // register kernels.
     const bool ws_threads = o.threads == kWsThreadsPerCta || o.threads == kWsThreadsPerCtaWide;
-    const bool ws_workload = workload == CREDIT_WL_RMSNORM_FORWARD || workload == CREDIT_WL_LAYERNORM_FORWARD || grads;
+    const bool row_op = is_row_op(workload);   // no per-column registers: any slice length, 8 output warps only
+    const bool ws_workload = workload == CREDIT_WL_RMSNORM_FORWARD || workload == CREDIT_WL_LAYERNORM_FORWARD || grads ||
+                             (row_op && o.threads != kWsThreadsPerCta);
     if (ws_workload && p->aligned && !(o.flags & CREDIT_FLAG_NO_REGISTER_PATH) && (o.threads == 0 || ws_threads) &&
         o.schedule != CREDIT_SCHEDULE_ROW_PER_CLUSTER && (o.stages == 0 || o.stages >= 3) &&
         o.variant != CREDIT_VARIANT_BLOCK_SMEM) {
@@ -449,7 +453,7 @@ int plan_static(int workload, const Shape& s, int dtype, const credit_launch_opt
         const int threads = o.threads ? o.threads : kWsThreadsPerCtaWide;
         const bool wide = threads == kWsThreadsPerCtaWide;
         const int out_threads = threads - 96;   // three service warps
-        const int max_slice = out_threads * ws_max_elems_per_thread(grads, wide);
+        const int max_slice = row_op ? (1 << 30) : out_threads * ws_max_elems_per_thread(grads, wide);
         auto ws_fits = [&](int c) {
             return round_up((s.cols + c - 1) / c, 64) <= max_slice && kWsControlBytes + 3 * stage_bytes_for(c) <= max_smem;
         };
@@ -463,7 +467,8 @@ int plan_static(int workload, const Shape& s, int dtype, const credit_launch_opt
             p->slice_elems = round_up((s.cols + c - 1) / c, 64);
             const int nvec = p->slice_elems / s.vec_elems;
             int vpt = 1;
-            while (vpt * out_threads < nvec) vpt *= 2;
+            while (vpt * out_threads < nvec && !row_op) vpt *= 2;
+            if (row_op) vpt = std::max(1, (nvec + out_threads - 1) / out_threads);
             const int stage_bytes = stage_bytes_for(c);
             int stages = o.stages ? o.stages : 6;
             while (stages > 3 && kWsControlBytes + stages * stage_bytes > max_smem) --stages;
@@ -481,8 +486,8 @@ int plan_static(int workload, const Shape& s, int dtype, const credit_launch_opt
                         max_slice, stage_bytes_for(std::max(o.cluster_size, 1)));
     } else if (ws_threads) {
         return fail(CREDIT_ERR_UNSUPPORTED,
-                    "threads = %d selects a warp-specialised kernel: RMSNorm / LayerNorm forward or LayerNorm "
-                    "backward with column sums, 16-byte aligned rows, persistent schedule, at least three stages",
+                    "threads = %d selects a warp-specialised kernel: 16-byte aligned rows, persistent schedule, at "
+                    "least three stages (LayerNorm backward: with column sums; reference-sweep workloads: 352 only)",
                     o.threads);
     }
     int cluster = o.cluster_size;
@@ -642,13 +647,17 @@ double predicted_ms(int workload, const Shape& s, const credit_plan_info& p, boo
 // forward and 40 backward, 12 % more with a ring too short to run the passes two rows apart.
 double predicted_ws_ms(int workload, const Shape& s, const credit_plan_info& p, bool grads) {
     const int nin = inputs_staged(workload);
-    const double bytes_per_cta_row = static_cast<double>(nin + 1) * p.slice_elems * s.elem_bytes;
+    double nout = 1.0;   // output arrays of the element type written per row
+    if (workload == CREDIT_WL_PEARSON_BACKWARD || workload == CREDIT_WL_LARS_MOMENTUM) nout = 2.0;
+    if (workload == CREDIT_WL_ROWWISE_QUANT) nout = 0.25;
+    const double bytes_per_cta_row = (nin + nout) * p.slice_elems * s.elem_bytes;
     const double sms = static_cast<double>(std::max(p.num_clusters, 1)) * p.cluster_size;
     const double per_sm_gbps = std::min(6538.6 / sms, 58.0);
     const double hbm_us = bytes_per_cta_row / (per_sm_gbps * 1.0e3);
     const int out_threads = p.threads - 96;
     const double elems = std::ceil(static_cast<double>(p.slice_elems) / out_threads);
-    const double issue_us = ((p.cluster_size >= 16 ? 1100.0 : 400.0) + (grads ? 40.0 : 25.0) * elems) / 1930.0;
+    const double per_elem = grads ? 40.0 : (is_row_op(workload) ? 12.0 * (nin + nout) : 25.0);
+    const double issue_us = ((p.cluster_size >= 16 ? 1100.0 : 400.0) + per_elem * elems) / 1930.0;
     double row_us = std::max(hbm_us, issue_us);
     if (p.stages < 5) row_us *= 1.12;
     const double rows_per_cluster = std::ceil(static_cast<double>(s.rows) / std::max(p.num_clusters, 1));
@@ -663,7 +672,11 @@ std::map<std::tuple<int, int, int, int, int, bool, bool, int, int, int, int>, in
 void choose_cluster_by_model(int device, const DeviceState& dev, int workload, const Shape& s, int dtype,
                              bool pointers_aligned, bool grads, credit_launch_opts* o) {
     if (o->cluster_size != 0 || s.rows == 0 || !dev.info.cluster_launch) return;
-    if (workload == CREDIT_WL_ROW_REDUCE || is_row_op(workload)) return;
+    if (workload == CREDIT_WL_ROW_REDUCE) return;
+    // Reference-sweep workloads: the smallest cluster whose ring fits (plan_static's rule) was the
+    // fastest or within 10 % of it at every measured point: smaller clusters cover more SMs (148,
+    // 148, 132, 120, 112 for sizes 1 ... 16) and spread a row's fixed costs over longer slices.
+    if (is_row_op(workload)) return;
     if (o->variant == CREDIT_VARIANT_BLOCK_READ || o->variant == CREDIT_VARIANT_BLOCK_SMEM) return;
     if (o->schedule == CREDIT_SCHEDULE_ROW_PER_CLUSTER) return;
     const auto key = std::make_tuple(device, workload, s.rows, s.cols, dtype, pointers_aligned, grads, o->variant,
@@ -1021,6 +1034,19 @@ int credit_row_op(int workload, const float* in0, const float* in1, const float*
     int rc = resolve(workload, rows, cols, CREDIT_F32, opts, al, false, &r);
     if (rc != CREDIT_OK) return rc;
     if (r.shape.rows == 0) return CREDIT_OK;
+    if (is_ws_plan(r.plan)) {
+        NormParams prm{};
+        prm.x = in0;
+        prm.dy = in1;
+        prm.in2 = in2;
+        prm.row_in = row_in;
+        prm.y = out0;
+        prm.out1 = out1;
+        prm.row_out = row_out;
+        StagedArgs a = staged_args(r);
+        void* args[] = {&prm, &a};
+        return launch_cluster_kernel(make_launch(r, stream), args);
+    }
     RowOpArgs io;
     for (int n = 0; n < 3; ++n) io.in[n] = ins[n];
     io.row_in = row_in;

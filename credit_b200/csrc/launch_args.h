@@ -12,7 +12,7 @@ constexpr int kMaxStages = 8;
 // shared memory holds one pair of partial sums per output thread for four rows.
 constexpr int kWsThreadsPerCta = 608;
 constexpr int kWsThreadsPerCtaWide = 352;
-constexpr int kWsControlBytes = 20480;
+constexpr int kWsControlBytes = 22528;
 // Bytes reserved at the start of dynamic shared memory for barriers and
 // reduction scratch; row data starts after it (keeps 1024-byte alignment).
 constexpr int kControlBytes = 4096;
@@ -34,8 +34,12 @@ struct StagedArgs {
 // Pointers of the normalisation workloads, as the warp-specialised kernels take them (one struct
 // for RMSNorm forward, LayerNorm forward and LayerNorm backward; unused members are NULL).
 struct NormParams {
-    const void* x;
-    const void* dy;
+    const void* x;           // first staged input
+    const void* dy;          // second staged input
+    const void* in2;         // third staged input (reference-sweep workloads)
+    void* out1;              // second output (reference-sweep workloads)
+    const float* row_in;     // per-row input (Pearson: upstream gradient [rows])
+    float* row_out;          // per-row output (quantiser: scale [rows])
     const float* gamma;
     const float* beta;
     const float* mean_in;    // given statistics (backward)

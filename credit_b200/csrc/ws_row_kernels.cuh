@@ -1,5 +1,6 @@
-// Warp-specialised wide-row kernels: RMSNorm forward, LayerNorm forward and LayerNorm
-// backward with given statistics and parameter gradients, on one pipeline.
+// Warp-specialised wide-row kernels: one pipeline for RMSNorm forward, LayerNorm forward,
+// LayerNorm backward with given statistics and parameter gradients (policies below) and the
+// five workloads of the reference sweep (policies in ws_row_ops.cuh).
 //
 // The register-resident kernels (register_row_kernels.cuh) run every warp through one
 // latency chain per row: ring wait -> loads -> partial sums -> shuffle tree -> DSMEM
@@ -12,18 +13,20 @@
 //   producer warp (1 lane)  keeps a ring of D stages full with bulk-async (TMA) copies
 //                           of the CTA's slices of the cluster's next rows;
 //   output warps (16 or 8)  iteration i: pass 1 of row i (read the slice from its stage,
-//                           the thread's share of the row's one or two sums, left in
-//                           shared memory; one arrival per warp on a CTA-local
+//                           the thread's share of the row's partial record -- up to 8
+//                           sums, maxima or whatever the workload's `combine` folds --
+//                           left in shared memory; one arrival per warp on a CTA-local
 //                           mbarrier), then pass 2 of row i - ahead (whose cluster-wide
-//                           sums were published long ago: read the slice again, write
+//                           record was published long ago: read the slice again, write
 //                           the outputs, free the stage);
-//   collector warp          per row: waits for the output threads' pairs, adds them up
-//                           and pushes the CTA's pair to every CTA of the cluster with
+//   collector warp          per row: waits for the output threads' records, folds them
+//                           and pushes the CTA's record to every CTA of the cluster with
 //                           st.async, which lands data and arrival on the receiver's
-//                           mbarrier;
-//   receiver warp           per row: waits for the P pairs of the cluster, adds them in
-//                           rank order (every CTA gets the same bits) and publishes the
-//                           row's two sums to the output warps behind one more mbarrier.
+//                           mbarrier; one of its lanes also loads the rows' scalars
+//                           (statistics, shifts) a few rows early and publishes them;
+//   receiver warp           per row: waits for the P records of the cluster, folds them
+//                           in a fixed order (every CTA gets the same bits) and publishes
+//                           the row's record to the output warps behind one more mbarrier.
 //
 // A row's slice is read from shared memory twice instead of being held in registers
 // across the exchange (for LayerNorm backward 3 x 32 KiB of shared-memory traffic per
@@ -58,22 +61,22 @@ constexpr int kWsServiceWarps = 3;   // producer, collector, receiver
 static_assert(kWsThreadsPerCta == (kWsMaxOutputWarps + kWsServiceWarps) * 32 &&
                   kWsThreadsPerCtaWide == (8 + kWsServiceWarps) * 32,
               "the host plans with these CTA sizes: output warps + service warps");
-constexpr int kWsLocalBuffers = 4;
 constexpr int kWsSlotBuffers = 8;
 
+// KP floats per partial record (2, 4 or 8), L CTA-local record buffers, THREADS output threads.
+template <int KP, int L, int THREADS>
 struct alignas(16) WsControl {
     uint64_t full[kMaxStages];                 // stage has landed (1 arrival + transaction bytes)
     uint64_t empty[kMaxStages];                // stage has been read twice by every output warp
-    uint64_t local_bar[kWsLocalBuffers];       // every output warp has left its pairs of a row
-    uint64_t ex_bar[kWsSlotBuffers];           // the P pairs of a row are in slot
-    uint64_t ready_bar[kWsSlotBuffers];        // the row's two sums are in total
+    uint64_t local_bar[4];                     // every output warp has left its records of a row
+    uint64_t ex_bar[kWsSlotBuffers];           // the P records of a row are in slot
+    uint64_t ready_bar[kWsSlotBuffers];        // the row's record is in total
     uint64_t info_bar[kWsSlotBuffers];         // the row's scalars are in row_info
     float4 row_info[kWsSlotBuffers];           // per-row scalars, published kWsInfoLead rows early
-    float2 total[kWsSlotBuffers];
-    float slot[kWsSlotBuffers][2 * kMaxClusterSize];   // [source rank][partial]
-    float2 thread_part[kWsLocalBuffers][kWsMaxOutputWarps * 32];   // [row % 4][output thread]
+    alignas(16) float total[kWsSlotBuffers][KP];
+    alignas(16) float slot[kWsSlotBuffers][kMaxClusterSize][KP];   // [row % 8][source rank]
+    alignas(16) float thread_part[L][THREADS][KP];                 // [row % L][output thread]
 };
-static_assert(sizeof(WsControl) <= kWsControlBytes, "control block overflows its reservation");
 
 // Rows between pass 1 and pass 2 of an output warp, from the ring depth the host chose.
 __device__ __forceinline__ int ws_rows_ahead(int stages) { return stages >= 5 ? 2 : 1; }
@@ -84,9 +87,45 @@ __device__ __forceinline__ int ws_rows_ahead(int stages) { return stages >= 5 ? 
 // microseconds for one stalls its whole row step. One lane of the collector warp loads them
 // kWsInfoLead + 1 rows ahead and publishes them in shared memory kWsInfoLead rows ahead.
 struct WsRow {
-    float a, b, c;
+    float a, b, c, d, e, f, g;
 };
 constexpr int kWsInfoLead = 3;   // > ahead: the output warps run at most `ahead` rows before the collector
+
+// A partial record of KP floats to / from shared memory with the widest accesses.
+template <int KP>
+__device__ __forceinline__ void ws_load_record(const float* p, float (&v)[KP]) {
+    if constexpr (KP == 2) {
+        const float2 t = *reinterpret_cast<const float2*>(p);
+        v[0] = t.x; v[1] = t.y;
+    } else {
+#pragma unroll
+        for (int k = 0; k < KP; k += 4) {
+            const float4 t = *reinterpret_cast<const float4*>(p + k);
+            v[k] = t.x; v[k + 1] = t.y; v[k + 2] = t.z; v[k + 3] = t.w;
+        }
+    }
+}
+template <int KP>
+__device__ __forceinline__ void ws_store_record(float* p, const float (&v)[KP]) {
+    if constexpr (KP == 2) {
+        *reinterpret_cast<float2*>(p) = make_float2(v[0], v[1]);
+    } else {
+#pragma unroll
+        for (int k = 0; k < KP; k += 4) *reinterpret_cast<float4*>(p + k) = make_float4(v[k], v[k + 1], v[k + 2], v[k + 3]);
+    }
+}
+// Pushes a record into the same place of CTA `peer`'s shared memory; every 8- or 16-byte message
+// credits the peer's mbarrier with its bytes.
+template <int KP>
+__device__ __forceinline__ void ws_send_record(uint32_t local_addr, uint32_t peer, const float (&v)[KP], uint32_t local_bar) {
+    const uint32_t dst = map_to_rank(local_addr, peer), bar = map_to_rank(local_bar, peer);
+    if constexpr (KP == 2) {
+        st_async_f32x2(dst, v[0], v[1], bar);
+    } else {
+#pragma unroll
+        for (int k = 0; k < KP; k += 4) st_async_f32x4(dst + 4 * k, v[k], v[k + 1], v[k + 2], v[k + 3], bar);
+    }
+}
 
 // ---------------------------------------------------------------------------
 // the pipeline
@@ -104,9 +143,14 @@ ws_row_kernel(NormParams prm, StagedArgs a) {
     constexpr int VPT = Op::kVectors;
     constexpr bool FULL = Op::kFull;
     constexpr int E = PairVec<T>::kElems;
+    constexpr int KP = Op::kPartials;          // floats per partial record
+    constexpr int L = Op::kLocalBuffers;       // CTA-local record buffers (a power of two)
+    using Control = WsControl<KP, L, THREADS>;
+    static_assert(sizeof(Control) <= kWsControlBytes, "control block overflows its reservation");
+    static_assert(KP == 2 || KP == 4 || KP == 8, "records travel as 8- or 16-byte messages");
 
     extern __shared__ __align__(1024) unsigned char smem[];
-    auto& ctl = *reinterpret_cast<WsControl*>(smem);
+    auto& ctl = *reinterpret_cast<Control*>(smem);
     unsigned char* data = smem + kWsControlBytes;
 
     const uint32_t rank = cluster_cta_rank();
@@ -116,8 +160,8 @@ ws_row_kernel(NormParams prm, StagedArgs a) {
     const int nvec = g.local / E;
     const int my_rows = cluster < a.rows ? (a.rows - cluster + a.num_clusters - 1) / a.num_clusters : 0;
     const int stages = a.stages;
-    const int ahead = ws_rows_ahead(stages);
-    if ((FULL ? nvec != VPT * THREADS : nvec > VPT * THREADS) && threadIdx.x == 0)
+    const int ahead = min(ws_rows_ahead(stages), L - 1);
+    if (Op::kRegisterSlice && (FULL ? nvec != VPT * THREADS : nvec > VPT * THREADS) && threadIdx.x == 0)
         atomicOr(a.status, kStatusBadGeometry);
 
     if (threadIdx.x == 0) {
@@ -125,7 +169,7 @@ ws_row_kernel(NormParams prm, StagedArgs a) {
             mbar_init(smem_u32(&ctl.full[s]), 1);
             mbar_init(smem_u32(&ctl.empty[s]), OUT_WARPS);
         }
-        for (int b = 0; b < kWsLocalBuffers; ++b) mbar_init(smem_u32(&ctl.local_bar[b]), OUT_WARPS);
+        for (int b = 0; b < L; ++b) mbar_init(smem_u32(&ctl.local_bar[b]), OUT_WARPS);
         for (int b = 0; b < kWsSlotBuffers; ++b) {
             mbar_init(smem_u32(&ctl.ex_bar[b]), 1);
             mbar_init(smem_u32(&ctl.ready_bar[b]), 1);
@@ -167,7 +211,7 @@ ws_row_kernel(NormParams prm, StagedArgs a) {
             ctl.row_info[ib] = Op::publish_row(info);
             mbar_arrive(smem_u32(&ctl.info_bar[ib]));   // release
         };
-        WsRow next_info{0.0f, 0.0f, 0.0f};
+        WsRow next_info{};
         if (Op::kRowInfo && lane == 0) {
             for (int r = 0; r < kWsInfoLead && r < my_rows; ++r)
                 publish(r, Op::fetch_row(prm, cluster + r * a.num_clusters, a.cols));
@@ -182,44 +226,75 @@ ws_row_kernel(NormParams prm, StagedArgs a) {
                 if (it + kWsInfoLead + 1 < my_rows)
                     next_info = Op::fetch_row(prm, cluster + (it + kWsInfoLead + 1) * a.num_clusters, a.cols);
             }
-            const int lb = it & (kWsLocalBuffers - 1);
+            const int lb = it & (L - 1);
             const int xb = it & (kWsSlotBuffers - 1);
-            mbar_wait_parked_bounded(smem_u32(&ctl.local_bar[lb]), (static_cast<uint32_t>(it) / kWsLocalBuffers) & 1u, a.status);
+            mbar_wait_parked_bounded(smem_u32(&ctl.local_bar[lb]), (static_cast<uint32_t>(it) / L) & 1u, a.status);
             const uint32_t bar = smem_u32(&ctl.ex_bar[xb]);
-            if (lane == 0) mbar_arrive_expect_tx(bar, nranks * 2u * static_cast<uint32_t>(sizeof(float)));
-            const float4* parts = reinterpret_cast<const float4*>(&ctl.thread_part[lb][0]);   // two pairs each
-            float2 acc0 = splat(0.0f), acc1 = splat(0.0f);
+            if (lane == 0) mbar_arrive_expect_tx(bar, nranks * static_cast<uint32_t>(KP * sizeof(float)));
+            float rec[KP];
+            if constexpr (KP == 2 && Op::kAdditive) {
+                const float4* parts = reinterpret_cast<const float4*>(&ctl.thread_part[lb][0][0]);   // two records each
+                float2 acc0 = splat(0.0f), acc1 = splat(0.0f);
 #pragma unroll
-            for (int k = 0; k < THREADS / 64; ++k) {
-                const float4 v = parts[lane + 32 * k];
-                acc0 = __fadd2_rn(acc0, make_float2(v.x, v.y));
-                acc1 = __fadd2_rn(acc1, make_float2(v.z, v.w));
+                for (int k = 0; k < THREADS / 64; ++k) {
+                    const float4 v = parts[lane + 32 * k];
+                    acc0 = __fadd2_rn(acc0, make_float2(v.x, v.y));
+                    acc1 = __fadd2_rn(acc1, make_float2(v.z, v.w));
+                }
+                const float2 mine = __fadd2_rn(acc0, acc1);
+                // both sums over the warp in one tree (warp_sum_split): the first ends in lanes 0..15,
+                // the second in lanes 16..31
+                const float t = warp_sum_split(mine.x, mine.y);
+                rec[0] = __shfl_sync(0xffffffffu, t, 0);
+                rec[1] = __shfl_sync(0xffffffffu, t, 16);
+            } else {
+                Op::identity(rec);
+#pragma unroll
+                for (int k = 0; k < THREADS / 32; ++k) {
+                    float v[KP];
+                    ws_load_record<KP>(&ctl.thread_part[lb][lane + 32 * k][0], v);
+                    Op::combine(rec, v);
+                }
+#pragma unroll
+                for (int offset = 16; offset > 0; offset >>= 1) {
+                    float o[KP];
+#pragma unroll
+                    for (int k = 0; k < KP; ++k) o[k] = __shfl_xor_sync(0xffffffffu, rec[k], offset);
+                    Op::combine(rec, o);
+                }
             }
-            const float2 mine = __fadd2_rn(acc0, acc1);
-            // both sums over the warp in one tree (warp_sum_split): the first ends in lanes 0..15, the
-            // second in lanes 16..31
-            const float t = warp_sum_split(mine.x, mine.y);
-            const float t0 = __shfl_sync(0xffffffffu, t, 0);
-            const float t1 = __shfl_sync(0xffffffffu, t, 16);
-            if (lane < nranks)
-                st_async_f32x2(map_to_rank(smem_u32(&ctl.slot[xb][2 * rank]), lane), t0, t1, map_to_rank(bar, lane));
+            if (lane < nranks) ws_send_record<KP>(smem_u32(&ctl.slot[xb][rank][0]), lane, rec, bar);
         }
         return;
     }
 
     // ---- receiver: the cluster's P pairs of a row -> the row's two sums, published to the output warps
     if (warp == OUT_WARPS + 2) {
-        const uint32_t half = lane >> 4, idx = lane & 15;
         for (int it = 0; it < my_rows; ++it) {
             const int xb = it & (kWsSlotBuffers - 1);
             mbar_wait_parked_bounded(smem_u32(&ctl.ex_bar[xb]), (static_cast<uint32_t>(it) / kWsSlotBuffers) & 1u, a.status);
-            float t = idx < nranks ? ctl.slot[xb][2 * idx + half] : 0.0f;
+            float rec[KP];
+            if constexpr (KP == 2 && Op::kAdditive) {
+                const uint32_t half = lane >> 4, idx = lane & 15;
+                float t = idx < nranks ? ctl.slot[xb][idx][half] : 0.0f;
 #pragma unroll
-            for (int offset = 8; offset > 0; offset >>= 1) t += __shfl_xor_sync(0xffffffffu, t, offset);
-            const float second = __shfl_sync(0xffffffffu, t, 16);
+                for (int offset = 8; offset > 0; offset >>= 1) t += __shfl_xor_sync(0xffffffffu, t, offset);
+                rec[0] = t;
+                rec[1] = __shfl_sync(0xffffffffu, t, 16);
+            } else {
+                Op::identity(rec);
+                if (lane < nranks) ws_load_record<KP>(&ctl.slot[xb][lane][0], rec);
+#pragma unroll
+                for (int offset = 8; offset > 0; offset >>= 1) {   // ranks sit in lanes 0..15
+                    float o[KP];
+#pragma unroll
+                    for (int k = 0; k < KP; ++k) o[k] = __shfl_xor_sync(0xffffffffu, rec[k], offset);
+                    Op::combine(rec, o);
+                }
+            }
             if (lane == 0) {
-                ctl.total[xb] = make_float2(t, second);
-                mbar_arrive(smem_u32(&ctl.ready_bar[xb]));   // release: the pair is visible to whoever sees the phase
+                ws_store_record<KP>(&ctl.total[xb][0], rec);
+                mbar_arrive(smem_u32(&ctl.ready_bar[xb]));   // release: the record is visible to whoever sees the phase
             }
         }
         return;
@@ -241,14 +316,16 @@ ws_row_kernel(NormParams prm, StagedArgs a) {
 #pragma unroll
             for (int n = 0; n < NIN; ++n)
                 tiles[n] = reinterpret_cast<const uint4*>(stage_tile<T, NIN>(data, stage1, n, a.slice_elems));
-            const int lb = it & (kWsLocalBuffers - 1);
+            const int lb = it & (L - 1);
             float4 info = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
             if (Op::kRowInfo) {
                 const int ib = it & (kWsSlotBuffers - 1);
                 mbar_wait_bounded(smem_u32(&ctl.info_bar[ib]), (static_cast<uint32_t>(it) / kWsSlotBuffers) & 1u, a.status);
                 info = ctl.row_info[ib];
             }
-            ctl.thread_part[lb][threadIdx.x] = Op::pass1(st, tiles, nvec, info);
+            float part[KP];
+            Op::pass1(st, tiles, nvec, info, part);
+            ws_store_record<KP>(&ctl.thread_part[lb][threadIdx.x][0], part);
             __syncwarp();   // the other lanes' stores are ordered before lane 0's release
             if (lane == 0) mbar_arrive(smem_u32(&ctl.local_bar[lb]));
             if (++stage1 == stages) {
@@ -263,7 +340,8 @@ ws_row_kernel(NormParams prm, StagedArgs a) {
             const int row = cluster + it2 * a.num_clusters;
             const int xb = it2 & (kWsSlotBuffers - 1);
             mbar_wait_bounded(smem_u32(&ctl.ready_bar[xb]), (static_cast<uint32_t>(it2) / kWsSlotBuffers) & 1u, a.status);
-            const float2 sums = ctl.total[xb];
+            float sums[KP];
+            ws_load_record<KP>(&ctl.total[xb][0], sums);
             // the row's scalars were published before its pass 1, which this warp has run
             const float4 info = Op::kRowInfo ? ctl.row_info[xb] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
             const uint4* tiles[NIN];
@@ -290,6 +368,11 @@ struct RmsNormFwdOp {
     static constexpr int kInputs = 1, kOutWarps = OUT_WARPS, kVectors = VPT, THREADS = OUT_WARPS * 32;
     static constexpr bool kFull = FULL;
     static constexpr int E = PairVec<T>::kElems, PAIRS = PairVec<T>::kPairs;
+    // a record of two sums; the thread owns fixed vectors of the slice (register-resident parameters)
+    static constexpr int kPartials = 2, kLocalBuffers = 4;
+    static constexpr bool kAdditive = true, kRegisterSlice = true;
+    __device__ __forceinline__ static void identity(float (&v)[2]) { v[0] = v[1] = 0.0f; }
+    __device__ __forceinline__ static void combine(float (&v)[2], const float (&o)[2]) { v[0] += o[0]; v[1] += o[1]; }
     struct State {
         float2 gam[VPT][PAIRS];
     };
@@ -308,7 +391,8 @@ struct RmsNormFwdOp {
             if (FULL || v < nvec) load_param_pairs<PAIRS>(p.gamma + col0 + v * E, st.gam[i]);
         }
     }
-    __device__ __forceinline__ static float2 pass1(State&, const uint4* const (&tiles)[1], int nvec, const float4&) {
+    __device__ __forceinline__ static void pass1(State&, const uint4* const (&tiles)[1], int nvec, const float4&,
+                                                 float (&part)[2]) {
         float2 q[2] = {splat(0.0f), splat(0.0f)};
 #pragma unroll
         for (int i = 0; i < VPT; ++i) {
@@ -321,11 +405,13 @@ struct RmsNormFwdOp {
             }
         }
         const float2 t = __fadd2_rn(q[0], q[1]);
-        return make_float2(t.x + t.y, 0.0f);
+        part[0] = t.x + t.y;
+        part[1] = 0.0f;
     }
     __device__ __forceinline__ static void pass2(State& st, const uint4* const (&tiles)[1], int nvec, const float4&,
-                                                 float2 sums, const NormParams& p, int row, int cols, int col0, uint32_t) {
-        const float2 scale = splat(rsqrtf(sums.x * (1.0f / static_cast<float>(cols)) + p.eps));
+                                                 const float (&sums)[2], const NormParams& p, int row, int cols, int col0,
+                                                 uint32_t) {
+        const float2 scale = splat(rsqrtf(sums[0] * (1.0f / static_cast<float>(cols)) + p.eps));
         uint4* out = reinterpret_cast<uint4*>(static_cast<T*>(p.y) + static_cast<size_t>(row) * cols + col0);
 #pragma unroll
         for (int i = 0; i < VPT; ++i) {
@@ -353,6 +439,11 @@ struct LayerNormFwdOp {
     static constexpr int kInputs = 1, kOutWarps = OUT_WARPS, kVectors = VPT, THREADS = OUT_WARPS * 32;
     static constexpr bool kFull = FULL;
     static constexpr int E = PairVec<T>::kElems, PAIRS = PairVec<T>::kPairs;
+    // a record of two sums; the thread owns fixed vectors of the slice (register-resident parameters)
+    static constexpr int kPartials = 2, kLocalBuffers = 4;
+    static constexpr bool kAdditive = true, kRegisterSlice = true;
+    __device__ __forceinline__ static void identity(float (&v)[2]) { v[0] = v[1] = 0.0f; }
+    __device__ __forceinline__ static void combine(float (&v)[2], const float (&o)[2]) { v[0] += o[0]; v[1] += o[1]; }
     struct State {
         float2 gam[VPT][PAIRS], bet[VPT][PAIRS];
     };
@@ -384,7 +475,8 @@ struct LayerNormFwdOp {
             }
         }
     }
-    __device__ __forceinline__ static float2 pass1(State&, const uint4* const (&tiles)[1], int nvec, const float4& r) {
+    __device__ __forceinline__ static void pass1(State&, const uint4* const (&tiles)[1], int nvec, const float4& r,
+                                                 float (&part)[2]) {
         const float2 neg_shift = splat(-r.x);
         float2 s[2] = {splat(0.0f), splat(0.0f)}, q[2] = {splat(0.0f), splat(0.0f)};
 #pragma unroll
@@ -402,13 +494,14 @@ struct LayerNormFwdOp {
             }
         }
         const float2 st = __fadd2_rn(s[0], s[1]), qt = __fadd2_rn(q[0], q[1]);
-        return make_float2(st.x + st.y, qt.x + qt.y);
+        part[0] = st.x + st.y;
+        part[1] = qt.x + qt.y;
     }
     __device__ __forceinline__ static void pass2(State& st, const uint4* const (&tiles)[1], int nvec, const float4& r,
-                                                 float2 sums, const NormParams& p, int row, int cols, int col0,
+                                                 const float (&sums)[2], const NormParams& p, int row, int cols, int col0,
                                                  uint32_t rank) {
         float mean, var;
-        moments_from_shifted(sums.x, sums.y, r.x, cols, mean, var);
+        moments_from_shifted(sums[0], sums[1], r.x, cols, mean, var);
         const float rstd = rsqrtf(var + p.eps);
         if (rank == 0 && threadIdx.x == 0) {
             p.mean_out[row] = mean;
@@ -451,6 +544,11 @@ struct LayerNormBwdOp {
     static constexpr int kInputs = 2, kOutWarps = OUT_WARPS, kVectors = VPT, THREADS = OUT_WARPS * 32;
     static constexpr bool kFull = FULL;
     static constexpr int E = PairVec<T>::kElems, PAIRS = PairVec<T>::kPairs;
+    // a record of two sums; the thread owns fixed vectors of the slice (register-resident parameters)
+    static constexpr int kPartials = 2, kLocalBuffers = 4;
+    static constexpr bool kAdditive = true, kRegisterSlice = true;
+    __device__ __forceinline__ static void identity(float (&v)[2]) { v[0] = v[1] = 0.0f; }
+    __device__ __forceinline__ static void combine(float (&v)[2], const float (&o)[2]) { v[0] += o[0]; v[1] += o[1]; }
     struct State {
         float2 gam[VPT][PAIRS], dgam[VPT][PAIRS], dbet[VPT][PAIRS];
     };
@@ -477,7 +575,8 @@ struct LayerNormBwdOp {
         }
     }
     // this thread's share of S1 = sum g and S2 = sum g * (x - mean)
-    __device__ __forceinline__ static float2 pass1(State& st, const uint4* const (&tiles)[2], int nvec, const float4& r) {
+    __device__ __forceinline__ static void pass1(State& st, const uint4* const (&tiles)[2], int nvec, const float4& r,
+                                                 float (&part)[2]) {
         const float mean = r.x;
         const float2 neg_mean = splat(-mean);
         float2 s1[2] = {splat(0.0f), splat(0.0f)}, s2[2] = {splat(0.0f), splat(0.0f)};   // two chains each
@@ -500,20 +599,22 @@ struct LayerNormBwdOp {
         }
         const float2 s1t = __fadd2_rn(s1[0], s1[1]), s2t = __fadd2_rn(s2[0], s2[1]);
         const float t1 = s1t.x + s1t.y, t2 = s2t.x + s2t.y;
-        return make_float2(t1, sizeof(T) == 2 ? fmaf(-mean, t1, t2) : t2);
+        part[0] = t1;
+        part[1] = sizeof(T) == 2 ? fmaf(-mean, t1, t2) : t2;
     }
     __device__ __forceinline__ static void pass2(State& st, const uint4* const (&tiles)[2], int nvec, const float4& r,
-                                                 float2 sums, const NormParams& p, int row, int cols, int col0, uint32_t) {
+                                                 const float (&sums)[2], const NormParams& p, int row, int cols, int col0,
+                                                 uint32_t) {
         const float mean = r.x, rstd = r.y;
         const float inv_cols = 1.0f / static_cast<float>(cols);
         const float2 neg_mean = splat(-mean), rstd2 = splat(rstd);
-        const float2 ca = splat(-rstd * rstd * rstd * (sums.y * inv_cols));
-        const float2 cb = splat(-rstd * (sums.x * inv_cols));
+        const float2 ca = splat(-rstd * rstd * rstd * (sums[1] * inv_cols));
+        const float2 cb = splat(-rstd * (sums[0] * inv_cols));
         // 16-bit rows work on xhat = x * rstd - mean * rstd (one fused operation; the rounding of
         // the constant is far below the output's 2^-9): dx = xhat * ca_hat + g * rstd + cb and
         // dgamma += dy * xhat, one operation less per pair than the (x - mean) form fp32 rows keep.
         const float2 shift2 = splat(-mean * rstd);
-        const float2 ca_hat = splat(-rstd * rstd * (sums.y * inv_cols));
+        const float2 ca_hat = splat(-rstd * rstd * (sums[1] * inv_cols));
         uint4* out = reinterpret_cast<uint4*>(static_cast<T*>(p.y) + static_cast<size_t>(row) * cols + col0);
 #pragma unroll
         for (int i = 0; i < VPT; ++i) {

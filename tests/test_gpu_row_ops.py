@@ -28,6 +28,9 @@ DEV = torch.device("cuda:0")
 GOLDEN = Path(__file__).resolve().parent / "golden" / "reference_workloads.npz"
 ROW_OPS = ["weighted_var_backward", "pearson_backward", "softmax_logits_backward", "lars_momentum",
            "rowwise_quant"]
+WORKLOAD_IDS = {"weighted_var_backward": N.WL_WEIGHTED_VAR_BACKWARD, "pearson_backward": N.WL_PEARSON_BACKWARD,
+                "softmax_logits_backward": N.WL_SOFTMAX_LOGITS_BACKWARD, "lars_momentum": N.WL_LARS_MOMENTUM,
+                "rowwise_quant": N.WL_ROWWISE_QUANT}
 
 
 def run(name, inputs, cluster_size=0, opts=None):
@@ -90,6 +93,63 @@ def test_golden_inputs_reproduce_reference_outputs(native_lib, name, cluster_siz
 def test_matches_oracle(native_lib, name, rows, cols, cluster_size):
     inputs = W.WORKLOADS[name].input_factory(rows, cols, "cpu", seed=rows + cols)
     compare(name, run(name, inputs, cluster_size), oracle64(name, inputs))
+
+
+@pytest.mark.parametrize("name", ROW_OPS)
+@pytest.mark.parametrize("threads", [256, 512])
+@pytest.mark.parametrize("rows,cols,cluster_size", [(64, 4096, 0), (33, 16384, 4), (9, 65536, 16), (300, 8192, 8)])
+def test_lock_step_kernels(native_lib, name, threads, rows, cols, cluster_size):
+    """threads = 256 / 512 keep the staged kernels that make one pass and one cluster barrier per
+    dependent reduction (the automatic choice for aligned rows is the warp-specialised pipeline)."""
+    inputs = W.WORKLOADS[name].input_factory(rows, cols, "cpu", seed=rows + cols)
+    opts = {"threads": threads}
+    compare(name, run(name, inputs, cluster_size, opts), oracle64(name, inputs))
+    assert N.plan(WORKLOAD_IDS[name], rows, cols, N.F32, dict(opts, cluster_size=cluster_size)).threads == threads
+
+
+@pytest.mark.parametrize("name", ROW_OPS)
+@pytest.mark.parametrize("cluster_size,stages", [(1, 0), (2, 3), (4, 4), (8, 0), (16, 5)])
+def test_warp_specialised_pipeline_many_rows(native_lib, name, cluster_size, stages):
+    """threads = 352 on aligned rows: 20+ rows per cluster, so the ring and every buffer of the
+    pipeline wrap; the second shape leaves CTAs with short and empty slices."""
+    opts = {"threads": 352, "stages": stages}
+    for rows, cols in ((3100, 2048), (2999, 1096)):
+        inputs = W.WORKLOADS[name].input_factory(rows, cols, "cpu", seed=rows)
+        compare(name, run(name, inputs, cluster_size, opts), oracle64(name, inputs))
+        assert N.plan(WORKLOAD_IDS[name], rows, cols, N.F32, dict(opts, cluster_size=cluster_size)).threads == 352
+
+
+def test_softmax_extreme_logits(native_lib):
+    """Online softmax: a row whose maximum arrives late, rows of equal logits, -inf entries and a
+    huge dynamic range give the same result as the three-pass formula."""
+    rows, cols = 6, 8192
+    torch.manual_seed(2)
+    logits = torch.randn(rows, cols) * 3.0
+    logits[0, cols - 1] = 80.0                    # the maximum is the last element
+    logits[1, :] = 1.5                            # all equal
+    logits[2, 100:200] = float("-inf")            # masked entries
+    logits[3, :] = torch.linspace(-200.0, 50.0, cols)
+    logits[4, 0] = 60.0                           # the maximum is the first element
+    dy = torch.randn(rows, cols)
+    want = O.softmax_logits_backward(logits.double(), dy.double()).float()
+    for p in (1, 4, 16):
+        (got,) = run("softmax_logits_backward", (logits, dy), p)
+        assert torch.allclose(got, want, atol=3e-6, rtol=3e-3), float((got - want).abs().max())
+
+
+@pytest.mark.parametrize("name", ["pearson_backward", "weighted_var_backward"])
+def test_shifted_moments_with_a_large_offset(native_lib, name):
+    """mean >> spread: the one-pass shifted moments keep the centred sums accurate."""
+    rows, cols = 5, 16384
+    inputs = list(W.WORKLOADS[name].input_factory(rows, cols, "cpu", seed=4))
+    inputs[0] = inputs[0] * 0.01 + 300.0
+    if name == "pearson_backward":
+        inputs[1] = inputs[1] * 0.01 - 120.0
+    want = oracle64(name, inputs)
+    got = run(name, inputs, 8)
+    for g, w in zip(got, want):
+        w = w.float()
+        assert torch.allclose(g, w, atol=3e-3 * float(w.abs().max()), rtol=3e-3), float((g - w).abs().max())
 
 
 @pytest.mark.parametrize("name", ROW_OPS)
