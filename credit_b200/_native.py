@@ -161,6 +161,10 @@ PROTOTYPES: dict[str, tuple] = {
     "credit_layernorm_backward_stats_host": (
         c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
                 c_int, _OPTS_P, c_void_p, c_size_t, c_void_p]),
+    "credit_comm_get_unique_id": (c_int, [c_void_p]),
+    "credit_comm_init_rank": (c_int, [POINTER(c_void_p), c_int, c_int, c_void_p]),
+    "credit_comm_destroy": (c_int, [c_void_p]),
+    "credit_layernorm_bwd_allreduce": (c_int, [c_void_p, c_void_p, c_int64, c_void_p]),
     "credit_ffn_forward_host_scratch_bytes": (c_size_t, [c_int64, c_int64, c_int64]),
     "credit_ffn_forward_host": (
         c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_float, c_void_p,

@@ -41,6 +41,7 @@ LIB_SOURCES = [
     "tables_ws_layernorm_fwd.cu",
     "tables_ws_layernorm_bwd.cu",
     "tables_ws_row_ops.cu",
+    "comm_entry.cu",
 ]
 OBJ_DIR = LIB_DIR / "obj"
 # name of the executable -> (source, links against the shared library)
@@ -98,7 +99,7 @@ def build_library(force: bool = False, verbose: bool = False, ptxas_log: Path | 
     with ThreadPoolExecutor(max_workers=min(len(LIB_SOURCES), os.cpu_count() or 1)) as pool:
         results = list(pool.map(lambda src: _compile_object(src, verbose), LIB_SOURCES))
     objects = [str(obj) for obj, _ in results]
-    _run([nvcc_path(), *ARCH_FLAGS, "-shared", "-o", str(LIB_PATH), *objects], verbose)
+    _run([nvcc_path(), *ARCH_FLAGS, "-shared", "-o", str(LIB_PATH), *objects, "-ldl"], verbose)
     if ptxas_log is not None:
         ptxas_log.write_text("\n".join(log for _, log in results))
     return LIB_PATH

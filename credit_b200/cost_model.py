@@ -133,6 +133,16 @@ class B200Calibration:
     cta_launch_ns: float = 4.8                 # streaming kernels: CTA launch throughput of the device
     launch_base_us: float = 3.0                # fixed cost of a launch
     streaming_ctas_to_saturate: int = 320      # CTAs of the streaming reduction that fill HBM
+    # warp-specialised pipeline (8 output warps): a row costs a cluster the larger of its CTAs'
+    # share of the HBM bandwidth and the output warps' issue time
+    ws_sm_gbps_cap: float = 58.0               # most one SM pulls through bulk copies (7.0 TB/s on 120 SMs)
+    ws_fixed_cycles: float = 400.0             # per row and CTA, whatever the slice length
+    ws_fixed_cycles_p16: float = 1100.0        # the same in clusters of 16
+    ws_cycles_per_element_fwd: float = 25.0    # per row element a thread owns, forward kernels
+    ws_cycles_per_element_bwd: float = 40.0    # LayerNorm backward with column sums
+    ws_cycles_per_element_per_array: float = 12.0   # reference-sweep workloads, per staged or written array
+    ws_short_ring_penalty: float = 1.12        # fewer than five stages: the passes run one row apart
+    ws_fill_rows: float = 3.0                  # ring fill, rows between the passes, the last cluster's extra row
 
     def exchange(self, cluster_size: int) -> float:
         table = self.exchange_cycles or {1: 150.0, 2: 315.0, 4: 322.0, 8: 351.0, 16: 420.0}
@@ -175,6 +185,35 @@ def predict_cluster_ms(rows: int, cols: int, cluster_size: int, resident_cluster
     k = cal.overlap_exponent
     predicted = (hbm_ms ** k + latency_ms ** k) ** (1.0 / k)
     return ClusterPrediction(cluster_size, hbm_ms, rows_per_cluster, row_period_us, predicted)
+
+
+def predict_ws_ms(rows: int, cols: int, cluster_size: int, resident_clusters: int, threads: int,
+                  elem_bytes: int, arrays_in: int, arrays_out: float, stages: int, backward: bool = False,
+                  row_op: bool = False, cal: B200Calibration = B200Calibration()) -> ClusterPrediction:
+    """Predicted time of one call of a warp-specialised kernel (threads 352 or 608 per CTA), the
+    formula of the library's planner (launch.cu: predicted_ws_ms): the SMs the co-resident clusters
+    cover share the copy ceiling, one SM pulls at most `ws_sm_gbps_cap`, and the output warps need
+    a fixed number of cycles per row plus a number per row element a thread owns.
+    arrays_in / arrays_out: arrays of the element type staged / written per row (0.25 for int8
+    output of fp32 input)."""
+    if min(rows, cols, cluster_size, resident_clusters, threads - 96) <= 0:
+        raise ValueError("all sizes must be positive")
+    slice_elems = -(-math.ceil(cols / cluster_size) // 64) * 64
+    bytes_per_cta_row = (arrays_in + arrays_out) * slice_elems * elem_bytes
+    sms = resident_clusters * cluster_size
+    per_sm_gbps = min(cal.hbm_gbps / sms, cal.ws_sm_gbps_cap)
+    hbm_us = bytes_per_cta_row / (per_sm_gbps * 1.0e3)
+    elems = math.ceil(slice_elems / (threads - 96))
+    per_elem = (cal.ws_cycles_per_element_bwd if backward else
+                cal.ws_cycles_per_element_per_array * (arrays_in + arrays_out) if row_op else
+                cal.ws_cycles_per_element_fwd)
+    fixed = cal.ws_fixed_cycles_p16 if cluster_size >= 16 else cal.ws_fixed_cycles
+    issue_us = (fixed + per_elem * elems) / (cal.clock_ghz * 1.0e3)
+    row_us = max(hbm_us, issue_us) * (cal.ws_short_ring_penalty if stages < 5 else 1.0)
+    rows_per_cluster = math.ceil(rows / resident_clusters)
+    predicted = row_us * (rows_per_cluster + cal.ws_fill_rows) * 1.0e-3
+    hbm_ms = (arrays_in + arrays_out) * rows * cols * elem_bytes / (cal.hbm_gbps * 1.0e6)
+    return ClusterPrediction(cluster_size, hbm_ms, rows_per_cluster, row_us, predicted)
 
 
 def predict_streaming_ms(rows: int, cluster_size: int, algorithmic_bytes: float,

@@ -12,6 +12,7 @@
 #include <cmath>
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <map>
 #include <mutex>
@@ -613,6 +614,17 @@ struct Resolved {
 // with resident(P) from the driver's occupancy query. Calibrated on B200 (copy ceiling
 // 6538.6 GB/s, 1.93 GHz under these kernels, exchange cycles from primitive_benchmark).
 // ---------------------------------------------------------------------------
+// The copy ceiling the planner's models divide by: 6538.6 GB/s was measured on B200; a host that
+// has measured its own device sets CREDIT_HBM_GBPS (read once).
+double calibrated_hbm_gbps() {
+    static const double value = [] {
+        const char* text = std::getenv("CREDIT_HBM_GBPS");
+        const double v = text != nullptr ? std::atof(text) : 0.0;
+        return v > 100.0 ? v : 6538.6;
+    }();
+    return value;
+}
+
 double compulsory_bytes(int workload, const Shape& s, bool grads) {
     const double rc = static_cast<double>(s.rows) * s.cols, e = s.elem_bytes;
     switch (workload) {
@@ -624,7 +636,7 @@ double compulsory_bytes(int workload, const Shape& s, bool grads) {
 }
 
 double predicted_ms(int workload, const Shape& s, const credit_plan_info& p, bool grads) {
-    const double hbm_ms = compulsory_bytes(workload, s, grads) / (6538.6 * 1.0e6);
+    const double hbm_ms = compulsory_bytes(workload, s, grads) / (calibrated_hbm_gbps() * 1.0e6);
     if (p.vectors_per_thread == 0) return hbm_ms / 0.5;   // shared-memory re-read kernels
     static const double kExchange[5] = {157.0, 315.0, 322.0, 351.0, 420.0};   // P = 1, 2, 4, 8, 16
     int log2p = 0;
@@ -652,7 +664,7 @@ double predicted_ws_ms(int workload, const Shape& s, const credit_plan_info& p, 
     if (workload == CREDIT_WL_ROWWISE_QUANT) nout = 0.25;
     const double bytes_per_cta_row = (nin + nout) * p.slice_elems * s.elem_bytes;
     const double sms = static_cast<double>(std::max(p.num_clusters, 1)) * p.cluster_size;
-    const double per_sm_gbps = std::min(6538.6 / sms, 58.0);
+    const double per_sm_gbps = std::min(calibrated_hbm_gbps() / sms, 58.0);
     const double hbm_us = bytes_per_cta_row / (per_sm_gbps * 1.0e3);
     const int out_threads = p.threads - 96;
     const double elems = std::ceil(static_cast<double>(p.slice_elems) / out_threads);

@@ -95,10 +95,25 @@ def make_device_profile(parsed: dict[str, Any], properties: Any) -> DeviceProfil
     )
 
 
+def measured_hbm_gbps(path: Any = None) -> float | None:
+    """The copy ceiling of this machine's GPU from a MEASURED_PEAKS.json (key hbm_gbs) at `path`
+    or at the repository root, if one exists."""
+    import json
+    from pathlib import Path
+    candidate = Path(path) if path is not None else Path(__file__).resolve().parents[1] / "MEASURED_PEAKS.json"
+    try:
+        return float(json.loads(candidate.read_text())["hbm_gbs"])
+    except Exception:
+        return None
+
+
 def make_b200_calibration(parsed: dict[str, Any], hbm_gbps: float | None = None,
                           clock_ghz: float | None = None) -> B200Calibration:
     """Calibration of the row-period model from a parsed benchmark: the exchange cost per
-    cluster size comes from the "mbarrier exchange" lines when they are present."""
+    cluster size comes from the "mbarrier exchange" lines when they are present; the copy ceiling
+    is the given one, else the machine's measured one (measured_hbm_gbps), else the default."""
+    if hbm_gbps is None:
+        hbm_gbps = measured_hbm_gbps()
     exchange = {p: v["mbarrier_exchange_cycles"] for p, v in parsed.get("per_cluster", {}).items()
                 if "mbarrier_exchange_cycles" in v}
     if exchange:

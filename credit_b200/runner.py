@@ -32,7 +32,7 @@ from .workloads import WORKLOADS
 PACKAGE_DIR = Path(__file__).resolve().parent
 BIN_DIR = PACKAGE_DIR / "bin"
 DEFAULT_N_VALUES = (4096, 8192, 16384, 32768, 65536)
-DEFAULT_CLUSTER_SIZES = (2, 4, 8, 16)
+DEFAULT_CLUSTER_SIZES = (2, 4, 8, 16)   # 1 is swept too when asked for: --cluster-sizes 1,2,4,8,16
 CLI_WORKLOADS = ("layernorm_backward", "rmsnorm_forward", "row_reduce", "layernorm_forward",
                  "layernorm_backward_stats", "weighted_var_backward", "pearson_backward",
                  "softmax_logits_backward", "lars_momentum", "rowwise_quant")
@@ -84,8 +84,8 @@ class RunConfig:
             problems.append("at least one workload is required")
         if not self.n_values or min(self.n_values) <= 0:
             problems.append("n_values must contain positive integers")
-        if not self.cluster_sizes or not set(self.cluster_sizes) <= {2, 4, 8, 16}:
-            problems.append("cluster_sizes must be selected from 2, 4, 8 and 16")
+        if not self.cluster_sizes or not set(self.cluster_sizes) <= {1, 2, 4, 8, 16}:
+            problems.append("cluster_sizes must be selected from 1, 2, 4, 8 and 16")
         if self.warmup <= 0 or self.iterations <= 0 or self.trials <= 0:
             problems.append("warmup, iterations, and trials must be positive")
         if self.rows < 0:
@@ -258,22 +258,41 @@ def run_control_trials(bin_dir: Path, rows: int, cluster_size: int, barriers: in
     return samples
 
 
-def resident_clusters(name: str, rows: int, cols: int, dtype: str, cluster_size: int) -> tuple[int, int, bool]:
-    """(co-resident clusters, threads per CTA, register path?) of the kernel a call would launch, from
-    the library's own planner (which asks the driver); (0, 0, False) if the shape does not fit this
-    cluster size."""
+# arrays of the element type a workload stages / writes per row (int8 output of fp32 input: 0.25)
+_ARRAYS = {"rmsnorm_forward": (1, 1.0), "row_reduce": (1, 0.0), "layernorm_forward": (1, 1.0),
+           "layernorm_backward": (2, 1.0), "layernorm_backward_stats": (2, 1.0), "weighted_var_backward": (3, 1.0),
+           "pearson_backward": (2, 2.0), "softmax_logits_backward": (2, 1.0), "lars_momentum": (3, 2.0),
+           "rowwise_quant": (1, 0.25)}
+_ROW_OPS = ("weighted_var_backward", "pearson_backward", "softmax_logits_backward", "lars_momentum", "rowwise_quant")
+WS_THREADS = (352, 608)   # CTA sizes of the warp-specialised kernels
+
+
+def resident_clusters(name: str, rows: int, cols: int, dtype: str, cluster_size: int) -> tuple[int, int, bool, int]:
+    """(co-resident clusters, threads per CTA, register path?, ring stages) of the kernel the
+    executable's cluster variant launches at this cluster size, from the library's own planner
+    (which asks the driver); (0, 0, False, 0) if the shape does not fit this cluster size."""
     from . import _native as N
     try:
         plan = N.plan(_WORKLOAD_IDS[name], rows, cols, N.BF16 if dtype == "bf16" else N.F32,
-                      {"cluster_size": cluster_size, "schedule": N.SCHEDULE_PERSISTENT})
+                      {"cluster_size": cluster_size, "variant": N.VARIANT_CLUSTER_SMEM if cluster_size > 1 else 0})
     except N.CreditError:
-        return 0, 0, False
-    return plan.num_clusters, plan.threads, plan.vectors_per_thread > 0
+        return 0, 0, False, 0
+    return plan.num_clusters, plan.threads, plan.vectors_per_thread > 0, plan.stages
+
+
+def library_cluster_size(name: str, rows: int, cols: int, dtype: str) -> int:
+    """The cluster size the library picks by itself (cluster_size = 0); 0 if it cannot plan the shape."""
+    from . import _native as N
+    try:
+        return N.plan(_WORKLOAD_IDS[name], rows, cols, N.BF16 if dtype == "bf16" else N.F32).cluster_size
+    except N.CreditError:
+        return 0
 
 
 def build_summary(config: RunConfig, profile: cost_model.DeviceProfile, calibration: cost_model.B200Calibration,
                   raw_cuda: list[dict[str, Any]], control_samples: dict[tuple[str, int, int], list[float]],
-                  residency: dict[tuple[str, int, int], tuple]):
+                  residency: dict[tuple[str, int, int], tuple], auto_choice: dict[tuple[str, int], int] | None = None):
+    auto_choice = auto_choice or {}
     groups: dict[tuple[str, int, str, int], list[float]] = defaultdict(list)
     block_names: dict[tuple[str, int], set[str]] = defaultdict(set)
     shape_rows: dict[tuple[str, int], int] = {}
@@ -323,10 +342,15 @@ def build_summary(config: RunConfig, profile: cost_model.DeviceProfile, calibrat
                                 "local_store_residual_ms": est.local_store_residual_ms,
                                 "dsmem_store_ms": est.dsmem_store_ms, "predicted_delta_ms": est.predicted_delta_ms,
                                 "predicted_profitable": est.predicted_profitable})
-                resident, threads, register_path = (*residency.get((name, cols, p), (0, 0)), True)[:3]
+                resident, threads, register_path, stages = (*residency.get((name, cols, p), (0, 0)), True, 3)[:4]
                 pred = None
                 if not spec.staged_bytes_per_element:       # streaming reduction: nothing staged
                     pred = cost_model.predict_streaming_ms(rows, p, alg_bytes, calibration)
+                elif resident > 0 and threads in WS_THREADS:
+                    arrays_in, arrays_out = _ARRAYS[name]
+                    pred = cost_model.predict_ws_ms(rows, cols, p, resident, threads, elem, arrays_in, arrays_out,
+                                                    stages, backward=name == "layernorm_backward_stats",
+                                                    row_op=name in _ROW_OPS, cal=calibration)
                 elif resident > 0:
                     pred = cost_model.predict_cluster_ms(rows, cols, p, resident, threads, alg_bytes,
                                                          len(spec.reductions_per_stage), True, calibration,
@@ -343,6 +367,8 @@ def build_summary(config: RunConfig, profile: cost_model.DeviceProfile, calibrat
             ref_delta, ref_p, ref_est = max(ref_candidates, default=(math.nan, 0, None), key=lambda t: t[0])
             b200_p = cost_model.best_cluster_size(b200_predictions) if b200_predictions else 0
             at_predicted = next((ms for ms, p in measured if p == b200_p), math.nan)
+            lib_p = int(auto_choice.get((name, cols), 0))
+            at_library = next((ms for ms, p in measured if p == lib_p), math.nan)
             profitable = best_ms < block["median"] if math.isfinite(block["median"]) else True
             summary_rows.append({
                 "workload": name, "label": spec.label, "category": spec.category, "rows": rows, "cols": cols,
@@ -366,6 +392,11 @@ def build_summary(config: RunConfig, profile: cost_model.DeviceProfile, calibrat
                 # neighbouring sizes is a few per cent)
                 "b200_model_within_5pct": bool(math.isfinite(at_predicted) and at_predicted <= 1.05 * best_ms),
                 "measured_ms_at_b200_predicted": at_predicted,
+                # what cluster_size = 0 launches (the planner inside the library), scored among the swept sizes
+                "library_cluster_size": lib_p,
+                "library_picks_measured_best": lib_p == best_p,
+                "library_within_5pct": bool(math.isfinite(at_library) and at_library <= 1.05 * best_ms),
+                "measured_ms_at_library_choice": at_library,
             })
     return summary_rows, cluster_rows
 
@@ -399,7 +430,8 @@ def run_suite(raw_config: dict[str, Any], output_dir: Path, requested_gpu: str =
     raw_cuda: list[dict[str, Any]] = []
     control_rows: list[dict[str, Any]] = []
     control_samples: dict[tuple[str, int, int], list[float]] = {}
-    residency: dict[tuple[str, int, int], tuple[int, int]] = {}
+    residency: dict[tuple[str, int, int], tuple] = {}
+    auto_choice: dict[tuple[str, int], int] = {}
     for name in config.workloads:
         spec = WORKLOADS[name]
         for p in config.cluster_sizes:
@@ -420,11 +452,14 @@ def run_suite(raw_config: dict[str, Any], output_dir: Path, requested_gpu: str =
                 control_rows.extend({"workload": name, "cols": cols, "cluster_size": p, "delta_ms": s}
                                     for s in samples)
                 residency[(name, cols, p)] = resident_clusters(name, rows, cols, dtype, p)
+                auto_choice[(name, cols)] = library_cluster_size(name, rows, cols, dtype)
     write_csv(output_dir / "control_raw.csv", control_rows)
     write_csv(output_dir / "plans.csv", [
         {"workload": k[0], "cols": k[1], "cluster_size": k[2], "resident_clusters": v[0], "threads": v[1],
-         "register_path": int(v[2])} for k, v in residency.items()])
-    summary_rows, cluster_rows = build_summary(config, profile, calibration, raw_cuda, control_samples, residency)
+         "register_path": int(v[2]), "stages": v[3], "library_cluster_size": auto_choice.get((k[0], k[1]), 0)}
+        for k, v in residency.items()])
+    summary_rows, cluster_rows = build_summary(config, profile, calibration, raw_cuda, control_samples, residency,
+                                               auto_choice)
     write_csv(output_dir / "summary.csv", summary_rows)
     write_csv(output_dir / "cluster_sweep.csv", cluster_rows)
     (output_dir / "metadata.json").write_text(json.dumps(metadata, indent=2))
@@ -432,7 +467,9 @@ def run_suite(raw_config: dict[str, Any], output_dir: Path, requested_gpu: str =
     hits = sum(1 for r in summary_rows if r["b200_model_picks_measured_best"])
     near = sum(1 for r in summary_rows if r["b200_model_within_5pct"])
     metadata.update({"status": "complete", "finished": time.time(), "points": len(summary_rows),
-                     "b200_model_hits": hits, "b200_model_within_5pct": near})
+                     "b200_model_hits": hits, "b200_model_within_5pct": near,
+                     "library_hits": sum(1 for r in summary_rows if r["library_picks_measured_best"]),
+                     "library_within_5pct": sum(1 for r in summary_rows if r["library_within_5pct"])})
     (output_dir / "metadata.json").write_text(json.dumps(metadata, indent=2))
     return metadata
 
@@ -463,12 +500,13 @@ def rescore_bundle(bundle_dir: Path) -> dict[str, Any]:
     with (bundle_dir / "control_raw.csv").open(newline="") as f:
         for r in csv.DictReader(f):
             control[(r["workload"], int(r["cols"]), int(r["cluster_size"]))].append(float(r["delta_ms"]))
-    residency = {}
+    residency, auto_choice = {}, {}
     with (bundle_dir / "plans.csv").open(newline="") as f:
         for r in csv.DictReader(f):
             residency[(r["workload"], int(r["cols"]), int(r["cluster_size"]))] = (
-                int(r["resident_clusters"]), int(r["threads"]), bool(int(r["register_path"])))
-    summary_rows, cluster_rows = build_summary(config, profile, calibration, raw_cuda, control, residency)
+                int(r["resident_clusters"]), int(r["threads"]), bool(int(r["register_path"])), int(r.get("stages") or 3))
+            auto_choice[(r["workload"], int(r["cols"]))] = int(r.get("library_cluster_size") or 0)
+    summary_rows, cluster_rows = build_summary(config, profile, calibration, raw_cuda, control, residency, auto_choice)
     write_csv(bundle_dir / "summary.csv", summary_rows)
     write_csv(bundle_dir / "cluster_sweep.csv", cluster_rows)
     write_report(bundle_dir)

@@ -333,6 +333,31 @@ int credit_ffn_forward_host(const void* x_host, const void* w1_packed, const voi
                             const float* gamma, void* y_host, int64_t m, int64_t d, int64_t h, float eps,
                             void* scratch, size_t scratch_bytes, void* stream);
 
+/* Multi-GPU: rows sharded over the GPUs of a node ---------------------------- */
+
+/* Rows are independent in every workload, so a matrix is split into contiguous row
+ * blocks, one per GPU (one process per GPU), parameters are replicated and outputs
+ * stay sharded. The single quantity that spans the shards is LayerNorm backward's
+ * dgamma / dbeta (column sums over ALL rows): each rank calls
+ * credit_layernorm_backward_stats with dgamma = buf and dbeta = buf + cols of one
+ * [2, cols] fp32 device buffer, then credit_layernorm_bwd_allreduce(comm, buf, cols,
+ * stream) sums that buffer over the ranks, in place, on the same stream (NCCL over
+ * NVLink; no host synchronisation in between). The reference is single-device
+ * (device 0 is hard-coded, src/workloads/layernorm_backward.cu:443); these entry
+ * points have no counterpart there.
+ *
+ * Set-up: rank 0 obtains an id (CREDIT_COMM_ID_BYTES bytes) and hands it to the other
+ * ranks by whatever channel the host has; every rank then calls credit_comm_init_rank
+ * with its own device current (collective: returns when all ranks have called it).
+ * NCCL is loaded at run time (libnccl.so.2); where it is absent these calls return
+ * CREDIT_ERR_UNSUPPORTED and the rest of the library is unaffected. */
+#define CREDIT_COMM_ID_BYTES 128
+typedef struct credit_comm credit_comm;
+int credit_comm_get_unique_id(void* id_out);
+int credit_comm_init_rank(credit_comm** comm, int world_size, int rank, const void* id);
+int credit_comm_destroy(credit_comm* comm);
+int credit_layernorm_bwd_allreduce(credit_comm* comm, float* dgamma_dbeta, int64_t cols, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -61,3 +61,93 @@ def test_sharded_layernorm_backward_allreduces_parameter_gradients(native_lib):
         out = manager.dict()
         mp.spawn(_worker, args=(world, port, rows, cols, out), nprocs=world, join=True)
         assert dict(out) == {0: True, 1: True}
+
+
+def _abi_worker(rank: int, world: int, id_path: str, rows: int, cols: int, out):
+    """The same sharded call with the collective of the C ABI (credit_comm_*,
+    credit_layernorm_bwd_allreduce) instead of torch.distributed: the id travels through a file."""
+    import ctypes
+    import time
+    from pathlib import Path
+
+    from credit_b200 import _native as N
+    from credit_b200 import launchers as L
+    from credit_b200 import sharding
+    from credit_b200 import workloads as W
+    from oracle import reference_ops as O
+
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    lib = N.load()
+    ident = ctypes.create_string_buffer(128)
+    path = Path(id_path)
+    if rank == 0:
+        N.check(lib.credit_comm_get_unique_id(ident))
+        tmp = path.with_suffix(".tmp")
+        tmp.write_bytes(ident.raw)
+        tmp.rename(path)
+    else:
+        deadline = time.time() + 60
+        while not path.exists():
+            if time.time() > deadline:
+                raise RuntimeError("rank 0 never published the id")
+            time.sleep(0.05)
+        ident = ctypes.create_string_buffer(path.read_bytes(), 128)
+    comm = ctypes.c_void_p()
+    N.check(lib.credit_comm_init_rank(ctypes.byref(comm), world, rank, ident))
+    try:
+        full = W.make_layernorm_backward_stats_inputs(rows, cols, "cpu", seed=9)
+        x, dy, gamma, mean, rstd = full
+        r0, r1 = sharding.shard_rows(rows, world, rank)
+        local = (x[r0:r1].to(dev), dy[r0:r1].to(dev), gamma.to(dev), mean[r0:r1].to(dev), rstd[r0:r1].to(dev))
+        dx = torch.empty_like(local[0])
+        both, dgamma, dbeta = sharding.allocate_param_grads(cols, dev)
+        stream = torch.cuda.current_stream().cuda_stream
+        L.launch_layernorm_backward_stats(local, (dx, dgamma, dbeta))
+        N.check(lib.credit_layernorm_bwd_allreduce(comm, both.data_ptr(), cols, stream))
+        torch.cuda.synchronize()
+        want_dx, want_dg, want_db = O.layernorm_backward_stats(*full, dtype=torch.float64)
+
+        def close(got, want, rtol, scale):
+            err = (got.double().cpu() - want).abs()
+            return bool((err <= rtol * want.abs() + rtol * scale).all())
+
+        out[rank] = (close(dx, want_dx[r0:r1], 2e-2, 2.0) and close(dgamma, want_dg, 1e-5, 4.0 * rows ** 0.5)
+                     and close(dbeta, want_db, 1e-5, 4.0 * rows ** 0.5) and N.device_status() == 0)
+    finally:
+        N.check(lib.credit_comm_destroy(comm))
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_c_abi_collective_allreduces_parameter_gradients(native_lib, tmp_path):
+    import torch.multiprocessing as mp
+
+    world, rows, cols = 2, 301, 4096
+    with mp.Manager() as manager:
+        out = manager.dict()
+        mp.spawn(_abi_worker, args=(world, str(tmp_path / "nccl_id.bin"), rows, cols, out), nprocs=world, join=True)
+        assert dict(out) == {0: True, 1: True}
+
+
+def test_c_abi_collective_in_a_world_of_one(native_lib):
+    """One rank: init, an all-reduce that is the identity, destroy; bad arguments are reported."""
+    import ctypes
+
+    from credit_b200 import _native as N
+
+    lib = N.load()
+    torch.cuda.set_device(0)
+    ident = ctypes.create_string_buffer(128)
+    N.check(lib.credit_comm_get_unique_id(ident))
+    comm = ctypes.c_void_p()
+    N.check(lib.credit_comm_init_rank(ctypes.byref(comm), 1, 0, ident))
+    buf = torch.arange(2 * 1000, dtype=torch.float32, device="cuda:0").reshape(2, 1000)
+    want = buf.clone()
+    N.check(lib.credit_layernorm_bwd_allreduce(comm, buf.data_ptr(), 1000, torch.cuda.current_stream().cuda_stream))
+    torch.cuda.synchronize()
+    assert torch.equal(buf, want)
+    assert lib.credit_layernorm_bwd_allreduce(comm, None, 1000, None) == N.ERR_INVALID_ARGUMENT
+    assert lib.credit_layernorm_bwd_allreduce(None, buf.data_ptr(), 1000, None) == N.ERR_INVALID_ARGUMENT
+    assert lib.credit_comm_init_rank(ctypes.byref(ctypes.c_void_p()), 2, 5, ident) == N.ERR_INVALID_ARGUMENT
+    N.check(lib.credit_comm_destroy(comm))
