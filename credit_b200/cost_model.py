@@ -136,9 +136,9 @@ class B200Calibration:
     # warp-specialised pipeline (8 output warps): a row costs a cluster the larger of its CTAs'
     # share of the HBM bandwidth and the output warps' issue time
     ws_sm_gbps_cap: float = 58.0               # most one SM pulls through bulk copies (7.0 TB/s on 120 SMs)
-    ws_fixed_cycles: float = 400.0             # per row and CTA, whatever the slice length
-    ws_fixed_cycles_p16: float = 1100.0        # the same in clusters of 16
-    ws_cycles_per_element_fwd: float = 25.0    # per row element a thread owns, forward kernels
+    ws_fixed_cycles: float = 550.0             # per row and CTA, whatever the slice length
+    ws_p16_penalty: float = 1.15               # clusters of 16 ran this much slower than the terms say
+    ws_cycles_per_element_fwd: float = 28.0    # per row element a thread owns, forward kernels
     ws_cycles_per_element_bwd: float = 40.0    # LayerNorm backward with column sums
     ws_cycles_per_element_per_array: float = 12.0   # reference-sweep workloads, per staged or written array
     ws_short_ring_penalty: float = 1.12        # fewer than five stages: the passes run one row apart
@@ -207,9 +207,10 @@ def predict_ws_ms(rows: int, cols: int, cluster_size: int, resident_clusters: in
     per_elem = (cal.ws_cycles_per_element_bwd if backward else
                 cal.ws_cycles_per_element_per_array * (arrays_in + arrays_out) if row_op else
                 cal.ws_cycles_per_element_fwd)
-    fixed = cal.ws_fixed_cycles_p16 if cluster_size >= 16 else cal.ws_fixed_cycles
-    issue_us = (fixed + per_elem * elems) / (cal.clock_ghz * 1.0e3)
+    issue_us = (cal.ws_fixed_cycles + per_elem * elems) / (cal.clock_ghz * 1.0e3)
     row_us = max(hbm_us, issue_us) * (cal.ws_short_ring_penalty if stages < 5 else 1.0)
+    if cluster_size >= 16:
+        row_us *= cal.ws_p16_penalty
     rows_per_cluster = math.ceil(rows / resident_clusters)
     predicted = row_us * (rows_per_cluster + cal.ws_fill_rows) * 1.0e-3
     hbm_ms = (arrays_in + arrays_out) * rows * cols * elem_bytes / (cal.hbm_gbps * 1.0e6)

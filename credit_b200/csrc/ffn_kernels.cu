@@ -28,7 +28,10 @@
 // In the second GEMM the CTAs of a cluster walk over the same row blocks in step;
 // the per-row partial sums travel with st.async and are counted on the receiving
 // CTA's mbarrier (two slot buffers), so the producer and MMA warps never stop for
-// the exchange.
+// the exchange. A cluster works on TWO row blocks at a time where it can (one in each
+// of a CTA's two accumulators): the B tile of a k block is then staged once for two
+// MMAs, a third less traffic into shared memory per FLOP, and W2 passes through the
+// chip once per two rounds of row blocks instead of once per round.
 // Every mbarrier wait is bounded; a timeout sets the device status word and the
 // kernel still releases its tensor memory.
 
@@ -63,11 +66,14 @@ constexpr int kRingBytes = 192 * 1024;
 // both SMs read both halves, so a CTA moves a third less through its shared memory
 // per MMA, which is what bounds the one-CTA form (TMA writes + MMA reads = 192 bytes
 // per clock against 128 available).
-template <bool PAIR>
+// DUAL (second GEMM): a stage holds the A tiles of two row blocks and one B tile, A0 | A1 | B; an
+// item of a single row block leaves A1 unused.
+template <bool PAIR, bool DUAL = false>
 struct Ring {
     static constexpr int kBRows = PAIR ? kBN / 2 : kBN;
     static constexpr int kBTileBytes = kBRows * kBK * 2;
-    static constexpr int kStageBytes = kATileBytes + kBTileBytes;
+    static constexpr int kBOffset = (DUAL ? 2 : 1) * kATileBytes;
+    static constexpr int kStageBytes = kBOffset + kBTileBytes;
     static constexpr int kStages = kRingBytes / kStageBytes;
     static_assert(kStages <= kMaxFfnStages, "control block has too few barriers");
 };
@@ -270,17 +276,28 @@ __device__ __forceinline__ void wait_or_give_up(uint32_t bar, uint32_t parity, i
 //                partials to its accumulator and runs the epilogue.
 struct WorkItem {
     int tile;       // row block (NORM) or tile number
+    int tile2;      // >= 0: a second row block worked on at the same time (other accumulator)
     int kb0, kb1;   // k blocks [kb0, kb1)
 };
 
 struct TileWalk {
     int m_tiles, k_blocks;
     int fixed_n;           // >= 0: every work item is a row block and the column tile is fixed
+    int dual_next, dual_step, dual_end;   // pairs of row blocks (2 * p, 2 * p + 1), p below dual_end
     int next, step, end;   // plain walk
     int tail_tile;         // >= 0: one more item, part of a shared row block
     int tail_kb0, tail_kb1;
 
     __device__ __forceinline__ bool pop(WorkItem& w) {
+        w.tile2 = -1;
+        if (dual_next < dual_end) {
+            w.tile = 2 * dual_next;
+            w.tile2 = 2 * dual_next + 1;
+            w.kb0 = 0;
+            w.kb1 = k_blocks;
+            dual_next += dual_step;
+            return true;
+        }
         if (next < end) {
             w.tile = next;
             w.kb0 = 0;
@@ -340,7 +357,7 @@ ffn_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 float* __restrict__ partials, int* __restrict__ flags, int* status) {
     static_assert(!(NORM_EPILOGUE && PAIR), "the row-norm epilogue uses the cluster for whole rows");
     constexpr int CG = PAIR ? 2 : 1;
-    using R = Ring<PAIR>;
+    using R = Ring<PAIR, NORM_EPILOGUE>;
     constexpr int kStages = R::kStages;
     constexpr int kStageBytes = R::kStageBytes;
     constexpr int kTileRows = PAIR ? 2 * kBM : kBM;   // rows of a work item
@@ -368,15 +385,24 @@ ffn_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     walk0.k_blocks = k_blocks;
     walk0.tail_tile = -1;
     walk0.tail_kb0 = walk0.tail_kb1 = 0;
+    walk0.dual_next = walk0.dual_end = 0;
+    walk0.dual_step = 1;
     int group = 1;   // clusters sharing the tail row block of this cluster
     const int cluster_id = static_cast<int>(blockIdx.x / (NORM_EPILOGUE ? nranks : CG));
     const int num_clusters = static_cast<int>(gridDim.x / (NORM_EPILOGUE ? nranks : CG));
     if (NORM_EPILOGUE) {
-        walk0.next = cluster_id;
+        // rounds of two row blocks per cluster first, then at most one round of single blocks, then
+        // the blocks that are left (fewer than clusters) shared by groups of clusters
+        const int dual_rounds = m_tiles / (2 * num_clusters);
+        const int dual_blocks = dual_rounds * 2 * num_clusters;
+        walk0.dual_next = cluster_id;
+        walk0.dual_step = num_clusters;
+        walk0.dual_end = dual_rounds * num_clusters;
+        walk0.next = dual_blocks + cluster_id;
         walk0.step = num_clusters;
         walk0.end = m_tiles;
         walk0.fixed_n = static_cast<int>(rank);
-        const int left = m_tiles % num_clusters;
+        const int left = (m_tiles - dual_blocks) % num_clusters;
         // at most 4 clusters per block (the owner reads every helper's tile twice), at least 4 k
         // blocks per part
         int share = left != 0 ? num_clusters / left : 1;
@@ -431,6 +457,8 @@ ffn_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 walk.locate(w.tile, m_tile, n_tile);
                 const int a_row = m_tile * kTileRows + half * kBM;
                 const int b_row = n_tile * kBN + half * R::kBRows;
+                const bool dual = NORM_EPILOGUE && w.tile2 >= 0;
+                const uint32_t stage_tx = CG * (kATileBytes + R::kBTileBytes) + (dual ? kATileBytes : 0);
                 for (int kb = w.kb0; kb < w.kb1; ++kb) {
                     wait_or_give_up(smem_u32(&ctl.empty[stage]), parity, status, gave_up);
                     // the stage's "full" barrier is the leader's: its MMA thread consumes both halves
@@ -438,10 +466,11 @@ ffn_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     // first: the phase cannot end before this arrival)
                     const uint32_t local_bar = smem_u32(&ctl.full[stage]);
                     const uint32_t bar = PAIR ? map_to_rank(local_bar, rank & ~1u) : local_bar;
-                    if (leader) mbar_arrive_expect_tx(local_bar, CG * kStageBytes);
+                    if (leader) mbar_arrive_expect_tx(local_bar, stage_tx);
                     const uint32_t a_dst = smem_u32(tiles + stage * kStageBytes);
                     tma_load_2d<CG>(a_dst, &map_a, bar, kb * kBK, a_row);
-                    tma_load_2d<CG>(a_dst + kATileBytes, &map_b, bar, kb * kBK, b_row);
+                    if (dual) tma_load_2d<CG>(a_dst + kATileBytes, &map_a, bar, kb * kBK, w.tile2 * kTileRows);
+                    tma_load_2d<CG>(a_dst + R::kBOffset, &map_b, bar, kb * kBK, b_row);
                     if (++stage == kStages) {
                         stage = 0;
                         parity ^= 1u;
@@ -458,12 +487,15 @@ ffn_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             uint32_t parity = 0;
             TileWalk walk = walk0;
             WorkItem w;
-            for (int it = 0; walk.pop(w); ++it) {
-                const int buf = it & 1;
-                // the epilogue warps (of both CTAs) have read this accumulator out; passes at once
-                // the first two times
-                wait_or_give_up(smem_u32(&ctl.acc_empty[buf]), ((static_cast<uint32_t>(it) >> 1) & 1u) ^ 1u, status,
-                                gave_up);
+            uint32_t uses[2] = {0u, 0u};   // times each accumulator has been filled so far
+            int singles = 0;
+            while (walk.pop(w)) {
+                const bool dual = NORM_EPILOGUE && w.tile2 >= 0;
+                const int buf = dual ? 0 : (singles++ & 1);   // single items alternate; a dual item takes both
+                // the epilogue warps (of both CTAs) have read the accumulator(s) out; passes at once
+                // the first time
+                wait_or_give_up(smem_u32(&ctl.acc_empty[buf]), (uses[buf] & 1u) ^ 1u, status, gave_up);
+                if (dual) wait_or_give_up(smem_u32(&ctl.acc_empty[1]), (uses[1] & 1u) ^ 1u, status, gave_up);
                 tc_fence_after_sync();
                 const uint32_t acc = tmem_base + static_cast<uint32_t>(buf * kAccCols);
                 for (int kb = w.kb0; kb < w.kb1; ++kb) {
@@ -471,11 +503,18 @@ ffn_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     tc_fence_after_sync();
                     const uint32_t a_addr = smem_u32(tiles + stage * kStageBytes);
                     const uint64_t desc_a = smem_desc_k_major_sw128(a_addr);
-                    const uint64_t desc_b = smem_desc_k_major_sw128(a_addr + kATileBytes);
+                    const uint64_t desc_b = smem_desc_k_major_sw128(a_addr + R::kBOffset);
 #pragma unroll
                     for (int k = 0; k < kBK / kUmmaK; ++k) {
                         // advance 16 bf16 = 32 bytes inside the swizzle row: +2 in the address field
                         umma_bf16<CG>(acc, desc_a + 2u * k, desc_b + 2u * k, idesc, (kb != w.kb0 || k != 0) ? 1u : 0u);
+                    }
+                    if (dual) {   // the second row block against the same B tile, into the other accumulator
+                        const uint64_t desc_a2 = smem_desc_k_major_sw128(a_addr + kATileBytes);
+#pragma unroll
+                        for (int k = 0; k < kBK / kUmmaK; ++k)
+                            umma_bf16<CG>(acc + kAccCols, desc_a2 + 2u * k, desc_b + 2u * k, idesc,
+                                          (kb != w.kb0 || k != 0) ? 1u : 0u);
                     }
                     // stage reusable (in both CTAs) when these MMAs are done
                     if (PAIR)
@@ -487,10 +526,15 @@ ffn_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                         parity ^= 1u;
                     }
                 }
+                ++uses[buf];
                 if (PAIR)   // accumulator complete (in both CTAs)
                     umma_commit_pair(smem_u32(&ctl.acc_full[buf]), pair_mask);
                 else
                     umma_commit<CG>(smem_u32(&ctl.acc_full[buf]));
+                if (dual) {
+                    ++uses[1];
+                    umma_commit<CG>(smem_u32(&ctl.acc_full[1]));
+                }
             }
         }
         __syncwarp();
@@ -501,16 +545,23 @@ ffn_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         TileWalk walk = walk0;
         WorkItem w;
         int exchanges = 0;   // row-norm exchanges done: selects the slot buffer and its barrier phase
-        for (int it = 0; walk.pop(w); ++it) {
+        uint32_t uses[2] = {0u, 0u};   // times each accumulator has been read out so far
+        int singles = 0;
+        while (walk.pop(w)) {
+          const bool dual = NORM_EPILOGUE && w.tile2 >= 0;
+          const int single_buf = dual ? 0 : (singles++ & 1);
+          // a dual item is two row blocks, one per accumulator: the same epilogue twice
+          for (int sub = 0; sub < (dual ? 2 : 1); ++sub) {
             int m_tile, n_tile;
-            walk.locate(w.tile, m_tile, n_tile);
-            const int buf = it & 1;
+            walk.locate(sub == 0 ? w.tile : w.tile2, m_tile, n_tile);
+            const int buf = dual ? sub : single_buf;
             const size_t row = static_cast<size_t>(m_tile) * kTileRows + half * kBM + row_in_tile;
             const size_t col0 = static_cast<size_t>(n_tile) * kBN;
             const uint32_t lane_base =
                 tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(buf * kAccCols);
             __nv_bfloat16* dst = out + row * n_total + col0;
-            wait_or_give_up(smem_u32(&ctl.acc_full[buf]), (static_cast<uint32_t>(it) >> 1) & 1u, status, gave_up);
+            wait_or_give_up(smem_u32(&ctl.acc_full[buf]), uses[buf] & 1u, status, gave_up);
+            ++uses[buf];
             tc_fence_after_sync();
 
             if (!NORM_EPILOGUE) {
@@ -617,7 +668,7 @@ ffn_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     }
                 }
             }
-            // accumulator `buf` may be overwritten by the MMAs of item it + 2: one arrival per warp
+            // accumulator `buf` may be overwritten by the MMAs of the next item that uses it: one arrival per warp
             // on the barrier of the CTA that issues them
             tc_fence_before_sync();
             __syncwarp();
@@ -628,6 +679,7 @@ ffn_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 else
                     mbar_arrive(bar);
             }
+          }
         }
     }
 

@@ -385,9 +385,10 @@ int plan_static(int workload, const Shape& s, int dtype, const credit_launch_opt
         p->threads = o.threads ? o.threads : 256;
         int cluster = o.cluster_size;
         if (cluster == 0) {
-            // Enough CTAs to cover the device a few times, but slices of at least 64 KiB.
+            // One CTA per row unless the rows are too few to cover the device twice (measured: at 512
+            // rows one CTA per row wins from 4 K to 1 M columns); slices of at least 64 KiB.
             cluster = 1;
-            while (cluster < max_cluster && 1ll * s.rows * cluster < 16ll * dev.sm_count &&
+            while (cluster < max_cluster && 1ll * s.rows * cluster < 2ll * dev.sm_count &&
                    1ll * s.cols * 4 / (cluster * 2) >= 65536)
                 cluster *= 2;
             if (o.variant == CREDIT_VARIANT_CLUSTER_SMEM && cluster < 2) cluster = 2;
@@ -638,7 +639,7 @@ double compulsory_bytes(int workload, const Shape& s, bool grads) {
 double predicted_ms(int workload, const Shape& s, const credit_plan_info& p, bool grads) {
     const double hbm_ms = compulsory_bytes(workload, s, grads) / (calibrated_hbm_gbps() * 1.0e6);
     if (p.vectors_per_thread == 0) return hbm_ms / 0.5;   // shared-memory re-read kernels
-    static const double kExchange[5] = {157.0, 315.0, 322.0, 351.0, 420.0};   // P = 1, 2, 4, 8, 16
+    static const double kExchange[5] = {150.0, 315.0, 322.0, 351.0, 420.0};   // P = 1, 2, 4, 8, 16
     int log2p = 0;
     while ((1 << log2p) < p.cluster_size) ++log2p;
     const int stages = workload == CREDIT_WL_LAYERNORM_BACKWARD ? 2 : 1;
@@ -655,8 +656,9 @@ double predicted_ms(int workload, const Shape& s, const credit_plan_info& p, boo
 // about 58 GB/s through bulk copies) and the output warps' issue time for one row (a fixed part per
 // row plus a part per row element a thread owns); a kernel costs rows-per-cluster + 3 such periods
 // (ring fill, the rows between the two passes, the last cluster's extra row). Constants measured on
-// B200 with 8 output warps: fixed part 400 cycles (1100 in clusters of 16), 25 cycles per element
-// forward and 40 backward, 12 % more with a ring too short to run the passes two rows apart.
+// B200 with 8 output warps: fixed part 550 cycles, 28 cycles per element forward and 40 backward,
+// 12 % more with a ring too short to run the passes two rows apart, 15 % more in clusters of 16
+// (7 of them are co-resident, and they ran that much slower than the terms above say).
 double predicted_ws_ms(int workload, const Shape& s, const credit_plan_info& p, bool grads) {
     const int nin = inputs_staged(workload);
     double nout = 1.0;   // output arrays of the element type written per row
@@ -668,10 +670,11 @@ double predicted_ws_ms(int workload, const Shape& s, const credit_plan_info& p, 
     const double hbm_us = bytes_per_cta_row / (per_sm_gbps * 1.0e3);
     const int out_threads = p.threads - 96;
     const double elems = std::ceil(static_cast<double>(p.slice_elems) / out_threads);
-    const double per_elem = grads ? 40.0 : (is_row_op(workload) ? 12.0 * (nin + nout) : 25.0);
-    const double issue_us = ((p.cluster_size >= 16 ? 1100.0 : 400.0) + per_elem * elems) / 1930.0;
+    const double per_elem = grads ? 40.0 : (is_row_op(workload) ? 12.0 * (nin + nout) : 28.0);
+    const double issue_us = (550.0 + per_elem * elems) / 1930.0;
     double row_us = std::max(hbm_us, issue_us);
     if (p.stages < 5) row_us *= 1.12;
+    if (p.cluster_size >= 16) row_us *= 1.15;
     const double rows_per_cluster = std::ceil(static_cast<double>(s.rows) / std::max(p.num_clusters, 1));
     return row_us * (rows_per_cluster + 3.0) * 1.0e-3;
 }

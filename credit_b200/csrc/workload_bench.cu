@@ -556,9 +556,11 @@ void run_row_op_shape(const Workload& w, int rows, int cols, int chosen, const O
             verify_row_op(w.id, b, sh, rows, cols, "block");
         }
     }
-    if (opts.profile_variant != "block" && chosen >= 2) {
+    // --cluster-size 1 (an extension: the reference prints n/a there) puts the same pipeline with one
+    // CTA per row in the cluster column, so that a sweep can cover the size the planner often picks
+    if (opts.profile_variant != "block" && chosen >= 1) {
         o = credit_launch_opts{};
-        o.variant = CREDIT_VARIANT_CLUSTER_SMEM;
+        o.variant = chosen >= 2 ? CREDIT_VARIANT_CLUSTER_SMEM : CREDIT_VARIANT_AUTO;
         o.cluster_size = chosen;
         cluster = time_row_op("cluster_smem", w.id, b, rows, cols, o, opts, bytes);
         if (cluster.valid && opts.verify) {
@@ -641,9 +643,11 @@ void run_shape(const Workload& w, int dtype, int rows, int cols, int chosen, con
             verify_outputs(w.id, dtype, b, rows, cols, "block");
         }
     }
-    if (opts.profile_variant != "block" && chosen >= 2) {
+    // --cluster-size 1 (an extension: the reference prints n/a there) puts the same pipeline with one
+    // CTA per row in the cluster column, so that a sweep can cover the size the planner often picks
+    if (opts.profile_variant != "block" && chosen >= 1) {
         o = credit_launch_opts{};
-        o.variant = CREDIT_VARIANT_CLUSTER_SMEM;
+        o.variant = chosen >= 2 ? CREDIT_VARIANT_CLUSTER_SMEM : CREDIT_VARIANT_AUTO;
         o.cluster_size = chosen;
         cluster = time_variant("cluster_smem", w.id, dtype, b, rows, cols, o, opts, elem);
         if (cluster.valid && opts.verify) {

@@ -32,7 +32,7 @@ from .workloads import WORKLOADS
 PACKAGE_DIR = Path(__file__).resolve().parent
 BIN_DIR = PACKAGE_DIR / "bin"
 DEFAULT_N_VALUES = (4096, 8192, 16384, 32768, 65536)
-DEFAULT_CLUSTER_SIZES = (2, 4, 8, 16)   # 1 is swept too when asked for: --cluster-sizes 1,2,4,8,16
+DEFAULT_CLUSTER_SIZES = (1, 2, 4, 8, 16)   # 1: the same pipeline with one CTA per row
 CLI_WORKLOADS = ("layernorm_backward", "rmsnorm_forward", "row_reduce", "layernorm_forward",
                  "layernorm_backward_stats", "weighted_var_backward", "pearson_backward",
                  "softmax_logits_backward", "lars_momentum", "rowwise_quant")
@@ -274,7 +274,7 @@ def resident_clusters(name: str, rows: int, cols: int, dtype: str, cluster_size:
     from . import _native as N
     try:
         plan = N.plan(_WORKLOAD_IDS[name], rows, cols, N.BF16 if dtype == "bf16" else N.F32,
-                      {"cluster_size": cluster_size, "variant": N.VARIANT_CLUSTER_SMEM if cluster_size > 1 else 0})
+                      {"cluster_size": cluster_size, "variant": N.VARIANT_CLUSTER_SMEM if cluster_size > 1 else N.VARIANT_AUTO})
     except N.CreditError:
         return 0, 0, False, 0
     return plan.num_clusters, plan.threads, plan.vectors_per_thread > 0, plan.stages

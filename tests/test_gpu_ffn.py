@@ -31,7 +31,10 @@ def check(y, want):
 @pytest.mark.parametrize("m,d,h", [(128, 256, 512), (256, 512, 1024), (128, 1024, 2048), (384, 2048, 512),
                                     (128, 4096, 1024), (1024, 512, 8192),
                                     # more row blocks than resident clusters: the second GEMM splits blocks by k range
-                                    (1152, 4096, 512), (2048, 2048, 768)])
+                                    (1152, 4096, 512), (2048, 2048, 768),
+                                    # two row blocks at a time per cluster (both accumulators, one B tile): one round
+                                    # of pairs plus a split tail; two rounds of pairs; pairs, a single round and a tail
+                                    (2048, 4096, 512), (3584, 4096, 256), (3072, 4096, 256)])
 def test_ffn_forward_matches_oracle(native_lib, m, d, h):
     x, w1, w2, gamma = W.make_ffn_inputs(m, d, "cpu", seed=m + d, hidden=h)
     y, w1p = run_ffn(x, w1, w2, gamma)
