@@ -39,7 +39,7 @@ LIB_SOURCES = [
     "host_entry.cu",
     "tables_ws_rmsnorm.cu",
     "tables_ws_layernorm_fwd.cu",
-    "tables_ws_layernorm_bwd.cu",
+    "tables_ws_layernorm_bwd.cu", "tables_ws_layernorm_bwd_dx.cu",
     "tables_ws_row_ops.cu",
     "comm_entry.cu",
 ]

@@ -140,6 +140,8 @@ class B200Calibration:
     ws_p16_penalty: float = 1.15               # clusters of 16 ran this much slower than the terms say
     ws_cycles_per_element_fwd: float = 28.0    # per row element a thread owns, forward kernels
     ws_cycles_per_element_bwd: float = 40.0    # LayerNorm backward with column sums
+    ws_load_latency_us: float = 1.5            # a ring stage's request lands after about this long
+    ws_cycles_per_element_bwd_dx: float = 36.0   # LayerNorm backward, dx only (two staged inputs)
     ws_cycles_per_element_per_array: float = 12.0   # reference-sweep workloads, per staged or written array
     ws_short_ring_penalty: float = 1.12        # fewer than five stages: the passes run one row apart
     ws_fill_rows: float = 3.0                  # ring fill, rows between the passes, the last cluster's extra row
@@ -206,9 +208,12 @@ def predict_ws_ms(rows: int, cols: int, cluster_size: int, resident_clusters: in
     elems = math.ceil(slice_elems / (threads - 96))
     per_elem = (cal.ws_cycles_per_element_bwd if backward else
                 cal.ws_cycles_per_element_per_array * (arrays_in + arrays_out) if row_op else
+                cal.ws_cycles_per_element_bwd_dx if arrays_in == 2 else
                 cal.ws_cycles_per_element_fwd)
     issue_us = (cal.ws_fixed_cycles + per_elem * elems) / (cal.clock_ghz * 1.0e3)
-    row_us = max(hbm_us, issue_us) * (cal.ws_short_ring_penalty if stages < 5 else 1.0)
+    in_flight = max(1, stages - (3 if stages >= 5 else 2))   # ring stages that are loads on their way
+    row_us = max(hbm_us, issue_us, cal.ws_load_latency_us / in_flight)
+    row_us *= cal.ws_short_ring_penalty if stages < 5 else 1.0
     if cluster_size >= 16:
         row_us *= cal.ws_p16_penalty
     rows_per_cluster = math.ceil(rows / resident_clusters)

@@ -22,6 +22,7 @@ const void* row_reduce_kernel_for(int load_path, int threads, bool aligned);
 const void* ws_rmsnorm_kernel_for(int dtype, int out_warps, int vpt, bool full);
 const void* ws_layernorm_fwd_kernel_for(int dtype, int out_warps, int vpt, bool full);
 const void* ws_layernorm_bwd_kernel_for(int dtype, int out_warps, int vpt, bool full);
+const void* ws_layernorm_bwd_dx_kernel_for(int dtype, int out_warps, int vpt, bool full, bool recompute);
 // Reference-sweep workloads on the same pipeline (fp32, 8 output warps, slices of any length).
 const void* ws_row_op_kernel_for(int workload);
 // One CTA of 512 threads per row, nothing staged (CREDIT_VARIANT_BLOCK_READ).

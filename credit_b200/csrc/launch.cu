@@ -245,8 +245,8 @@ int check_opts(const credit_launch_opts* o, credit_launch_opts* out) {
                     z.cluster_size);
     if (z.variant < CREDIT_VARIANT_AUTO || z.variant > CREDIT_VARIANT_CLUSTER_SMEM)
         return fail(CREDIT_ERR_INVALID_ARGUMENT, "unknown variant %d", z.variant);
-    if (z.stages < 0 || z.stages > kMaxStages)
-        return fail(CREDIT_ERR_INVALID_ARGUMENT, "stages must be in [0, %d] (got %d)", kMaxStages,
+    if (z.stages < 0 || z.stages > kWsMaxStages)
+        return fail(CREDIT_ERR_INVALID_ARGUMENT, "stages must be in [0, %d] (got %d)", kWsMaxStages,
                     z.stages);
     if (z.threads != 0 && z.threads != 256 && z.threads != 512 && z.threads != kWsThreadsPerCta &&
         z.threads != kWsThreadsPerCtaWide)
@@ -293,8 +293,10 @@ const void* workload_func(int workload, int dtype, const credit_plan_info& p, bo
         switch (workload) {
             case CREDIT_WL_RMSNORM_FORWARD: return ws_rmsnorm_kernel_for(dtype, out_warps, vpt, full);
             case CREDIT_WL_LAYERNORM_FORWARD: return ws_layernorm_fwd_kernel_for(dtype, out_warps, vpt, full);
+            case CREDIT_WL_LAYERNORM_BACKWARD: return ws_layernorm_bwd_dx_kernel_for(dtype, out_warps, vpt, full, true);
             case CREDIT_WL_LAYERNORM_BACKWARD_STATS:
-                return want_grads ? ws_layernorm_bwd_kernel_for(dtype, out_warps, vpt, full) : nullptr;
+                return want_grads ? ws_layernorm_bwd_kernel_for(dtype, out_warps, vpt, full)
+                                  : ws_layernorm_bwd_dx_kernel_for(dtype, out_warps, vpt, full, false);
             default: return nullptr;
         }
     }
@@ -399,6 +401,8 @@ int plan_static(int workload, const Shape& s, int dtype, const credit_launch_opt
             int chunk_bytes = o.chunk_bytes ? o.chunk_bytes : 16384;
             chunk_bytes = std::min(chunk_bytes, round_up(p->slice_elems * 4, 1024));
             p->chunk_elems = chunk_bytes / 4;
+            if (o.stages > kMaxStages)
+                return fail(CREDIT_ERR_UNSUPPORTED, "the row reduction takes rings of at most %d stages", kMaxStages);
             p->stages = o.stages ? o.stages : 3;
             p->smem_bytes = kControlBytes + p->stages * chunk_bytes;
             if (p->smem_bytes > max_smem)
@@ -439,14 +443,17 @@ int plan_static(int workload, const Shape& s, int dtype, const credit_launch_opt
     };
 
     // The warp-specialised kernels (ws_row_kernels.cuh: 16 or 8 output warps plus producer, collector
-    // and receiver warps) serve RMSNorm forward, LayerNorm forward and LayerNorm backward with column
-    // sums whenever the rows are 16-byte aligned, the slice fits the output threads' registers and a
-    // ring of at least three stages fits shared memory. threads = 256 / 512 keep the lock-step
-    // register kernels.
+    // and receiver warps) serve RMSNorm forward, LayerNorm forward and every form of LayerNorm
+    // backward whenever the rows are 16-byte aligned, the slice fits the output threads' registers
+    // and a ring of at least three stages fits shared memory. threads = 256 / 512 keep the lock-step
+    // register kernels. (LayerNorm backward with recomputed statistics sends records of four sums:
+    // like the reference-sweep workloads it has the 8-output-warp form only.)
     const bool ws_threads = o.threads == kWsThreadsPerCta || o.threads == kWsThreadsPerCtaWide;
     const bool row_op = is_row_op(workload);   // no per-column registers: any slice length, 8 output warps only
-    const bool ws_workload = workload == CREDIT_WL_RMSNORM_FORWARD || workload == CREDIT_WL_LAYERNORM_FORWARD || grads ||
-                             (row_op && o.threads != kWsThreadsPerCta);
+    const bool wide_only = row_op || workload == CREDIT_WL_LAYERNORM_BACKWARD;
+    const bool ws_workload = wide_only ? o.threads != kWsThreadsPerCta
+                                       : (workload == CREDIT_WL_RMSNORM_FORWARD || workload == CREDIT_WL_LAYERNORM_FORWARD ||
+                                          workload == CREDIT_WL_LAYERNORM_BACKWARD_STATS);
     if (ws_workload && p->aligned && !(o.flags & CREDIT_FLAG_NO_REGISTER_PATH) && (o.threads == 0 || ws_threads) &&
         o.schedule != CREDIT_SCHEDULE_ROW_PER_CLUSTER && (o.stages == 0 || o.stages >= 3) &&
         o.variant != CREDIT_VARIANT_BLOCK_SMEM) {
@@ -456,15 +463,35 @@ int plan_static(int workload, const Shape& s, int dtype, const credit_launch_opt
         const bool wide = threads == kWsThreadsPerCtaWide;
         const int out_threads = threads - 96;   // three service warps
         const int max_slice = row_op ? (1 << 30) : out_threads * ws_max_elems_per_thread(grads, wide);
-        auto ws_fits = [&](int c) {
-            return round_up((s.cols + c - 1) / c, 64) <= max_slice && kWsControlBytes + 3 * stage_bytes_for(c) <= max_smem;
+        // Automatic choice, from a sweep of cluster size x ring depth on B200 (four workloads, row
+        // lengths 4096 ... 65536): the smallest cluster that fits wins or is within 2 % of the winner
+        // nearly everywhere, because small clusters cover more SMs (148, 148, 132, 120, 112 for sizes
+        // 1 ... 16) and spread a row's fixed costs over longer slices. A ring of three stages runs the
+        // two passes one row apart and costs 5 - 20 %, so a cluster that only fits three yields to the
+        // next size, except that 16 never replaces 8. The row-period model picked clusters too large
+        // (15 % mean loss on the same sweep, against 1.7 % for this rule).
+        auto ws_fits = [&](int c, int min_stages) {
+            return round_up((s.cols + c - 1) / c, 64) <= max_slice &&
+                   kWsControlBytes + min_stages * stage_bytes_for(c) <= max_smem;
         };
+        // Ring depth a cluster size must reach to be taken over the next one, from the same sweeps:
+        // four for the normalisation workloads and Pearson, six for LARS (three inputs and two
+        // outputs per row: its best size always had stages of 24 KiB), three for the others.
+        const int wanted_stages = workload == CREDIT_WL_LARS_MOMENTUM ? 6
+                                  : (row_op && workload != CREDIT_WL_PEARSON_BACKWARD) ? 3 : 4;
         int c = o.cluster_size;
         if (c == 0) {
-            c = o.variant == CREDIT_VARIANT_CLUSTER_SMEM ? 2 : 1;
-            while (c < max_cluster && !ws_fits(c)) c *= 2;
+            const int first = o.variant == CREDIT_VARIANT_CLUSTER_SMEM ? 2 : 1;
+            int with3 = 0, with4 = 0;
+            for (int t = first; t <= max_cluster; t *= 2) {
+                if (with3 == 0 && ws_fits(t, 3)) with3 = t;
+                if (with4 == 0 && ws_fits(t, wanted_stages)) with4 = t;
+            }
+            c = with4 != 0 ? with4 : with3;
+            if (c == 16 && with3 != 0 && with3 <= 8) c = with3;
+            if (c == 0) c = 2 * max_cluster;   // nothing fits: fall through to the other kernels
         }
-        if (c <= max_cluster && ws_fits(c)) {
+        if (c <= max_cluster && ws_fits(c, 3)) {
             p->cluster_size = c;
             p->slice_elems = round_up((s.cols + c - 1) / c, 64);
             const int nvec = p->slice_elems / s.vec_elems;
@@ -472,7 +499,14 @@ int plan_static(int workload, const Shape& s, int dtype, const credit_launch_opt
             while (vpt * out_threads < nvec && !row_op) vpt *= 2;
             if (row_op) vpt = std::max(1, (nvec + out_threads - 1) / out_threads);
             const int stage_bytes = stage_bytes_for(c);
-            int stages = o.stages ? o.stages : 6;
+            // Ring depth: up to 8 stages. Where six or more fit half of the SM's shared memory the
+            // ring stays inside that half, so that two CTAs share an SM (short slices: 2 x 8 stages
+            // measured faster than 1 x 12 or 1 x 16); otherwise whatever fits, up to 8.
+            auto most_stages = [&](int limit) { return std::min(8, (limit - kWsControlBytes) / std::max(stage_bytes, 1)); };
+            const int half_smem = (max_smem - 2048) / 2;
+            int stages = o.stages ? o.stages
+                         : row_op ? 6   // as swept for the reference workloads
+                                  : (most_stages(half_smem) >= 6 ? most_stages(half_smem) : most_stages(max_smem));
             while (stages > 3 && kWsControlBytes + stages * stage_bytes > max_smem) --stages;
             p->threads = threads;
             p->vectors_per_thread = vpt;
@@ -489,9 +523,12 @@ int plan_static(int workload, const Shape& s, int dtype, const credit_launch_opt
     } else if (ws_threads) {
         return fail(CREDIT_ERR_UNSUPPORTED,
                     "threads = %d selects a warp-specialised kernel: 16-byte aligned rows, persistent schedule, at "
-                    "least three stages (LayerNorm backward: with column sums; reference-sweep workloads: 352 only)",
+                    "least three stages (LayerNorm backward with recomputed statistics and the reference-sweep "
+                    "workloads: 352 only)",
                     o.threads);
     }
+    if (o.stages > kMaxStages)
+        return fail(CREDIT_ERR_UNSUPPORTED, "only the warp-specialised kernels take rings deeper than %d stages", kMaxStages);
     int cluster = o.cluster_size;
     if (cluster == 0) {
         // Smallest cluster whose slice fits the stage budget and, for aligned rows,
@@ -656,9 +693,10 @@ double predicted_ms(int workload, const Shape& s, const credit_plan_info& p, boo
 // about 58 GB/s through bulk copies) and the output warps' issue time for one row (a fixed part per
 // row plus a part per row element a thread owns); a kernel costs rows-per-cluster + 3 such periods
 // (ring fill, the rows between the two passes, the last cluster's extra row). Constants measured on
-// B200 with 8 output warps: fixed part 550 cycles, 28 cycles per element forward and 40 backward,
+// B200 with 8 output warps: fixed part 550 cycles, 28 cycles per element forward, 36 backward and 40 backward with column sums,
 // 12 % more with a ring too short to run the passes two rows apart, 15 % more in clusters of 16
-// (7 of them are co-resident, and they ran that much slower than the terms above say).
+// (7 of them are co-resident, and they ran that much slower than the terms above say), and a row
+// period of at least 1.5 us / (ring stages that are loads in flight).
 double predicted_ws_ms(int workload, const Shape& s, const credit_plan_info& p, bool grads) {
     const int nin = inputs_staged(workload);
     double nout = 1.0;   // output arrays of the element type written per row
@@ -670,9 +708,12 @@ double predicted_ws_ms(int workload, const Shape& s, const credit_plan_info& p, 
     const double hbm_us = bytes_per_cta_row / (per_sm_gbps * 1.0e3);
     const int out_threads = p.threads - 96;
     const double elems = std::ceil(static_cast<double>(p.slice_elems) / out_threads);
-    const double per_elem = grads ? 40.0 : (is_row_op(workload) ? 12.0 * (nin + nout) : 28.0);
+    const double per_elem = grads ? 40.0 : (is_row_op(workload) ? 12.0 * (nin + nout) : (nin == 2 ? 36.0 : 28.0));
     const double issue_us = (550.0 + per_elem * elems) / 1930.0;
-    double row_us = std::max(hbm_us, issue_us);
+    // loads in flight: three stages (two with a short ring) sit between the passes, the others are
+    // requests that take about 1.5 us to land, one row each
+    const int in_flight = std::max(1, p.stages - (p.stages >= 5 ? 3 : 2));
+    double row_us = std::max(std::max(hbm_us, issue_us), 1.5 / in_flight);
     if (p.stages < 5) row_us *= 1.12;
     if (p.cluster_size >= 16) row_us *= 1.15;
     const double rows_per_cluster = std::ceil(static_cast<double>(s.rows) / std::max(p.num_clusters, 1));
@@ -688,12 +729,17 @@ void choose_cluster_by_model(int device, const DeviceState& dev, int workload, c
                              bool pointers_aligned, bool grads, credit_launch_opts* o) {
     if (o->cluster_size != 0 || s.rows == 0 || !dev.info.cluster_launch) return;
     if (workload == CREDIT_WL_ROW_REDUCE) return;
-    // Reference-sweep workloads: the smallest cluster whose ring fits (plan_static's rule) was the
-    // fastest or within 10 % of it at every measured point: smaller clusters cover more SMs (148,
-    // 148, 132, 120, 112 for sizes 1 ... 16) and spread a row's fixed costs over longer slices.
+    // Reference-sweep workloads: plan_static's measured rule (the smallest cluster whose ring is deep
+    // enough) decides for both of their kernel families.
     if (is_row_op(workload)) return;
     if (o->variant == CREDIT_VARIANT_BLOCK_READ || o->variant == CREDIT_VARIANT_BLOCK_SMEM) return;
     if (o->schedule == CREDIT_SCHEDULE_ROW_PER_CLUSTER) return;
+    {
+        // the warp-specialised kernels choose by plan_static's measured rule, not by the model
+        credit_plan_info plan;
+        if (plan_static(workload, s, dtype, *o, pointers_aligned, grads, dev.info, &plan) == CREDIT_OK && is_ws_plan(plan)) return;
+        t_last_error[0] = '\0';
+    }
     const auto key = std::make_tuple(device, workload, s.rows, s.cols, dtype, pointers_aligned, grads, o->variant,
                                      o->threads, o->stages, o->flags);
     {
@@ -933,6 +979,16 @@ int credit_layernorm_backward(const void* x, const void* dy, const float* gamma,
         return launch_cluster_kernel(make_launch(r, stream), args);
     }
     StagedArgs a = staged_args(r);
+    if (is_ws_plan(r.plan)) {
+        NormParams prm{};
+        prm.x = x;
+        prm.dy = dy;
+        prm.gamma = gamma;
+        prm.y = dx;
+        prm.eps = eps;
+        void* args[] = {&prm, &a};
+        return launch_cluster_kernel(make_launch(r, stream), args);
+    }
     if (r.plan.vectors_per_thread > 0) {
         void* args[] = {&x, &dy, &gamma, &no_stats, &no_stats, &dx, &no_partials, &eps, &a};
         return launch_cluster_kernel(make_launch(r, stream), args);

@@ -7,6 +7,7 @@ namespace credit {
 constexpr int kMaxClusterSize = 16;   // 8 portable, 16 with the non-portable opt-in
 constexpr int kMaxWarpsPerCta = 32;
 constexpr int kMaxStages = 8;
+constexpr int kWsMaxStages = 16;      // the warp-specialised kernels: short slices need a deeper ring
 // Threads per CTA of the warp-specialised kernels: 16 (or, "wide", 8) output warps plus three
 // service warps (producer, collector, receiver); their control block at the start of dynamic
 // shared memory holds one pair of partial sums per output thread for four rows.

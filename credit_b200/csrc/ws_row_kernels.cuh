@@ -54,6 +54,12 @@
 #include "norm_kernels.cuh"
 #include "register_row_kernels.cuh"
 
+#ifdef CREDIT_WS_OUTPUT_PARK
+#define WS_OUT_WAIT mbar_wait_polled_then_parked
+#else
+#define WS_OUT_WAIT mbar_wait_bounded
+#endif
+
 namespace credit {
 
 constexpr int kWsMaxOutputWarps = 16;
@@ -66,8 +72,8 @@ constexpr int kWsSlotBuffers = 8;
 // KP floats per partial record (2, 4 or 8), L CTA-local record buffers, THREADS output threads.
 template <int KP, int L, int THREADS>
 struct alignas(16) WsControl {
-    uint64_t full[kMaxStages];                 // stage has landed (1 arrival + transaction bytes)
-    uint64_t empty[kMaxStages];                // stage has been read twice by every output warp
+    uint64_t full[kWsMaxStages];               // stage has landed (1 arrival + transaction bytes)
+    uint64_t empty[kWsMaxStages];               // stage has been read twice by every output warp
     uint64_t local_bar[4];                     // every output warp has left its records of a row
     uint64_t ex_bar[kWsSlotBuffers];           // the P records of a row are in slot
     uint64_t ready_bar[kWsSlotBuffers];        // the row's record is in total
@@ -311,7 +317,7 @@ ws_row_kernel(NormParams prm, StagedArgs a) {
     for (int it = 0; it < my_rows + ahead; ++it) {
         // ---- pass 1 of row `it`: this thread's share of the row's sums
         if (it < my_rows) {
-            if (g.local > 0) mbar_wait_bounded(smem_u32(&ctl.full[stage1]), parity1, a.status);
+            if (g.local > 0) WS_OUT_WAIT(smem_u32(&ctl.full[stage1]), parity1, a.status);
             const uint4* tiles[NIN];
 #pragma unroll
             for (int n = 0; n < NIN; ++n)
@@ -320,7 +326,7 @@ ws_row_kernel(NormParams prm, StagedArgs a) {
             float4 info = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
             if (Op::kRowInfo) {
                 const int ib = it & (kWsSlotBuffers - 1);
-                mbar_wait_bounded(smem_u32(&ctl.info_bar[ib]), (static_cast<uint32_t>(it) / kWsSlotBuffers) & 1u, a.status);
+                WS_OUT_WAIT(smem_u32(&ctl.info_bar[ib]), (static_cast<uint32_t>(it) / kWsSlotBuffers) & 1u, a.status);
                 info = ctl.row_info[ib];
             }
             float part[KP];
@@ -339,7 +345,7 @@ ws_row_kernel(NormParams prm, StagedArgs a) {
             const int it2 = it - ahead;
             const int row = cluster + it2 * a.num_clusters;
             const int xb = it2 & (kWsSlotBuffers - 1);
-            mbar_wait_bounded(smem_u32(&ctl.ready_bar[xb]), (static_cast<uint32_t>(it2) / kWsSlotBuffers) & 1u, a.status);
+            WS_OUT_WAIT(smem_u32(&ctl.ready_bar[xb]), (static_cast<uint32_t>(it2) / kWsSlotBuffers) & 1u, a.status);
             float sums[KP];
             ws_load_record<KP>(&ctl.total[xb][0], sums);
             // the row's scalars were published before its pass 1, which this warp has run
@@ -538,8 +544,8 @@ struct LayerNormFwdOp {
 // xhat = c * rstd, g = dy * gamma, S1 = sum_row g and S2 = sum_row g * c:
 //   dx = g * rstd + c * (-rstd^3 * S2 / N) + (-rstd * S1 / N)
 // ---------------------------------------------------------------------------
-template <typename T, int OUT_WARPS, int VPT, bool FULL>
-struct LayerNormBwdOp {
+template <typename T, int OUT_WARPS, int VPT, bool FULL, bool GRADS>
+struct LayerNormBwdGivenOp {
     using Elem = T;
     static constexpr int kInputs = 2, kOutWarps = OUT_WARPS, kVectors = VPT, THREADS = OUT_WARPS * 32;
     static constexpr bool kFull = FULL;
@@ -549,8 +555,9 @@ struct LayerNormBwdOp {
     static constexpr bool kAdditive = true, kRegisterSlice = true;
     __device__ __forceinline__ static void identity(float (&v)[2]) { v[0] = v[1] = 0.0f; }
     __device__ __forceinline__ static void combine(float (&v)[2], const float (&o)[2]) { v[0] += o[0]; v[1] += o[1]; }
+    static constexpr int GV = GRADS ? VPT : 1;   // without column sums their registers shrink to a stub
     struct State {
-        float2 gam[VPT][PAIRS], dgam[VPT][PAIRS], dbet[VPT][PAIRS];
+        float2 gam[VPT][PAIRS], dgam[GV][PAIRS], dbet[GV][PAIRS];
     };
     __device__ __forceinline__ static void sources(const NormParams& p, const T* (&src)[2]) {
         src[0] = static_cast<const T*>(p.x);
@@ -568,8 +575,10 @@ struct LayerNormBwdOp {
 #pragma unroll
             for (int j = 0; j < PAIRS; ++j) {
                 st.gam[i][j] = splat(0.0f);
-                st.dgam[i][j] = splat(0.0f);
-                st.dbet[i][j] = splat(0.0f);
+                if constexpr (GRADS) {
+                    st.dgam[i][j] = splat(0.0f);
+                    st.dbet[i][j] = splat(0.0f);
+                }
             }
             if (FULL || v < nvec) load_param_pairs<PAIRS>(p.gamma + col0 + v * E, st.gam[i]);
         }
@@ -629,19 +638,20 @@ struct LayerNormBwdOp {
                     if (sizeof(T) == 2) {
                         const float2 xhat = __ffma2_rn(xv[j], rstd2, shift2);
                         o[j] = __ffma2_rn(xhat, ca_hat, __ffma2_rn(gg, rstd2, cb));
-                        st.dgam[i][j] = __ffma2_rn(dv[j], xhat, st.dgam[i][j]);
+                        if constexpr (GRADS) st.dgam[i][j] = __ffma2_rn(dv[j], xhat, st.dgam[i][j]);
                     } else {
                         const float2 c = __fadd2_rn(xv[j], neg_mean);
                         o[j] = __ffma2_rn(c, ca, __ffma2_rn(gg, rstd2, cb));
-                        st.dgam[i][j] = __ffma2_rn(__fmul2_rn(dv[j], c), rstd2, st.dgam[i][j]);
+                        if constexpr (GRADS) st.dgam[i][j] = __ffma2_rn(__fmul2_rn(dv[j], c), rstd2, st.dgam[i][j]);
                     }
-                    st.dbet[i][j] = __fadd2_rn(st.dbet[i][j], dv[j]);
+                    if constexpr (GRADS) st.dbet[i][j] = __fadd2_rn(st.dbet[i][j], dv[j]);
                 }
                 __stcs(out + v, PairVec<T>::pack(o));
             }
         }
     }
     __device__ __forceinline__ static void finish(State& st, const NormParams& p, int cluster, int cols, int col0, int nvec) {
+        if constexpr (!GRADS) return;
         float* out_g = p.partials + (static_cast<size_t>(cluster) * 2 + 0) * cols + col0;
         float* out_b = p.partials + (static_cast<size_t>(cluster) * 2 + 1) * cols + col0;
 #pragma unroll
@@ -658,6 +668,118 @@ struct LayerNormBwdOp {
             }
         }
     }
+};
+
+template <typename T, int OUT_WARPS, int VPT, bool FULL>
+using LayerNormBwdOp = LayerNormBwdGivenOp<T, OUT_WARPS, VPT, FULL, true>;
+template <typename T, int OUT_WARPS, int VPT, bool FULL>
+using LayerNormBwdDxOp = LayerNormBwdGivenOp<T, OUT_WARPS, VPT, FULL, false>;
+
+// ---------------------------------------------------------------------------
+// LayerNorm backward as the reference states it (dsmem_eval/workloads.py:53-61): the row's mean
+// and variance are recomputed from x and only dx is written. One pass over the staged slice
+// gathers a record of four sums about the row's shift K (the median of three samples, published
+// by the collector warp): with d = x - K and g = dy * gamma,
+//   A = sum d, B = sum d^2, C = sum g, D = sum g * d.
+// Then m = A / N, mean = K + m, var = B / N - m^2, S1 = C, S2 = sum g * (x - mean) = D - m * C and
+//   dx = g * rstd + (d - m) * (-rstd^3 * S2 / N) + (-rstd * S1 / N).
+// The record of four floats per thread bounds the kernel to 8 output warps (control block size).
+// ---------------------------------------------------------------------------
+template <typename T, int OUT_WARPS, int VPT, bool FULL>
+struct LayerNormBwdRecomputeOp {
+    using Elem = T;
+    static constexpr int kInputs = 2, kOutWarps = OUT_WARPS, kVectors = VPT, THREADS = OUT_WARPS * 32;
+    static constexpr bool kFull = FULL;
+    static constexpr int E = PairVec<T>::kElems, PAIRS = PairVec<T>::kPairs;
+    static constexpr int kPartials = 4, kLocalBuffers = 4;
+    static constexpr bool kAdditive = true, kRegisterSlice = true;
+    __device__ __forceinline__ static void identity(float (&v)[4]) { v[0] = v[1] = v[2] = v[3] = 0.0f; }
+    __device__ __forceinline__ static void combine(float (&v)[4], const float (&o)[4]) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) v[k] += o[k];
+    }
+    struct State {
+        float2 gam[VPT][PAIRS];
+    };
+    __device__ __forceinline__ static void sources(const NormParams& p, const T* (&src)[2]) {
+        src[0] = static_cast<const T*>(p.x);
+        src[1] = static_cast<const T*>(p.dy);
+    }
+    __device__ __forceinline__ static WsRow fetch_row(const NormParams& p, int row, int cols) {
+        const T* r = static_cast<const T*>(p.x) + static_cast<size_t>(row) * cols;
+        return WsRow{RowVec<T>::to_float(__ldg(r)), RowVec<T>::to_float(__ldg(r + (cols >> 1))),
+                     RowVec<T>::to_float(__ldg(r + (cols - 1)))};
+    }
+    static constexpr bool kRowInfo = true;
+    __device__ __forceinline__ static float4 publish_row(const WsRow& r) {
+        return make_float4(fmaxf(fminf(r.a, r.b), fminf(fmaxf(r.a, r.b), r.c)), 0.0f, 0.0f, 0.0f);
+    }
+    __device__ __forceinline__ static void init(State& st, const NormParams& p, int col0, int nvec) {
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+            const int v = threadIdx.x + i * THREADS;
+#pragma unroll
+            for (int j = 0; j < PAIRS; ++j) st.gam[i][j] = splat(0.0f);
+            if (FULL || v < nvec) load_param_pairs<PAIRS>(p.gamma + col0 + v * E, st.gam[i]);
+        }
+    }
+    __device__ __forceinline__ static void pass1(State& st, const uint4* const (&tiles)[2], int nvec, const float4& r,
+                                                 float (&part)[4]) {
+        const float2 neg_shift = splat(-r.x);
+        float2 sa = splat(0.0f), sb = splat(0.0f), sc = splat(0.0f), sd = splat(0.0f);
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+            const int v = threadIdx.x + i * THREADS;
+            if (FULL || v < nvec) {
+                float2 xv[PAIRS], dv[PAIRS];
+                PairVec<T>::unpack(tiles[0][v], xv);
+                PairVec<T>::unpack(tiles[1][v], dv);
+#pragma unroll
+                for (int j = 0; j < PAIRS; ++j) {
+                    const float2 d = __fadd2_rn(xv[j], neg_shift);
+                    const float2 gg = __fmul2_rn(dv[j], st.gam[i][j]);
+                    sa = __fadd2_rn(sa, d);
+                    sb = __ffma2_rn(d, d, sb);
+                    sc = __fadd2_rn(sc, gg);
+                    sd = __ffma2_rn(gg, d, sd);
+                }
+            }
+        }
+        part[0] = sa.x + sa.y;
+        part[1] = sb.x + sb.y;
+        part[2] = sc.x + sc.y;
+        part[3] = sd.x + sd.y;
+    }
+    __device__ __forceinline__ static void pass2(State& st, const uint4* const (&tiles)[2], int nvec, const float4& r,
+                                                 const float (&sums)[4], const NormParams& p, int row, int cols, int col0,
+                                                 uint32_t) {
+        const float inv_cols = 1.0f / static_cast<float>(cols);
+        const float m = sums[0] * inv_cols;
+        const float var = fmaxf(sums[1] * inv_cols - m * m, 0.0f);
+        const float rstd = rsqrtf(var + p.eps);
+        const float s2 = fmaf(-m, sums[2], sums[3]);
+        const float2 neg_center = splat(-(r.x + m)), rstd2 = splat(rstd);
+        const float2 ca = splat(-rstd * rstd * rstd * (s2 * inv_cols));
+        const float2 cb = splat(-rstd * (sums[2] * inv_cols));
+        uint4* out = reinterpret_cast<uint4*>(static_cast<T*>(p.y) + static_cast<size_t>(row) * cols + col0);
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+            const int v = threadIdx.x + i * THREADS;
+            if (FULL || v < nvec) {
+                float2 xv[PAIRS], dv[PAIRS], o[PAIRS];
+                PairVec<T>::unpack(tiles[0][v], xv);
+                PairVec<T>::unpack(tiles[1][v], dv);
+#pragma unroll
+                for (int j = 0; j < PAIRS; ++j) {
+                    const float2 gg = __fmul2_rn(dv[j], st.gam[i][j]);
+                    const float2 c = __fadd2_rn(xv[j], neg_center);
+                    o[j] = __ffma2_rn(c, ca, __ffma2_rn(gg, rstd2, cb));
+                }
+                __stcs(out + v, PairVec<T>::pack(o));
+            }
+        }
+    }
+    __device__ __forceinline__ static void finish(State&, const NormParams&, int, int, int, int) {}
 };
 
 }  // namespace credit

@@ -399,7 +399,7 @@ def test_layernorm_backward_stats_register_paths(opts, cluster_size):
                          BF16_RTOL)
 
 
-@pytest.mark.parametrize("stages", [0, 3, 4, 5, 8])
+@pytest.mark.parametrize("stages", [0, 3, 4, 5, 8, 16])
 @pytest.mark.parametrize("cluster_size", [1, 2, 4, 8, 16])
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
 @pytest.mark.parametrize("threads", [608, 352])
@@ -418,7 +418,7 @@ def test_layernorm_backward_stats_warp_specialised_kernel(threads, dtype, cluste
         assert plan.threads == threads and plan.stages >= 3
 
 
-@pytest.mark.parametrize("stages", [0, 3, 5])
+@pytest.mark.parametrize("stages", [0, 3, 5, 13])
 @pytest.mark.parametrize("cluster_size", [1, 2, 4, 8, 16])
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
 @pytest.mark.parametrize("threads", [608, 352])
@@ -440,15 +440,73 @@ def test_forward_warp_specialised_kernels(threads, dtype, cluster_size, stages):
         assert N.plan(N.WL_LAYERNORM_FORWARD, rows, cols, code, dict(opts, cluster_size=cluster_size)).threads == threads
 
 
+@pytest.mark.parametrize("stages", [0, 3, 5])
+@pytest.mark.parametrize("cluster_size", [1, 2, 4, 8, 16])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_layernorm_backward_reference_form_warp_specialised_kernel(dtype, cluster_size, stages):
+    """The reference form (statistics recomputed from the row, layernorm_backward.cu:217-251 does it
+    with two exchanges) as one pass with a record of four shifted sums: many rows per cluster so the
+    buffers wrap, a ragged width, a wide row, and rows far from zero (mean 1000, std 0.01) where an
+    unshifted sum of squares would cancel."""
+    opts = {"threads": 352, "stages": stages}
+    rtol = BF16_RTOL if dtype == torch.bfloat16 else FP32_RTOL
+    code = N.BF16 if dtype == torch.bfloat16 else N.F32
+    for rows, cols in ((3100, 4096), (2999, 1096), (40, 16384 * cluster_size if cluster_size <= 4 else 65536)):
+        x, dy, gamma = W.make_layernorm_inputs(rows, cols, "cpu", seed=rows + cols)
+        x, dy = x.to(dtype), dy.to(dtype)
+        try:
+            (dx,) = run("layernorm_backward", (x, dy, gamma), cluster_size, opts)
+        except N.UnsupportedShape:
+            assert cols > 4096   # only the wide row may exceed a small cluster's shared memory
+            continue
+        close(dx, O.layernorm_backward(x.double(), dy.double(), gamma.double()), rtol, scale=2.0, what="dx")
+        assert N.plan(N.WL_LAYERNORM_BACKWARD, rows, cols, code, dict(opts, cluster_size=cluster_size)).threads == 352
+    if dtype == torch.float32:
+        rows, cols = 64, 8192
+        x, dy, gamma = W.make_layernorm_inputs(rows, cols, "cpu", seed=5)
+        x = (1000.0 + 0.01 * torch.randn(rows, cols, generator=torch.Generator().manual_seed(9))).float()
+        (dx,) = try_run("layernorm_backward", (x, dy, gamma), cluster_size, opts)
+        want = O.layernorm_backward(x.double(), dy.double(), gamma.double())
+        # dx ~ 1 / std = 100 here; fp32 x carries 6e-5 of rounding on a spread of 1e-2, which the
+        # oracle sees too (same inputs), so the usual bound holds at that scale
+        close(dx, want, 2e-3, scale=float(want.abs().max()), what="dx far from zero")
+
+
+@pytest.mark.parametrize("cluster_size", [1, 2, 4, 8, 16])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("threads", [608, 352])
+def test_layernorm_backward_stats_dx_only_warp_specialised_kernel(threads, dtype, cluster_size):
+    opts = {"threads": threads}
+    for rows, cols in ((3100, 4096), (2999, 1096)):
+        inputs = W.make_layernorm_backward_stats_inputs(rows, cols, "cpu", seed=rows, dtype=dtype)
+        dev_inputs = to_dev(inputs)
+        dx = torch.empty_like(dev_inputs[0])
+        try:
+            L.launch_layernorm_backward_stats(dev_inputs, (dx,), cluster_size, opts)
+        except N.UnsupportedShape:
+            continue
+        torch.cuda.synchronize()
+        want_dx, _, _ = O.layernorm_backward_stats(*inputs, dtype=torch.float64)
+        close(dx.cpu(), want_dx, BF16_RTOL if dtype == torch.bfloat16 else FP32_RTOL, scale=2.0, what="dx")
+
+
 def test_layernorm_backward_stats_automatic_plan_is_warp_specialised():
     plan = N.plan(N.WL_LAYERNORM_BACKWARD_STATS, 8192, 65536, N.BF16)
     assert (plan.threads, plan.cluster_size, plan.vectors_per_thread, plan.full_tiles) == (352, 8, 4, 1)
     assert plan.stages == 6 and plan.smem_bytes == 22528 + 6 * 32768
+    # the reference's own workload at its largest sweep shape, and dx only with given statistics
+    plan = N.plan(N.WL_LAYERNORM_BACKWARD, 2048, 65536, N.F32)
+    assert (plan.threads, plan.cluster_size, plan.stages) == (352, 8, 3)   # 16 never replaces an 8 that fits
+    # the smallest cluster whose ring has four stages; short slices keep to half of the shared memory
+    plan = N.plan(N.WL_LAYERNORM_BACKWARD, 2048, 8192, N.F32)
+    assert (plan.cluster_size, plan.stages) == (2, 6)
+    plan = N.plan(N.WL_LAYERNORM_FORWARD, 4096, 4096, N.BF16)
+    assert (plan.cluster_size, plan.stages) == (1, 8) and plan.smem_bytes <= 113 * 1024
     # the forward kernels at their target shapes: same pipeline
     plan = N.plan(N.WL_LAYERNORM_FORWARD, 4096, 131072, N.BF16)
     assert (plan.threads, plan.cluster_size, plan.vectors_per_thread) == (352, 8, 8)
     plan = N.plan(N.WL_RMSNORM_FORWARD, 1024, 32768, N.F32)
-    assert plan.threads == 352 and plan.cluster_size in (8, 16)
+    assert (plan.threads, plan.cluster_size, plan.stages) == (352, 4, 6)
     # explicit thread counts keep the lock-step register kernels
     assert N.plan(N.WL_LAYERNORM_BACKWARD_STATS, 8192, 65536, N.BF16, {"threads": 512}).threads == 512
 
