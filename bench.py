@@ -54,8 +54,12 @@ ROW_CASES = [
     ("rmsnorm_forward", "rmsnorm_forward", 1024, 32768),
     ("layernorm_forward", "layernorm_forward", 4096, 131072),
     ("layernorm_backward_stats", "layernorm_backward_stats", 8192, 65536),
+    # the reference's own workload (statistics recomputed, dx only) at the largest shape of its sweep
+    ("layernorm_backward_reference_form", "layernorm_backward", 2048, 65536),
 ]
+E2E_KEYS = ("rmsnorm_forward", "layernorm_forward", "layernorm_backward_stats")   # workloads with a host-buffer entry point
 OTHER_ITERS = 50
+SUSTAINED_S = 1.5     # length of the back-to-back run reported beside each burst figure
 
 
 def measured_peaks() -> dict:
@@ -208,10 +212,12 @@ def cpu_baseline_for(key: str, budget_s: float = 4.0) -> dict:
         what, total = "torch CPU fp32 matmul + erf GELU + RMSNorm", m
     else:
         name, rows, cols = next((w, r, c) for k, w, r, c in ROW_CASES if k == key)
-        sample = {"rmsnorm_forward": 128, "layernorm_forward": 32, "layernorm_backward_stats": 64}[key]
+        sample = {"rmsnorm_forward": 128, "layernorm_forward": 32, "layernorm_backward_stats": 64,
+                  "layernorm_backward_reference_form": 64}[key]
         ins = W.WORKLOADS[name].input_factory(sample, cols, "cpu")
         fn = {"rmsnorm_forward": O.rmsnorm_forward, "layernorm_forward": O.layernorm_forward,
-              "layernorm_backward_stats": O.layernorm_backward_stats}[key]
+              "layernorm_backward_stats": O.layernorm_backward_stats,
+              "layernorm_backward_reference_form": O.layernorm_backward}[key]
         med, n = time_cpu(lambda: fn(*ins), budget_s)
         what, total = "torch CPU, fp32 arithmetic", rows
     return {"value": sample / med, "unit": "rows/s", "cores": cores, "kind": "port",
@@ -350,7 +356,7 @@ def measure_row_case(key: str, name: str, rows: int, cols: int, dev, sampler, pe
 
     case = RowCase(name, rows, cols, dev)
     wl = {"rmsnorm_forward": N.WL_RMSNORM_FORWARD, "layernorm_forward": N.WL_LAYERNORM_FORWARD,
-          "layernorm_backward_stats": N.WL_LAYERNORM_BACKWARD_STATS}[name]
+          "layernorm_backward_stats": N.WL_LAYERNORM_BACKWARD_STATS, "layernorm_backward": N.WL_LAYERNORM_BACKWARD}[name]
     plan = N.plan(wl, rows, cols, N.BF16 if case.dtype == torch.bfloat16 else N.F32)
     ms, window, iters = timed_ms(case.call, OTHER_ITERS, min_region_ms=120.0)
     achieved = case.bytes / ms / 1e6
@@ -366,6 +372,15 @@ def measure_row_case(key: str, name: str, rows: int, cols: int, dev, sampler, pe
         "gpu_launches": iters * plan.kernel_launches,
         "clocks": sampler.summary([window]),
     }
+    # The same call back to back for SUSTAINED_S seconds: these kernels draw the board's 1000 W limit
+    # after about 0.1 s of continuous streaming, the SM clock settles near 1.7 GHz, and a kernel whose
+    # output warps are close to their issue limit slows with it (a pure stream does not).
+    s_ms, s_window, s_iters = timed_ms(case.call, max(OTHER_ITERS, int(SUSTAINED_S * 1e3 / ms) + 1), warmup=0)
+    s_achieved = case.bytes / s_ms / 1e6
+    entry["sustained"] = {"ms": round(s_ms, 4), "iters": s_iters, "seconds": round(s_window[1] - s_window[0], 2),
+                          "gbps": round(s_achieved, 1), "frac": s_achieved / peaks["hbm_gbs"],
+                          "clocks": sampler.summary([s_window])}
+    entry["gpu_launches"] += s_iters * plan.kernel_launches
     if with_e2e:
         try:
             entry["e2e"] = e2e_row_case(key, case, dev)
@@ -442,7 +457,7 @@ def others_single_gpu(dev, sampler, peaks) -> dict:
     out = {}
     # the FFN first (tensor-bound, power-capped), before the memory-bound kernels have heated the GPU
     for key, fn in [("ffn_forward", lambda: measure_ffn(dev, sampler, peaks))] + [
-            (key, (lambda k=key, n=name, r=rows, c=cols: measure_row_case(k, n, r, c, dev, sampler, peaks, True)))
+            (key, (lambda k=key, n=name, r=rows, c=cols: measure_row_case(k, n, r, c, dev, sampler, peaks, k in E2E_KEYS)))
             for key, name, rows, cols in ROW_CASES]:
         try:
             out[key] = fn()

@@ -195,12 +195,6 @@ __device__ __forceinline__ bool mbar_wait_parked_bounded(uint32_t bar, uint32_t 
     return false;
 }
 
-// One poll, then the suspending wait: for warps that usually find the phase complete.
-__device__ __forceinline__ bool mbar_wait_polled_then_parked(uint32_t bar, uint32_t parity, int* status) {
-    if (mbar_poll(bar, parity)) return true;
-    return mbar_wait_parked_bounded(bar, parity, status);
-}
-
 // One bulk copy global -> this CTA's shared memory, completion counted in bytes
 // on `bar`. src, dst and bytes must all be multiples of 16.
 __device__ __forceinline__ void bulk_load(uint32_t dst_smem, const void* src_gmem, uint32_t bytes,

@@ -454,7 +454,13 @@ int plan_static(int workload, const Shape& s, int dtype, const credit_launch_opt
     const bool ws_workload = wide_only ? o.threads != kWsThreadsPerCta
                                        : (workload == CREDIT_WL_RMSNORM_FORWARD || workload == CREDIT_WL_LAYERNORM_FORWARD ||
                                           workload == CREDIT_WL_LAYERNORM_BACKWARD_STATS);
-    if (ws_workload && p->aligned && !(o.flags & CREDIT_FLAG_NO_REGISTER_PATH) && (o.threads == 0 || ws_threads) &&
+    // fp32 RMSNorm keeps the lock-step register kernel unless threads asks otherwise: with 512 threads
+    // and the smallest cluster whose slice fits them it ran 1024 x 32768 in 45.1 us against 46.4 - 50.3 us
+    // for every warp-specialised form (4096 x 32768: 163 us against 170 - 184 us), and within 4 % of the
+    // best form at the other row lengths from 4096 to 65536.
+    const bool lock_step_default = workload == CREDIT_WL_RMSNORM_FORWARD && dtype == CREDIT_F32 && o.threads == 0;
+    if (ws_workload && !lock_step_default && p->aligned && !(o.flags & CREDIT_FLAG_NO_REGISTER_PATH) &&
+        (o.threads == 0 || ws_threads) &&
         o.schedule != CREDIT_SCHEDULE_ROW_PER_CLUSTER && (o.stages == 0 || o.stages >= 3) &&
         o.variant != CREDIT_VARIANT_BLOCK_SMEM) {
         // measured at the target shapes: 8 output warps with twice the elements per thread win over 16
@@ -564,7 +570,7 @@ int plan_static(int workload, const Shape& s, int dtype, const credit_launch_opt
         const int max_vpt = max_elems_per_thread(workload, grads) / s.vec_elems;
         const int nvec = p->slice_elems / s.vec_elems;
         int threads = o.threads;
-        if (threads == 0) threads = nvec > 256 * max_vpt ? 512 : 256;
+        if (threads == 0) threads = (nvec > 256 * max_vpt || (lock_step_default && nvec >= 512)) ? 512 : 256;
         int vpt = 1;
         while (vpt * threads < nvec) vpt *= 2;
         // slices read twice from their stage need three stages; a caller who asks for fewer gets
@@ -729,6 +735,8 @@ void choose_cluster_by_model(int device, const DeviceState& dev, int workload, c
                              bool pointers_aligned, bool grads, credit_launch_opts* o) {
     if (o->cluster_size != 0 || s.rows == 0 || !dev.info.cluster_launch) return;
     if (workload == CREDIT_WL_ROW_REDUCE) return;
+    // fp32 RMSNorm: plan_static's smallest-fit rule for the lock-step kernel (see there)
+    if (workload == CREDIT_WL_RMSNORM_FORWARD && dtype == CREDIT_F32 && o->threads == 0) return;
     // Reference-sweep workloads: plan_static's measured rule (the smallest cluster whose ring is deep
     // enough) decides for both of their kernel families.
     if (is_row_op(workload)) return;

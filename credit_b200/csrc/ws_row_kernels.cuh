@@ -54,12 +54,6 @@
 #include "norm_kernels.cuh"
 #include "register_row_kernels.cuh"
 
-#ifdef CREDIT_WS_OUTPUT_PARK
-#define WS_OUT_WAIT mbar_wait_polled_then_parked
-#else
-#define WS_OUT_WAIT mbar_wait_bounded
-#endif
-
 namespace credit {
 
 constexpr int kWsMaxOutputWarps = 16;
@@ -317,7 +311,7 @@ ws_row_kernel(NormParams prm, StagedArgs a) {
     for (int it = 0; it < my_rows + ahead; ++it) {
         // ---- pass 1 of row `it`: this thread's share of the row's sums
         if (it < my_rows) {
-            if (g.local > 0) WS_OUT_WAIT(smem_u32(&ctl.full[stage1]), parity1, a.status);
+            if (g.local > 0) mbar_wait_bounded(smem_u32(&ctl.full[stage1]), parity1, a.status);
             const uint4* tiles[NIN];
 #pragma unroll
             for (int n = 0; n < NIN; ++n)
@@ -326,7 +320,7 @@ ws_row_kernel(NormParams prm, StagedArgs a) {
             float4 info = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
             if (Op::kRowInfo) {
                 const int ib = it & (kWsSlotBuffers - 1);
-                WS_OUT_WAIT(smem_u32(&ctl.info_bar[ib]), (static_cast<uint32_t>(it) / kWsSlotBuffers) & 1u, a.status);
+                mbar_wait_bounded(smem_u32(&ctl.info_bar[ib]), (static_cast<uint32_t>(it) / kWsSlotBuffers) & 1u, a.status);
                 info = ctl.row_info[ib];
             }
             float part[KP];
@@ -345,7 +339,7 @@ ws_row_kernel(NormParams prm, StagedArgs a) {
             const int it2 = it - ahead;
             const int row = cluster + it2 * a.num_clusters;
             const int xb = it2 & (kWsSlotBuffers - 1);
-            WS_OUT_WAIT(smem_u32(&ctl.ready_bar[xb]), (static_cast<uint32_t>(it2) / kWsSlotBuffers) & 1u, a.status);
+            mbar_wait_bounded(smem_u32(&ctl.ready_bar[xb]), (static_cast<uint32_t>(it2) / kWsSlotBuffers) & 1u, a.status);
             float sums[KP];
             ws_load_record<KP>(&ctl.total[xb][0], sums);
             // the row's scalars were published before its pass 1, which this warp has run

@@ -505,8 +505,10 @@ def test_layernorm_backward_stats_automatic_plan_is_warp_specialised():
     # the forward kernels at their target shapes: same pipeline
     plan = N.plan(N.WL_LAYERNORM_FORWARD, 4096, 131072, N.BF16)
     assert (plan.threads, plan.cluster_size, plan.vectors_per_thread) == (352, 8, 8)
+    assert N.plan(N.WL_RMSNORM_FORWARD, 1024, 32768, N.BF16).threads == 352
+    # fp32 RMSNorm: the lock-step register kernel, smallest cluster whose slice fits 512 threads
     plan = N.plan(N.WL_RMSNORM_FORWARD, 1024, 32768, N.F32)
-    assert (plan.threads, plan.cluster_size, plan.stages) == (352, 4, 6)
+    assert (plan.threads, plan.cluster_size, plan.vectors_per_thread) == (512, 4, 4)
     # explicit thread counts keep the lock-step register kernels
     assert N.plan(N.WL_LAYERNORM_BACKWARD_STATS, 8192, 65536, N.BF16, {"threads": 512}).threads == 512
 
