@@ -304,6 +304,64 @@ __global__ void tma_latency_kernel(const unsigned char* __restrict__ src, size_t
     }
 }
 
+// DSMEM bulk copy: the CTAs of the cluster work in pairs (ranks 2i, 2i + 1); each copies `bytes` from
+// its own shared memory into its partner's with cp.async.bulk (shared::cta -> shared::cluster),
+// completion counted in bytes on the RECEIVER's mbarrier, and a step ends when the partner's copy
+// has landed here. A CTA can be at most one step ahead of its partner (its next step needs the
+// partner's copy of this one), and two buffers and two barriers alternate, so a copy never meets a
+// barrier phase that is still in use.
+// cycles[0]: one copy in flight per step (latency of arm + copy + wait); cycles[1]: kBulkDepth
+// copies of `bytes` in flight per step (throughput).
+constexpr int kBulkIters = 256;
+constexpr int kBulkDepth = 4;
+constexpr int kBulkMaxBytes = 16384;
+
+__device__ __forceinline__ void bulk_copy_to_peer(uint32_t remote_dst, uint32_t local_src, uint32_t bytes,
+                                                  uint32_t remote_bar) {
+    asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                     remote_dst),
+                 "r"(local_src), "r"(bytes), "r"(remote_bar)
+                 : "memory");
+}
+
+__global__ void __launch_bounds__(32) dsmem_bulk_kernel(int bytes, long long* cycles, int* status) {
+    extern __shared__ __align__(128) unsigned char dyn[];   // source | 2 x kBulkDepth landing buffers
+    __shared__ uint64_t bars[2];
+    const uint32_t rank = cluster_cta_rank();
+    const uint32_t next = rank ^ 1u;   // the partner (cluster sizes are even)
+    unsigned char* src = dyn;
+    unsigned char* landing = dyn + kBulkMaxBytes;
+    for (int i = threadIdx.x; i < kBulkMaxBytes / 4; i += 32) reinterpret_cast<uint32_t*>(src)[i] = i + rank;
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(&bars[0]), 1);
+        mbar_init(smem_u32(&bars[1]), 1);
+        fence_mbar_init();
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the source is read by the async proxy
+    __syncthreads();
+    cluster_sync_all();
+    if (threadIdx.x == 0) {
+        uint32_t step = 0;
+        bool ok = true;
+        for (int mode = 0; mode < 2; ++mode) {
+            const int depth = mode == 0 ? 1 : kBulkDepth;
+            const long long t0 = clock64();
+            for (int i = 0; i < kBulkIters && ok; ++i, ++step) {
+                const uint32_t b = step & 1u;
+                const uint32_t my_bar = smem_u32(&bars[b]);
+                mbar_arrive_expect_tx(my_bar, static_cast<uint32_t>(depth * bytes));
+                for (int d = 0; d < depth; ++d)
+                    bulk_copy_to_peer(map_to_rank(smem_u32(landing + (b * kBulkDepth + d) * kBulkMaxBytes), next),
+                                      smem_u32(src), static_cast<uint32_t>(bytes), map_to_rank(my_bar, next));
+                ok = mbar_wait_bounded(my_bar, (step >> 1) & 1u, status);
+            }
+            if (rank == 0) cycles[mode] = clock64() - t0;
+        }
+    }
+    __syncthreads();
+    cluster_sync_all();   // nobody leaves while a peer may still copy into it
+}
+
 // ------------------------------------------------------------------ host helpers
 struct Summary { double lo, med, hi; };
 
@@ -525,6 +583,51 @@ int main(int argc, char** argv) {
         print_metric(label, "B/cycle/CTA", summarize(r.remote_read_cycles, 0, true, tp_bytes));
         std::snprintf(label, sizeof(label), "Cluster %2d DSMEM store throughput", P);
         print_metric(label, "B/cycle/CTA", summarize(r.remote_store_cycles, 0, true, tp_bytes));
+    }
+
+    // ---- DSMEM bulk copy (shared memory of one CTA -> shared memory of the next CTA of the cluster)
+    {
+        const int bulk_smem = kBulkMaxBytes * (1 + 2 * kBulkDepth);
+        CHECK(cudaFuncSetAttribute(dsmem_bulk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bulk_smem));
+        CHECK(cudaFuncSetAttribute(dsmem_bulk_kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
+        long long* d_bulk = nullptr;
+        int* d_status = nullptr;
+        CHECK(cudaMalloc(&d_bulk, 2 * sizeof(long long)));
+        CHECK(cudaMalloc(&d_status, sizeof(int)));
+        CHECK(cudaMemset(d_status, 0, sizeof(int)));
+        for (auto& pr : all) {
+            const int P = pr.first;
+            if (P != 2 && P != 8 && P != 16) continue;
+            for (int bytes : {256, 1024, 4096, 16384}) {
+                cudaLaunchConfig_t cfg{};
+                cfg.gridDim = dim3(P);
+                cfg.blockDim = dim3(32);
+                cfg.dynamicSmemBytes = bulk_smem;
+                cudaLaunchAttribute attr{};
+                attr.id = cudaLaunchAttributeClusterDimension;
+                attr.val.clusterDim.x = P;
+                attr.val.clusterDim.y = 1;
+                attr.val.clusterDim.z = 1;
+                cfg.attrs = &attr;
+                cfg.numAttrs = 1;
+                CHECK(cudaMemset(d_bulk, 0, 2 * sizeof(long long)));
+                CHECK(cudaLaunchKernelEx(&cfg, dsmem_bulk_kernel, bytes, d_bulk, d_status));
+                CHECK(cudaDeviceSynchronize());
+                long long c[2] = {0, 0};
+                CHECK(cudaMemcpy(c, d_bulk, sizeof(c), cudaMemcpyDeviceToHost));
+                char label[96];
+                std::snprintf(label, sizeof(label), "Cluster %2d DSMEM bulk %5d B step", P, bytes);
+                std::printf("%-34s : %9.2f cycles  (%.2f B/cycle/CTA with %d copies in flight)\n", label,
+                            static_cast<double>(c[0]) / kBulkIters,
+                            c[1] > 0 ? static_cast<double>(kBulkDepth) * bytes * kBulkIters / static_cast<double>(c[1]) : 0.0,
+                            kBulkDepth);
+            }
+        }
+        int st = 0;
+        CHECK(cudaMemcpy(&st, d_status, sizeof(int), cudaMemcpyDeviceToHost));
+        if (st) std::printf("DSMEM bulk copy waits timed out (status %d)\n", st);
+        cudaFree(d_bulk);
+        cudaFree(d_status);
     }
 
     // ---- bulk-async load latency from DRAM

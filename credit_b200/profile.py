@@ -74,6 +74,13 @@ def parse_primitive_output(output: str) -> dict[str, Any]:
         int(m.group(1)): float(m.group(2))
         for m in re.finditer(rf"^Bulk copy\s+(\d+) B latency\s*:\s*{_FLOAT}\s+cycles", output, flags=re.MULTILINE)
     }
+    # DSMEM bulk copies (shared memory -> a peer CTA's shared memory): cluster size -> bytes ->
+    # (cycles per step with one copy in flight, bytes per cycle and CTA with several in flight)
+    dsmem_bulk: dict[int, dict[int, tuple[float, float]]] = {}
+    for m in re.finditer(rf"^Cluster\s+(\d+)\s+DSMEM bulk\s+(\d+) B step\s*:\s*{_FLOAT}\s+cycles\s+\({_FLOAT} B/cycle/CTA",
+                         output, flags=re.MULTILINE):
+        dsmem_bulk.setdefault(int(m.group(1)), {})[int(m.group(2))] = (float(m.group(3)), float(m.group(4)))
+    parsed["dsmem_bulk_copy"] = dsmem_bulk
     return parsed
 
 

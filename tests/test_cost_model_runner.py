@@ -34,6 +34,9 @@ def test_parse_primitive_output(parsed):
     assert parsed["per_cluster"][8]["mbarrier_exchange_cycles"] == pytest.approx(350.64)
     assert parsed["per_cluster"][16]["barrier_exchange_cycles"] == pytest.approx(1059.40)
     assert parsed["bulk_copy_latency_cycles"]
+    # cp.async.bulk between the shared memories of two CTAs: cycles per step, bytes per cycle and CTA
+    assert parsed["dsmem_bulk_copy"][8][16384] == pytest.approx((1149.17, 17.78))
+    assert sorted(parsed["dsmem_bulk_copy"]) == [2, 8, 16]
 
 
 def test_parse_primitive_output_missing_line(parsed):

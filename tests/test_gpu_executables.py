@@ -147,6 +147,14 @@ def test_primitive_benchmark_output_parses_into_a_device_profile():
     assert sorted(parsed["per_cluster"]) == [2, 4, 8, 16]
     for p, entry in parsed["per_cluster"].items():
         assert entry["mbarrier_exchange_cycles"] > 0 and entry["barrier_exchange_cycles"] > 0, p
+    # bulk copies between the shared memories of two CTAs of a cluster (cp.async.bulk, completion on the
+    # receiver's mbarrier): a step costs more than a DSMEM load, and larger copies move more bytes per cycle
+    assert "timed out" not in done.stdout
+    for p in (2, 8, 16):
+        bulk = parsed["dsmem_bulk_copy"][p]
+        assert sorted(bulk) == [256, 1024, 4096, 16384]
+        assert bulk[256][0] > parsed["dsmem_read_latency_cycles"] * 0.5
+        assert bulk[16384][1] > bulk[256][1] > 0
     device_profile = profile.make_device_profile(parsed, torch.cuda.get_device_properties(0))
     assert device_profile.sm_count == parsed["sm_count"]
     calibration = profile.make_b200_calibration(parsed)
@@ -173,3 +181,33 @@ def test_pipeline_quick_run_writes_the_bundle(tmp_path):
     # the saved bundle can be re-scored offline
     again = spawn([sys.executable, "-m", "credit_b200.runner", "--rescore", out])
     assert again.returncode == 0 and json.loads(again.stdout)["points"] == 6
+
+
+REFERENCE_BIN = ROOT / "oracle" / "_ref"
+REFERENCE_WORKLOADS = ("layernorm_backward", "weighted_var_backward", "pearson_backward", "softmax_logits_backward",
+                       "lars_momentum", "rowwise_quant")
+
+
+@pytest.mark.parametrize("name", REFERENCE_WORKLOADS)
+def test_beside_the_reference_binary(name, record_property):
+    """The reference's own executable (built from its sources into oracle/_ref by oracle/Makefile,
+    when those sources were at hand) and this project's, same flags, same GPU, at the reference's
+    default cluster size 8 and its largest sweep width: both verify their results in-binary, both
+    print the protocol `runner.parse_cuda_output` reads, and this project's cluster kernel is not
+    slower than the reference's (measured 1.4x - 2x faster)."""
+    ref = REFERENCE_BIN / name
+    if not ref.exists():
+        pytest.skip("oracle/_ref is not built here (needs the reference sources at build time)")
+    flags = ["--csv", "--n-values", "65536", "--warmup", 5, "--iters", 20, "--cluster-size", 8]
+    theirs = spawn([ref] + flags)
+    ours = spawn([BIN / name] + flags)
+    assert theirs.returncode == 0, theirs.stdout[-1500:] + theirs.stderr[-1500:]
+    assert ours.returncode == 0, ours.stdout[-1500:] + ours.stderr[-1500:]
+    (t,) = runner.parse_cuda_output(theirs.stdout)
+    (o,) = runner.parse_cuda_output(ours.stdout)
+    assert (t["cols"], t["rows"]) == (o["cols"], o["rows"])
+    record_property("reference_cluster_ms", t["cluster_ms"])
+    record_property("credit_b200_cluster_ms", o["cluster_ms"])
+    print(f"{name}: reference block {t['block_ms']:.4f} cluster {t['cluster_ms']:.4f} ms (P={t['cluster_size']}); "
+          f"credit_b200 block {o['block_ms']:.4f} cluster {o['cluster_ms']:.4f} ms (P={o['cluster_size']})")
+    assert o["cluster_ms"] <= t["cluster_ms"] * 1.02

@@ -84,7 +84,7 @@ def test_layernorm_forward_full(native_lib):
     r = sample_rows(rows)
     wy, wm, wr = O.layernorm_forward(x[r.to(DEV)].cpu(), gamma.cpu(), beta.cpu(), dtype=torch.float64)
     got = y[r.to(DEV)].cpu().double()
-    assert bool(((got - wy).abs() <= 2e-2 * wy.abs() + 2e-2).all())
+    assert bool(((got - wy).abs() <= 2e-2 * wy.abs() + 1e-3 * wy.pow(2).mean(-1, keepdim=True).sqrt()).all())
 
 
 def test_layernorm_backward_stats_full(native_lib):
@@ -111,7 +111,10 @@ def test_layernorm_backward_stats_full(native_lib):
     wdx, _, _ = O.layernorm_backward_stats(x[r].cpu(), dy[r].cpu(), gamma.cpu(), mean[r].cpu(), rstd[r].cpu(),
                                            dtype=torch.float64)
     got = dx[r].cpu().double()
-    assert bool(((got - wdx).abs() <= 2e-2 * wdx.abs() + 2e-2 * wdx.abs().max()).all())
+    # relative 2e-2 per element plus an absolute term of 1e-3 of the ROW's own rms (dx of a row is a
+    # difference of three terms of that size; the bf16 rounding of the result is 2^-9 of the element)
+    row_rms = wdx.pow(2).mean(-1, keepdim=True).sqrt()
+    assert bool(((got - wdx).abs() <= 2e-2 * wdx.abs() + 1e-3 * row_rms).all())
 
 
 def test_layernorm_backward_is_linear_in_dy_full_width(native_lib):
