@@ -101,6 +101,34 @@ def test_b200_model(parsed):
         cost_model.best_cluster_size([])
 
 
+def test_warp_specialised_row_period_model():
+    """predict_ws_ms on hand-computed cases (the planner's predicted_ws_ms in launch.cu is the same
+    formula with the same constants)."""
+    cal = cost_model.B200Calibration()
+    # C4: bf16 8192 x 65536, P = 8, 15 resident clusters, 6 stages: the output warps' issue time for
+    # 32 elements per thread is just above the CTA's share of HBM
+    p = cost_model.predict_ws_ms(8192, 65536, 8, 15, 352, 2, 2, 1, 6, backward=True, cal=cal)
+    per_sm = cal.hbm_gbps / 120
+    hbm_us = 3 * 8192 * 2 / (per_sm * 1e3)
+    issue_us = (cal.ws_fixed_cycles + cal.ws_cycles_per_element_bwd * 32) / (cal.clock_ghz * 1e3)
+    assert issue_us > hbm_us > 0.9 * issue_us
+    assert p.row_period_us == pytest.approx(issue_us) and p.rows_per_cluster == math.ceil(8192 / 15)
+    assert p.predicted_ms == pytest.approx(issue_us * (p.rows_per_cluster + cal.ws_fill_rows) * 1e-3)
+    assert 0.48 < p.predicted_ms < 0.56        # measured 0.487 burst, 0.553 sustained
+    # a short slice in a shallow ring: the loads in flight bound the row period (3 of 6 stages)
+    q = cost_model.predict_ws_ms(2048, 16384, 8, 15, 352, 4, 2, 1, 6, cal=cal)
+    assert q.row_period_us == pytest.approx(cal.ws_load_latency_us / 3)
+    # three stages: two between the passes, one in flight, and the short-ring factor on top
+    r = cost_model.predict_ws_ms(2048, 65536, 8, 15, 352, 4, 2, 1, 3, cal=cal)
+    assert r.row_period_us == pytest.approx(max(3 * 8192 * 4 / (per_sm * 1e3), cal.ws_load_latency_us) * cal.ws_short_ring_penalty)
+    # clusters of 16 carry their measured penalty
+    s16 = cost_model.predict_ws_ms(4096, 131072, 16, 7, 352, 2, 1, 1, 8, cal=cal)
+    s8 = cost_model.predict_ws_ms(4096, 131072, 8, 15, 352, 2, 1, 1, 6, cal=cal)
+    assert s16.predicted_ms > s8.predicted_ms
+    with pytest.raises(ValueError):
+        cost_model.predict_ws_ms(0, 4096, 8, 15, 352, 2, 1, 1, 6)
+
+
 def test_best_cluster_size_prefers_smaller_on_tie():
     p = [cost_model.ClusterPrediction(8, 1.0, 1, 1.0, 1.0), cost_model.ClusterPrediction(4, 1.0, 1, 1.0, 1.0)]
     assert cost_model.best_cluster_size(p) == 4
@@ -210,9 +238,9 @@ def test_rescore_bundle_round_trip(tmp_path, parsed):
         {"workload": "layernorm_backward_stats", "cols": 65536, "cluster_size": p, "delta_ms": 0.03} for p in (2, 8)])
     runner.write_csv(tmp_path / "plans.csv", [
         {"workload": "layernorm_backward_stats", "cols": 65536, "cluster_size": 2, "resident_clusters": 74,
-         "threads": 256, "register_path": 0},
+         "threads": 256, "register_path": 0, "library_cluster_size": 8},
         {"workload": "layernorm_backward_stats", "cols": 65536, "cluster_size": 8, "resident_clusters": 15,
-         "threads": 512, "register_path": 1}])
+         "threads": 512, "register_path": 1, "library_cluster_size": 8}])
     result = runner.rescore_bundle(tmp_path)
     assert result == {"points": 1, "b200_model_hits": 1, "b200_model_within_5pct": 1}
     with (tmp_path / "summary.csv").open() as f:
@@ -222,8 +250,9 @@ def test_rescore_bundle_round_trip(tmp_path, parsed):
         sweep = list(csv.DictReader(f))
     assert [r["register_path"] for r in sweep] == ["False", "True"]
     report = (tmp_path / "REPORT.md").read_text()
-    assert "picks the measured-best cluster size at 1/1 points" in report
-    assert "| layernorm_backward_stats | 65536 | 1930.0 | 1840.0 | 830.0 | 8 | 8 | 830.0 | yes |" in report
+    assert "would pick the measured-best size at 1/1 points" in report and "The library's planner" in report
+    assert "| layernorm_backward_stats | 65536 | 1930.0 | 1840.0 | 830.0 | 8 | 8 | 830.0 | yes | 8 |" in report
+    assert "planner (what cluster_size = 0 launches: a rule calibrated on B200 sweeps) picks the measured-best cluster size at 1/1" in report
     assert json.loads((tmp_path / "aggregate.json").read_text())["b200_model_within_5pct"] == 1
 
 
