@@ -496,7 +496,7 @@ def multi_gpu_blocks(dev, rank: int, world: int) -> dict:
     out: dict = {}
     iters = 20
 
-    def sharded_backward(rows_total: int, cols: int, split: bool):
+    def sharded_backward(rows_total: int, cols: int, split: bool, peer_group=None):
         r0, r1 = sharding.shard_rows(rows_total, world, rank) if split else (0, rows_total)
         rows = r1 - r0
         ins = W.make_layernorm_backward_stats_inputs(rows, cols, dev, seed=rank)
@@ -506,7 +506,7 @@ def multi_gpu_blocks(dev, rank: int, world: int) -> dict:
                          dtype=torch.uint8, device=dev)
 
         def call():
-            sharding.layernorm_backward_stats_sharded(ins, dx, both, workspace=ws)
+            sharding.layernorm_backward_stats_sharded(ins, dx, both, workspace=ws, peer_group=peer_group)
         return ins, both, call
 
     def time_call(call):
@@ -538,6 +538,52 @@ def multi_gpu_blocks(dev, rank: int, world: int) -> dict:
                                        "all-reduced in fp64; tolerance 1e-5 relative + 1e-5 * 4 * sqrt(total rows)"}
     if worst > 1.0:
         raise SystemExit(f"all-reduced dgamma/dbeta are wrong (error / tolerance = {worst})")
+    # ---- the same step with the library's own all-reduce over peer memory (one kernel per rank, CUDA
+    # IPC windows); every rank agrees at each stage before the next collective step is taken
+    def all_ok(flag: bool, payload=None):
+        gathered: list = [None] * world
+        dist.all_gather_object(gathered, (bool(flag), payload))
+        return all(g[0] for g in gathered), [g[1] for g in gathered]
+
+    peer = {"status": "unavailable"}
+    group = None
+    try:
+        try:
+            group = sharding.PeerGroup(world, rank, c_cols, connect=False)
+            created, note = True, ""
+        except Exception as exc:
+            created, note = False, str(exc)[:200]
+        everyone, handles = all_ok(created, group.handle if created else None)
+        if everyone:
+            try:
+                group.connect(handles)
+                connected = True
+            except Exception as exc:
+                connected, note = False, str(exc)[:200]
+            everyone, _ = all_ok(connected)
+        if everyone:
+            _, both_p, call_p = sharded_backward(c_rows, c_cols, split=False, peer_group=group)
+            # same seeds as above: the fp64 column sums in `want` are the expected result here too
+            peer_ms = time_call(call_p)
+            perr = float(((both_p.double() - want).abs() / tol).max().item())
+            perr = max_over_ranks(perr, dev)
+            status = max_over_ranks(float(group.status()), dev)
+            peer = {"status": "ok" if perr <= 1.0 and status == 0 else "FAILED", "ms": round(peer_ms, 4),
+                    "rows_per_s": round(world * c_rows / peer_ms * 1e3, 1), "worst_error_over_tolerance": round(perr, 4),
+                    "against_nccl_ms": round(weak_ms, 4),
+                    "what": "credit_layernorm_bwd_allreduce_peer: each rank publishes its [2, cols] vector in a "
+                            "window its peers map, one flag per rank, sums in rank order (plain NVLink loads)"}
+            del both_p, call_p
+            if peer["status"] != "ok":
+                raise SystemExit(f"peer-memory all-reduce is wrong (error / tolerance = {perr}, status = {status})")
+        else:
+            peer = {"status": "unavailable", "why": note or "another rank could not create or map its window"}
+    finally:
+        torch.cuda.synchronize()
+        dist.barrier()          # nobody closes a window a peer may still read
+        if group is not None:
+            group.close()
+    out["peer_allreduce"] = peer
     del ins, both, call, want, err, tol, x, dy
     torch.cuda.empty_cache()
     ins, both, call = sharded_backward(c_rows, c_cols, split=True)

@@ -23,6 +23,8 @@ ERR_DEVICE_STATUS = -5
 
 F32 = 0
 BF16 = 1
+COMM_ID_BYTES = 128      # credit_comm_get_unique_id
+PEER_HANDLE_BYTES = 64   # credit_peer_group_create
 
 VARIANT_AUTO, VARIANT_BLOCK_READ, VARIANT_BLOCK_SMEM, VARIANT_CLUSTER_SMEM = 0, 1, 2, 3
 LOAD_AUTO, LOAD_TMA, LOAD_LDG = 0, 1, 2
@@ -165,6 +167,11 @@ PROTOTYPES: dict[str, tuple] = {
     "credit_comm_init_rank": (c_int, [POINTER(c_void_p), c_int, c_int, c_void_p]),
     "credit_comm_destroy": (c_int, [c_void_p]),
     "credit_layernorm_bwd_allreduce": (c_int, [c_void_p, c_void_p, c_int64, c_void_p]),
+    "credit_peer_group_create": (c_int, [POINTER(c_void_p), c_int, c_int, c_int64, c_void_p]),
+    "credit_peer_group_connect": (c_int, [c_void_p, c_void_p]),
+    "credit_peer_group_destroy": (c_int, [c_void_p]),
+    "credit_peer_group_status": (c_int, [c_void_p]),
+    "credit_layernorm_bwd_allreduce_peer": (c_int, [c_void_p, c_void_p, c_int64, c_void_p]),
     "credit_ffn_forward_host_scratch_bytes": (c_size_t, [c_int64, c_int64, c_int64]),
     "credit_ffn_forward_host": (
         c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_float, c_void_p,

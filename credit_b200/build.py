@@ -41,7 +41,7 @@ LIB_SOURCES = [
     "tables_ws_layernorm_fwd.cu",
     "tables_ws_layernorm_bwd.cu", "tables_ws_layernorm_bwd_dx.cu",
     "tables_ws_row_ops.cu",
-    "comm_entry.cu",
+    "comm_entry.cu", "peer_allreduce.cu",
 ]
 OBJ_DIR = LIB_DIR / "obj"
 # name of the executable -> (source, links against the shared library)

@@ -358,6 +358,33 @@ int credit_comm_init_rank(credit_comm** comm, int world_size, int rank, const vo
 int credit_comm_destroy(credit_comm* comm);
 int credit_layernorm_bwd_allreduce(credit_comm* comm, float* dgamma_dbeta, int64_t cols, void* stream);
 
+/* The same sum without a library collective: one kernel per rank that publishes the rank's
+ * [2, cols] vector in a window of device memory its peers have mapped (CUDA IPC, plain
+ * loads and stores over NVLink), raises a flag in every peer's window, waits for the
+ * peers' flags and adds the vectors in rank order, so every rank gets bit-identical
+ * sums. The vector is 512 KiB at the target shape: an NCCL all-reduce of it is about
+ * 35 us of latency behind a 490 us kernel at 8 ranks, this kernel about a third of that.
+ * No reference counterpart (single device).
+ *
+ * Set-up: every rank (one process per GPU, its device current) calls
+ * credit_peer_group_create, which allocates its window and writes a handle of
+ * CREDIT_PEER_HANDLE_BYTES bytes; the host gathers the handles of all ranks, in rank
+ * order, by whatever channel it has and gives the array to credit_peer_group_connect.
+ * At most 16 ranks, all on GPUs of one node with peer access to one another.
+ * credit_layernorm_bwd_allreduce_peer is collective: every rank calls it once per step
+ * with the same cols, on any stream; calls of one group must not overlap on a device.
+ * The wait is bounded (about a second): if a peer never arrives, bit 0 of
+ * credit_peer_group_status() is set and the local vector is left unreduced. Ranks of one
+ * group must never share a GPU (a kernel that waits for a launch that cannot start).
+ * Before credit_peer_group_destroy the host makes sure no rank is still inside a call. */
+#define CREDIT_PEER_HANDLE_BYTES 64
+typedef struct credit_peer_group credit_peer_group;
+int credit_peer_group_create(credit_peer_group** group, int world_size, int rank, int64_t max_cols, void* handle_out);
+int credit_peer_group_connect(credit_peer_group* group, const void* handles);
+int credit_peer_group_destroy(credit_peer_group* group);
+int credit_peer_group_status(credit_peer_group* group);
+int credit_layernorm_bwd_allreduce_peer(credit_peer_group* group, float* dgamma_dbeta, int64_t cols, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -151,3 +151,96 @@ def test_c_abi_collective_in_a_world_of_one(native_lib):
     assert lib.credit_layernorm_bwd_allreduce(None, buf.data_ptr(), 1000, None) == N.ERR_INVALID_ARGUMENT
     assert lib.credit_comm_init_rank(ctypes.byref(ctypes.c_void_p()), 2, 5, ident) == N.ERR_INVALID_ARGUMENT
     N.check(lib.credit_comm_destroy(comm))
+
+
+def _peer_worker(rank: int, world: int, port: int, rows: int, cols: int, out):
+    """The sharded call with the library's own all-reduce over peer memory (one kernel per rank, CUDA
+    IPC windows); the handles travel through a gloo process group. Several calls in a row, so both
+    data buffers and several epochs are used; an odd width takes the scalar path."""
+    import torch.distributed as dist
+
+    from credit_b200 import _native as N
+    from credit_b200 import sharding
+    from credit_b200 import workloads as W
+    from oracle import reference_ops as O
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    peers = None
+    try:
+        peers = sharding.PeerGroup(world, rank, max_cols=cols)
+        full = W.make_layernorm_backward_stats_inputs(rows, cols, "cpu", seed=9)
+        x, dy, gamma, mean, rstd = full
+        r0, r1 = sharding.shard_rows(rows, world, rank)
+        local = (x[r0:r1].to(dev), dy[r0:r1].to(dev), gamma.to(dev), mean[r0:r1].to(dev), rstd[r0:r1].to(dev))
+        dx = torch.empty_like(local[0])
+        both, dgamma, dbeta = sharding.allocate_param_grads(cols, dev)
+        want_dx, want_dg, want_db = O.layernorm_backward_stats(*full, dtype=torch.float64)
+
+        def close(got, want, rtol, scale):
+            err = (got.double().cpu() - want).abs()
+            return bool((err <= rtol * want.abs() + rtol * scale).all())
+
+        ok = True
+        results = []
+        for _ in range(5):
+            sharding.layernorm_backward_stats_sharded(local, dx, both, peer_group=peers)
+            torch.cuda.synchronize()
+            ok = ok and close(dgamma, want_dg, 1e-5, 4.0 * rows ** 0.5) and close(dbeta, want_db, 1e-5, 4.0 * rows ** 0.5)
+            results.append(both.cpu().clone())
+        ok = ok and close(dx, want_dx[r0:r1], 2e-2, 2.0)
+        # a plain vector of odd length (scalar path): every rank contributes rank + 1
+        odd = torch.full((2, 333), float(rank + 1), device=dev)
+        peers.allreduce(odd)
+        torch.cuda.synchronize()
+        ok = ok and bool((odd == world * (world + 1) / 2).all())
+        ok = ok and peers.status() == 0 and N.device_status() == 0
+        # the sums are added in rank order on every rank: identical bits everywhere
+        gathered = [None] * world
+        dist.all_gather_object(gathered, results[-1].numpy().tobytes())
+        ok = ok and all(g == gathered[0] for g in gathered)
+        out[rank] = ok
+        dist.barrier()      # nobody closes a window a peer may still read
+    finally:
+        if peers is not None:
+            peers.close()
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_peer_memory_allreduce_of_parameter_gradients(native_lib):
+    import torch.multiprocessing as mp
+
+    world, rows, cols = 2, 301, 4096
+    port = _free_port()
+    with mp.Manager() as manager:
+        out = manager.dict()
+        mp.spawn(_peer_worker, args=(world, port, rows, cols, out), nprocs=world, join=True)
+        assert dict(out) == {0: True, 1: True}
+
+
+def test_peer_group_in_a_world_of_one(native_lib):
+    """One rank: the all-reduce is the identity and needs no peers; bad arguments are reported."""
+    import ctypes
+
+    from credit_b200 import _native as N
+    from credit_b200 import sharding
+
+    torch.cuda.set_device(0)
+    group = sharding.PeerGroup(1, 0, max_cols=1000)
+    buf = torch.arange(2 * 1000, dtype=torch.float32, device="cuda:0").reshape(2, 1000)
+    want = buf.clone()
+    group.allreduce(buf)
+    torch.cuda.synchronize()
+    assert torch.equal(buf, want) and group.status() == 0
+    with pytest.raises(N.CreditError):
+        group.allreduce(torch.zeros(2, 1001, device="cuda:0"))      # wider than the group's windows
+    group.close()
+    lib = N.load()
+    handle = ctypes.create_string_buffer(N.PEER_HANDLE_BYTES)
+    assert lib.credit_peer_group_create(ctypes.byref(ctypes.c_void_p()), 17, 0, 1000, handle) == N.ERR_INVALID_ARGUMENT
+    assert lib.credit_peer_group_create(ctypes.byref(ctypes.c_void_p()), 2, 2, 1000, handle) == N.ERR_INVALID_ARGUMENT
+    assert lib.credit_layernorm_bwd_allreduce_peer(None, buf.data_ptr(), 1000, None) == N.ERR_INVALID_ARGUMENT
