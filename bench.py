@@ -566,11 +566,18 @@ def multi_gpu_blocks(dev, rank: int, world: int) -> dict:
             # same seeds as above: the fp64 column sums in `want` are the expected result here too
             peer_ms = time_call(call_p)
             perr = float(((both_p.double() - want).abs() / tol).max().item())
+            # the collective alone, back to back on a scratch copy (values grow, timing does not care)
+            scratch_both = both_p.clone()
+            only_nccl = time_call(lambda: sharding.allreduce_param_grads(scratch_both))
+            scratch_both.copy_(both_p)
+            only_peer = time_call(lambda: group.allreduce(scratch_both))
+            del scratch_both
             perr = max_over_ranks(perr, dev)
             status = max_over_ranks(float(group.status()), dev)
             peer = {"status": "ok" if perr <= 1.0 and status == 0 else "FAILED", "ms": round(peer_ms, 4),
                     "rows_per_s": round(world * c_rows / peer_ms * 1e3, 1), "worst_error_over_tolerance": round(perr, 4),
                     "against_nccl_ms": round(weak_ms, 4),
+                    "allreduce_alone_us": {"nccl": round(only_nccl * 1e3, 1), "peer": round(only_peer * 1e3, 1)},
                     "what": "credit_layernorm_bwd_allreduce_peer: each rank publishes its [2, cols] vector in a "
                             "window its peers map, one flag per rank, sums in rank order (plain NVLink loads)"}
             del both_p, call_p

@@ -32,7 +32,7 @@ using credit::report_error;
 constexpr int kMaxPeerRanks = 16;
 constexpr size_t kFlagBytes = 4096;
 constexpr int kPeerThreads = 256;
-constexpr int kPeerMaxCtas = 64;
+constexpr int kPeerMaxCtas = 128;
 
 struct PeerPointers {
     unsigned char* window[kMaxPeerRanks];
@@ -109,24 +109,35 @@ peer_allreduce_kernel(float* __restrict__ local, PeerPointers peers, int world, 
     __syncthreads();
     if (gave_up) return;   // the sums would be wrong: leave the local vector as it was
 
-    // 3. add the vectors in rank order (the same order on every rank: identical results)
+    // 3. add the vectors in rank order (the same order on every rank: identical results). All loads of
+    // an element are issued before the first add, so their NVLink round trips overlap.
     if (vec) {
         for (int i = tid; i < n / 4; i += nthreads) {
+            float4 v[kMaxPeerRanks];
+#pragma unroll
+            for (int r = 0; r < kMaxPeerRanks; ++r)
+                if (r < world) v[r] = ld_volatile_f32x4(reinterpret_cast<const float*>(peers.window[r] + data_offset) + 4 * i);
             float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-            for (int r = 0; r < world; ++r) {
-                const float4 v = ld_volatile_f32x4(reinterpret_cast<const float*>(peers.window[r] + data_offset) + 4 * i);
-                acc.x += v.x;
-                acc.y += v.y;
-                acc.z += v.z;
-                acc.w += v.w;
-            }
+#pragma unroll
+            for (int r = 0; r < kMaxPeerRanks; ++r)
+                if (r < world) {
+                    acc.x += v[r].x;
+                    acc.y += v[r].y;
+                    acc.z += v[r].z;
+                    acc.w += v[r].w;
+                }
             reinterpret_cast<float4*>(local)[i] = acc;
         }
     } else {
         for (int i = tid; i < n; i += nthreads) {
+            float v[kMaxPeerRanks];
+#pragma unroll
+            for (int r = 0; r < kMaxPeerRanks; ++r)
+                if (r < world) v[r] = ld_volatile_f32(reinterpret_cast<const float*>(peers.window[r] + data_offset) + i);
             float acc = 0.0f;
-            for (int r = 0; r < world; ++r)
-                acc += ld_volatile_f32(reinterpret_cast<const float*>(peers.window[r] + data_offset) + i);
+#pragma unroll
+            for (int r = 0; r < kMaxPeerRanks; ++r)
+                if (r < world) acc += v[r];
             local[i] = acc;
         }
     }
