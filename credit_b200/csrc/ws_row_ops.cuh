@@ -81,14 +81,20 @@ struct WsQuantOp : WsRowOpBase<1, 2> {
         const float max_abs = tot[0];
         const float inv = max_abs > 0.0f ? 127.0f / max_abs : 0.0f;
         if (rank == 0 && threadIdx.x == 0) p.row_out[row] = max_abs / 127.0f;
-        char4* out = reinterpret_cast<char4*>(static_cast<signed char*>(p.y) + static_cast<size_t>(row) * cols + col0);
-        auto q8 = [&](float x) {   // round half to even, as torch.round
-            return static_cast<signed char>(static_cast<int>(fminf(fmaxf(rintf(x * inv), -127.0f), 127.0f)));
+        // Round half to even, as torch.round, then clamp: clamp first (same result: the bounds are
+        // integers), then add 1.5 * 2^23, whose sum is rounded to a whole number by the adder itself; the
+        // low byte of the sum's bit pattern is the two's-complement int8. No conversion instructions
+        // (they run at a quarter of the rate of an add), bit-identical to clamp(rint(x * inv)).
+        auto q8 = [&](float x) {
+            return __float_as_uint(fminf(fmaxf(x * inv, -127.0f), 127.0f) + 12582912.0f);
         };
+        uint32_t* out = reinterpret_cast<uint32_t*>(static_cast<signed char*>(p.y) + static_cast<size_t>(row) * cols + col0);
 #pragma unroll 4
         for (int v = threadIdx.x; v < nvec; v += THREADS) {
             const float4 q = vec(tiles[0], v);
-            out[v] = make_char4(q8(q.x), q8(q.y), q8(q.z), q8(q.w));
+            const uint32_t lo = __byte_perm(q8(q.x), q8(q.y), 0x0040);   // bytes: x.b0, y.b0
+            const uint32_t hi = __byte_perm(q8(q.z), q8(q.w), 0x0040);
+            out[v] = __byte_perm(lo, hi, 0x5410);
         }
     }
 };
@@ -296,22 +302,26 @@ struct WsSoftmaxBwdOp : WsRowOpBase<2, 4> {
     }
     __device__ __forceinline__ static void pass1(State&, const uint4* const (&tiles)[2], int nvec, const float4&,
                                                  float (&part)[4]) {
-        float m = -INFINITY, s = 0.0f, t = 0.0f;
-#pragma unroll 2
+        // the thread's own maximum first (a pass over shared memory, no exponentials), then the sums at
+        // that scale in four independent chains: no branch and no rescaling inside the loop, so the
+        // exponentials of several vectors are in flight at once
+        float m = -INFINITY;
+#pragma unroll 4
+        for (int v = threadIdx.x; v < nvec; v += THREADS) {
+            const float4 x = vec(tiles[0], v);
+            m = fmaxf(m, fmaxf(fmaxf(x.x, x.y), fmaxf(x.z, x.w)));
+        }
+        const float mm = m == -INFINITY ? 0.0f : m;   // nothing but -inf: every term below is exp(-inf) = 0
+        float s4[4] = {0.0f, 0.0f, 0.0f, 0.0f}, t4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll 4
         for (int v = threadIdx.x; v < nvec; v += THREADS) {
             const float4 x = vec(tiles[0], v), g = vec(tiles[1], v);
-            const float c = fmaxf(fmaxf(x.x, x.y), fmaxf(x.z, x.w));
-            if (c > m) {              // a new maximum: bring the sums so far to its scale
-                const float f = rescale(m, c);
-                s *= f;
-                t *= f;
-                m = c;
-            }
-            const float mm = m == -INFINITY ? 0.0f : m;   // nothing but -inf so far: every term below is exp(-inf) = 0
             const float e0 = __expf(x.x - mm), e1 = __expf(x.y - mm), e2 = __expf(x.z - mm), e3 = __expf(x.w - mm);
-            s += (e0 + e1) + (e2 + e3);
-            t = fmaf(e0, g.x, fmaf(e1, g.y, fmaf(e2, g.z, fmaf(e3, g.w, t))));
+            s4[0] += e0; s4[1] += e1; s4[2] += e2; s4[3] += e3;
+            t4[0] = fmaf(e0, g.x, t4[0]); t4[1] = fmaf(e1, g.y, t4[1]);
+            t4[2] = fmaf(e2, g.z, t4[2]); t4[3] = fmaf(e3, g.w, t4[3]);
         }
+        const float s = (s4[0] + s4[1]) + (s4[2] + s4[3]), t = (t4[0] + t4[1]) + (t4[2] + t4[3]);
         part[0] = m; part[1] = s; part[2] = t; part[3] = 0.0f;
     }
     __device__ __forceinline__ static void pass2(State&, const uint4* const (&tiles)[2], int nvec, const float4&,
@@ -319,10 +329,11 @@ struct WsSoftmaxBwdOp : WsRowOpBase<2, 4> {
                                                  uint32_t) {
         const float m = tot[0];
         const float inv_sum = 1.0f / tot[1];
-        const float dot = tot[2] * inv_sum;
+        const float neg_dot_scaled = -(tot[2] * inv_sum) * inv_sum;
         float4* out = reinterpret_cast<float4*>(static_cast<float*>(p.y) + static_cast<size_t>(row) * cols + col0);
-        auto f = [&](float xv, float gv) { return __expf(xv - m) * inv_sum * (gv - dot); };
-#pragma unroll 2
+        // p * (g - dot) = e * (g / sum - dot / sum): one fused operation and one product per element
+        auto f = [&](float xv, float gv) { return __expf(xv - m) * fmaf(gv, inv_sum, neg_dot_scaled); };
+#pragma unroll 4
         for (int v = threadIdx.x; v < nvec; v += THREADS) {
             const float4 x = vec(tiles[0], v), g = vec(tiles[1], v);
             __stcs(out + v, make_float4(f(x.x, g.x), f(x.y, g.y), f(x.z, g.z), f(x.w, g.w)));
