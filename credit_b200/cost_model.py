@@ -244,3 +244,60 @@ def best_cluster_size(predictions: list[ClusterPrediction], tie: float = 0.01) -
         raise ValueError("no predictions")
     lowest = min(p.predicted_ms for p in predictions)
     return min(p.cluster_size for p in predictions if p.predicted_ms <= lowest * (1.0 + tie))
+
+
+# ---------------------------------------------------------------------------
+# The planner's rule for the warp-specialised kernels (launch.cu: plan_static), restated so that
+# a host can know the launch without a GPU. Calibrated on a B200 sweep of cluster size x ring
+# depth: small clusters cover more SMs and spread a row's fixed costs over longer slices, a ring
+# of three stages costs 5 - 20 %, clusters of 16 are never worth it where 8 fits.
+# ---------------------------------------------------------------------------
+WS_CONTROL_BYTES = 22528          # control block at the start of a CTA's dynamic shared memory
+WS_OUTPUT_THREADS = 256           # 8 output warps (threads = 352)
+_WS_WANTED_STAGES = {"lars_momentum": 6, "weighted_var_backward": 3, "softmax_logits_backward": 3, "rowwise_quant": 3}
+_WS_ROW_OPS = ("weighted_var_backward", "pearson_backward", "softmax_logits_backward", "lars_momentum", "rowwise_quant")
+
+
+def ws_plan_rule(workload: str, cols: int, elem_bytes: int, arrays_in: int, column_sums: bool = False,
+                 max_smem: int = 232448, max_cluster: int = 16) -> tuple[int, int] | None:
+    """(cluster size, ring stages) the library launches for a 16-byte aligned row of `cols` elements
+    when the caller leaves both to it, or None where no warp-specialised plan fits (the library
+    then falls back to its other kernels). `arrays_in`: arrays staged per row; `column_sums`:
+    LayerNorm backward with dgamma/dbeta (half the elements per thread). fp32 RMSNorm is not
+    planned here: the library keeps its lock-step kernel for it."""
+    if min(cols, elem_bytes, arrays_in) <= 0:
+        raise ValueError("all sizes must be positive")
+    row_op = workload in _WS_ROW_OPS
+    max_slice = (1 << 30) if row_op else WS_OUTPUT_THREADS * (32 if column_sums else 64)
+
+    def slice_elems(p: int) -> int:
+        return -(-(-(-cols // p)) // 64) * 64
+
+    def stage_bytes(p: int) -> int:
+        return arrays_in * slice_elems(p) * elem_bytes
+
+    def fits(p: int, stages: int) -> bool:
+        return slice_elems(p) <= max_slice and WS_CONTROL_BYTES + stages * stage_bytes(p) <= max_smem
+
+    sizes = [p for p in (1, 2, 4, 8, 16) if p <= max_cluster]
+    wanted = _WS_WANTED_STAGES.get(workload, 4)
+    with3 = next((p for p in sizes if fits(p, 3)), 0)
+    with_wanted = next((p for p in sizes if fits(p, wanted)), 0)
+    cluster = with_wanted or with3
+    if cluster == 16 and 0 < with3 <= 8:
+        cluster = with3
+    if cluster == 0:
+        return None
+    per_stage = stage_bytes(cluster)
+
+    def most(limit: int) -> int:
+        return min(8, (limit - WS_CONTROL_BYTES) // per_stage)
+
+    if row_op:
+        stages = 6
+    else:
+        half = (max_smem - 2048) // 2
+        stages = most(half) if most(half) >= 6 else most(max_smem)
+    while stages > 3 and WS_CONTROL_BYTES + stages * per_stage > max_smem:
+        stages -= 1
+    return cluster, stages

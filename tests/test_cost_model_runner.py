@@ -129,6 +129,23 @@ def test_warp_specialised_row_period_model():
         cost_model.predict_ws_ms(0, 4096, 8, 15, 352, 2, 1, 1, 6)
 
 
+def test_planner_rule_restated_in_python():
+    """cost_model.ws_plan_rule at shapes whose library plans are known from B200 runs (the GPU suite
+    compares the two over the whole sweep)."""
+    rule = cost_model.ws_plan_rule
+    assert rule("layernorm_backward_stats", 65536, 2, 2, column_sums=True) == (8, 6)     # C4
+    assert rule("layernorm_forward", 131072, 2, 1) == (8, 6)                             # C3
+    assert rule("layernorm_backward", 65536, 4, 2) == (8, 3)        # 16 never replaces an 8 that fits
+    assert rule("layernorm_backward", 8192, 4, 2) == (2, 6)         # P = 1 would have three stages only
+    assert rule("layernorm_forward", 4096, 2, 1) == (1, 8)          # short slice: 8 stages in half the shared memory
+    assert rule("lars_momentum", 16384, 4, 3) == (8, 6)             # LARS wants six stages
+    assert rule("weighted_var_backward", 65536, 4, 3) == (16, 4)
+    assert rule("pearson_backward", 16384, 4, 2) == (4, 6)
+    assert rule("layernorm_forward", 1 << 21, 2, 1) is None         # no slice fits the output threads
+    with pytest.raises(ValueError):
+        rule("layernorm_forward", 0, 2, 1)
+
+
 def test_best_cluster_size_prefers_smaller_on_tie():
     p = [cost_model.ClusterPrediction(8, 1.0, 1, 1.0, 1.0), cost_model.ClusterPrediction(4, 1.0, 1, 1.0, 1.0)]
     assert cost_model.best_cluster_size(p) == 4

@@ -513,6 +513,33 @@ def test_layernorm_backward_stats_automatic_plan_is_warp_specialised():
     assert N.plan(N.WL_LAYERNORM_BACKWARD_STATS, 8192, 65536, N.BF16, {"threads": 512}).threads == 512
 
 
+def test_python_restatement_of_the_planner_rule_matches_the_library():
+    """cost_model.ws_plan_rule against credit_plan over the sweep shapes and the target shapes."""
+    from credit_b200 import cost_model
+
+    cases = [("layernorm_backward", N.WL_LAYERNORM_BACKWARD, 2048, N.F32, 2, False),
+             ("layernorm_forward", N.WL_LAYERNORM_FORWARD, 4096, N.BF16, 1, False),
+             ("layernorm_backward_stats", N.WL_LAYERNORM_BACKWARD_STATS, 8192, N.BF16, 2, True),
+             ("rmsnorm_forward", N.WL_RMSNORM_FORWARD, 1024, N.BF16, 1, False),
+             ("weighted_var_backward", N.WL_WEIGHTED_VAR_BACKWARD, 4096, N.F32, 3, False),
+             ("pearson_backward", N.WL_PEARSON_BACKWARD, 4096, N.F32, 2, False),
+             ("softmax_logits_backward", N.WL_SOFTMAX_LOGITS_BACKWARD, 4096, N.F32, 2, False),
+             ("lars_momentum", N.WL_LARS_MOMENTUM, 4096, N.F32, 3, False),
+             ("rowwise_quant", N.WL_ROWWISE_QUANT, 4096, N.F32, 1, False)]
+    for name, wl, rows, dtype, arrays_in, sums in cases:
+        for cols in (4096, 8192, 16384, 32768, 65536, 131072):
+            want = cost_model.ws_plan_rule(name, cols, 2 if dtype == N.BF16 else 4, arrays_in, column_sums=sums)
+            try:
+                plan = N.plan(wl, rows, cols, dtype)
+            except N.UnsupportedShape:
+                assert want is None, (name, cols)
+                continue
+            if want is None:
+                assert plan.threads != 352, (name, cols)      # the library fell back to another kernel
+            else:
+                assert (plan.threads, plan.cluster_size, plan.stages) == (352,) + want, (name, cols)
+
+
 def test_layernorm_backward_stats_headline_width():
     rows, cols = 40, 65536
     inputs = W.make_layernorm_backward_stats_inputs(rows, cols, "cpu", seed=0)
