@@ -59,6 +59,7 @@ ROW_CASES = [
 ]
 E2E_KEYS = ("rmsnorm_forward", "layernorm_forward", "layernorm_backward_stats")   # workloads with a host-buffer entry point
 OTHER_ITERS = 50
+BURST_IDLE_S = 1.0     # idle time before a burst measurement
 SUSTAINED_S = 1.5     # length of the back-to-back run reported beside each burst figure
 
 
@@ -298,6 +299,15 @@ class RowCase:
                 else "inputs of one launch are larger than the 126 MB L2")
 
 
+def idle_before_burst() -> None:
+    """A burst figure is a kernel timed from an idle GPU: the previous workload's sustained loop leaves
+    the board at its power limit for a few hundred milliseconds (the `clocks` block of each figure
+    shows which state it was measured in)."""
+    import torch
+    torch.cuda.synchronize()
+    time.sleep(BURST_IDLE_S)
+
+
 def timed_ms(fn, iters: int, warmup: int = 3, min_region_ms: float = 0.0):
     """ms per call (CUDA events on the current stream), the wall-clock window of the region and
     the iterations timed. With `min_region_ms` the iteration count grows until the timed region
@@ -358,6 +368,7 @@ def measure_row_case(key: str, name: str, rows: int, cols: int, dev, sampler, pe
     wl = {"rmsnorm_forward": N.WL_RMSNORM_FORWARD, "layernorm_forward": N.WL_LAYERNORM_FORWARD,
           "layernorm_backward_stats": N.WL_LAYERNORM_BACKWARD_STATS, "layernorm_backward": N.WL_LAYERNORM_BACKWARD}[name]
     plan = N.plan(wl, rows, cols, N.BF16 if case.dtype == torch.bfloat16 else N.F32)
+    idle_before_burst()
     ms, window, iters = timed_ms(case.call, OTHER_ITERS, min_region_ms=120.0)
     achieved = case.bytes / ms / 1e6
     entry = {
