@@ -592,8 +592,8 @@ def multi_gpu_blocks(dev, rank: int, world: int) -> dict:
                     "what": "credit_layernorm_bwd_allreduce_peer: each rank publishes its [2, cols] vector in a "
                             "window its peers map, one flag per rank, sums in rank order (plain NVLink loads)"}
             del both_p, call_p
-            if peer["status"] != "ok":
-                raise SystemExit(f"peer-memory all-reduce is wrong (error / tolerance = {perr}, status = {status})")
+            # a wrong or timed-out peer all-reduce is reported, not fatal: the headline and the NCCL path
+            # above do not depend on it
         else:
             peer = {"status": "unavailable", "why": note or "another rank could not create or map its window"}
     finally:
