@@ -244,3 +244,48 @@ def test_peer_group_in_a_world_of_one(native_lib):
     assert lib.credit_peer_group_create(ctypes.byref(ctypes.c_void_p()), 17, 0, 1000, handle) == N.ERR_INVALID_ARGUMENT
     assert lib.credit_peer_group_create(ctypes.byref(ctypes.c_void_p()), 2, 2, 1000, handle) == N.ERR_INVALID_ARGUMENT
     assert lib.credit_layernorm_bwd_allreduce_peer(None, buf.data_ptr(), 1000, None) == N.ERR_INVALID_ARGUMENT
+
+
+def _peer_timeout_worker(rank: int, world: int, port: int, out):
+    """Only rank 0 calls the all-reduce: its bounded wait for rank 1's flag runs out (about a second),
+    the kernel returns, the group's status word says so and the buffer is left as it was. No GPU
+    faults or hangs: the wait is a polling loop with a time limit."""
+    import torch.distributed as dist
+
+    from credit_b200 import sharding
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    peers = None
+    try:
+        peers = sharding.PeerGroup(world, rank, max_cols=1024)
+        ok = peers.status() == 0
+        if rank == 0:
+            buf = torch.arange(2 * 1024, dtype=torch.float32, device=dev).reshape(2, 1024)
+            want = buf.clone()
+            peers.allreduce(buf)
+            torch.cuda.synchronize()          # returns after the wait has run out
+            ok = ok and peers.status() == 1 and torch.equal(buf, want)
+            # the context is still usable
+            ok = ok and float((buf + 1).sum().item()) == float(want.sum().item()) + buf.numel()
+        out[rank] = ok
+        dist.barrier()
+    finally:
+        if peers is not None:
+            peers.close()
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_peer_allreduce_wait_is_bounded(native_lib):
+    import torch.multiprocessing as mp
+
+    world = 2
+    port = _free_port()
+    with mp.Manager() as manager:
+        out = manager.dict()
+        mp.spawn(_peer_timeout_worker, args=(world, port, out), nprocs=world, join=True)
+        assert dict(out) == {0: True, 1: True}
