@@ -669,6 +669,14 @@ def test_bad_arguments_are_reported_not_fatal():
         N.plan(N.WL_RMSNORM_FORWARD, 8, 1 << 20, N.F32, {"variant": N.VARIANT_BLOCK_SMEM})
     with pytest.raises(ValueError):
         L.launch_rmsnorm_forward((x.cpu(), gamma), (y,))
+    # rings deeper than 8 stages belong to the warp-specialised kernels only; 17 is too deep for any
+    with pytest.raises(N.UnsupportedShape):
+        N.plan(N.WL_RMSNORM_FORWARD, 64, 4096, N.F32, {"threads": 512, "stages": 12})
+    with pytest.raises(N.UnsupportedShape):
+        N.plan(N.WL_ROW_REDUCE, 64, 65536, N.F32, {"load_path": N.LOAD_TMA, "stages": 12})
+    assert N.plan(N.WL_RMSNORM_FORWARD, 64, 4096, N.F32, {"threads": 352, "stages": 12}).stages == 12
+    with pytest.raises(N.CreditError):
+        N.plan(N.WL_RMSNORM_FORWARD, 64, 4096, N.F32, {"stages": 17})
     code = N.load().credit_rmsnorm_forward(None, None, None, 1, 1, 1e-6, 0, None, None)
     assert code == N.ERR_INVALID_ARGUMENT
     # the library still works after failures
