@@ -75,10 +75,14 @@ typedef enum credit_launch_flags {
 } credit_launch_flags;
 
 typedef struct credit_launch_opts {
-    int cluster_size; /* CTAs per row: 1,2,4,8,16; 0 = automatic */
+    int cluster_size; /* CTAs per row: 1,2,4,8,16; 0 = automatic (the smallest cluster whose ring is deep
+                         enough: a rule calibrated on B200 sweeps) */
     int variant;      /* credit_variant */
-    int stages;       /* shared-memory ring depth, 1..8; 0 = automatic */
-    int threads;      /* threads per CTA: 256 or 512; 0 = automatic */
+    int stages;       /* shared-memory ring depth: 1..8, up to 16 for the warp-specialised kernels (which
+                         need at least 3); 0 = automatic */
+    int threads;      /* threads per CTA selects the kernel form: 352 / 608 = warp-specialised pipeline
+                         with 8 / 16 output warps and three service warps (the default for 16-byte
+                         aligned rows, except fp32 RMSNorm), 256 / 512 = lock-step kernels; 0 = automatic */
     int schedule;     /* credit_schedule */
     int load_path;    /* credit_load_path (streaming kernels) */
     int chunk_bytes;  /* ring chunk of the streaming kernels, multiple of 1024; 0 = automatic */
